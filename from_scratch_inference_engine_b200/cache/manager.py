@@ -1,0 +1,295 @@
+"""The cache manager: pages of keys and values, a block table per request and group.
+
+Cache entries (one per writing call of the model's run order) with the same need -
+kv heads, head size, window - form a group.  A group has its own pool of page ids and
+its own block table per request, so layers that keep every key and layers that keep
+a window of them never compete silently for the same pages.  A page id of a group is
+valid in every entry of that group.
+
+Protocol per step, as the reference's (src/kvcache/block_manager.cpp:30-35,
+include/engine/block_manager.hpp:37-60): `reserve` grows the tables to hold the new
+tokens, the kernels write them, `commit` advances the length.  `commit` also gives
+back the pages of a windowed group that no later query can see.  `close` returns
+everything the request holds.  Prefix sharing follows the reference's design
+(src/kvcache/block_manager.cpp:132-221): full pages only, matched by a chained hash and
+confirmed by comparing tokens, reference counted, evicted least recently used first;
+unlike the reference, evictable cached pages count as free, so a pool full of cached
+prefixes cannot block admission.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+from .pool import OutOfPages, PagePool, StateSlots
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What one cache entry stores per token: kv_heads x head_dim keys and as many values.
+    window = 0 keeps every key; window = W keeps what a query can still see of the last W."""
+
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass
+class CacheGroup:
+    need: CacheNeed
+    entries: List[int]            # cache entry ids (positions in the run order) in this group
+    page_size: int
+    num_pages: int
+
+
+@dataclass
+class RequestCache:
+    """What one live request holds: per group a block table (page ids, -1 = given back),
+    the number of committed tokens, and a state slot."""
+
+    request_id: object
+    slot: int
+    tables: List[List[int]]
+    length: int = 0
+    shared_tokens: int = 0        # leading tokens that came from shared prefix pages
+    closed: bool = False
+
+
+@dataclass
+class _PrefixEntry:
+    parent: int
+    tokens: Tuple[int, ...]
+    pages: Tuple[int, ...]        # one page per group
+    last_used: int
+
+
+def _hash_block(parent: int, tokens: Sequence[int]) -> int:
+    """FNV-1a over the parent hash and the page's tokens; matches are confirmed by
+    comparing tokens, so a collision costs a probe, not correctness."""
+    h = (parent ^ 0xCBF29CE484222325) & 0xFFFFFFFFFFFFFFFF
+    for token in tokens:
+        value = token & 0xFFFFFFFFFFFFFFFF
+        for shift in range(0, 64, 8):
+            h ^= (value >> shift) & 0xFF
+            h = (h * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
+    return h
+
+
+def group_needs(needs: Sequence[Optional[CacheNeed]]) -> List[Tuple[CacheNeed, List[int]]]:
+    """Group cache entries by equal need, in order of first appearance."""
+    grouped: Dict[CacheNeed, List[int]] = {}
+    for entry, need in enumerate(needs):
+        if need is not None:
+            grouped.setdefault(need, []).append(entry)
+    return list(grouped.items())
+
+
+class CacheManager:
+    def __init__(self, needs: Sequence[Optional[CacheNeed]], page_size: int,
+                 num_pages, num_slots: int, enable_prefix_cache: bool = False):
+        """`needs[e]` is the need of cache entry e (None for an entry without keys).
+        `num_pages` is one count for every group or a list with one count per group."""
+        if page_size <= 0:
+            raise ValueError("CacheManager: page_size must be positive")
+        grouped = group_needs(needs)
+        counts = list(num_pages) if isinstance(num_pages, (list, tuple)) else \
+            [num_pages] * len(grouped)
+        if len(counts) != len(grouped):
+            raise ValueError(f"CacheManager: {len(grouped)} groups but {len(counts)} page counts")
+        self.page_size = page_size
+        self.groups = [CacheGroup(need, entries, page_size, n)
+                       for (need, entries), n in zip(grouped, counts)]
+        self.pools = [PagePool(g.num_pages) for g in self.groups]
+        self.slots = StateSlots(num_slots)
+        self.entry_group: Dict[int, Tuple[int, int]] = {}      # entry -> (group, index in group)
+        for gi, group in enumerate(self.groups):
+            for index, entry in enumerate(group.entries):
+                self.entry_group[entry] = (gi, index)
+        self.live: Dict[object, RequestCache] = {}
+        # sharing a prefix needs every position's keys to be kept: no windowed group
+        self.prefix_enabled = enable_prefix_cache and all(g.need.window == 0 for g in self.groups)
+        self._prefix: Dict[int, List[_PrefixEntry]] = {}
+        self._tick = 0
+        self.prefix_hits = 0
+
+    # ------------------------------------------------------------------ requests
+    def open(self, request_id) -> RequestCache:
+        if request_id in self.live:
+            raise RuntimeError(f"request {request_id!r} is already open")
+        handle = RequestCache(request_id, self.slots.acquire(), [[] for _ in self.groups])
+        self.live[request_id] = handle
+        return handle
+
+    def close(self, handle: RequestCache) -> None:
+        if handle.closed:
+            raise RuntimeError(f"request {handle.request_id!r} was closed twice")
+        for pool, table in zip(self.pools, handle.tables):
+            for page in table:
+                if page >= 0:
+                    pool.free(page)
+            table.clear()
+        self.slots.release(handle.slot)
+        handle.length = 0
+        handle.shared_tokens = 0
+        handle.closed = True
+        del self.live[handle.request_id]
+
+    def can_open(self) -> bool:
+        return self.slots.num_free > 0
+
+    # --------------------------------------------------------------------- sizes
+    def blocks_for(self, tokens: int) -> int:
+        return (tokens + self.page_size - 1) // self.page_size
+
+    def pages_needed(self, handle: RequestCache, n_new: int) -> List[int]:
+        """Pages each group must add so the request can hold `n_new` more tokens."""
+        want = self.blocks_for(handle.length + n_new)
+        return [max(0, want - len(table)) for table in handle.tables]
+
+    def free_pages(self) -> List[int]:
+        """Free pages per group, counting cached prefix pages nobody else holds."""
+        free = [pool.num_free for pool in self.pools]
+        if self._prefix:
+            for entries in self._prefix.values():
+                for entry in entries:
+                    if all(self.pools[g].ref_count(p) == 1 for g, p in enumerate(entry.pages)):
+                        for g in range(len(free)):
+                            free[g] += 1
+        return free
+
+    def can_reserve(self, handle: RequestCache, n_new: int,
+                    budget: Optional[List[int]] = None) -> bool:
+        budget = self.free_pages() if budget is None else budget
+        return all(n <= b for n, b in zip(self.pages_needed(handle, n_new), budget))
+
+    def max_tokens_per_request(self) -> int:
+        """Tokens one request alone can hold (the full-attention groups bound it)."""
+        full = [g.num_pages for g in self.groups if g.need.window == 0]
+        if not full:
+            return 1 << 62
+        return min(full) * self.page_size
+
+    # ------------------------------------------------------------ step protocol
+    def reserve(self, handle: RequestCache, n_new: int) -> None:
+        needed = self.pages_needed(handle, n_new)
+        if not all(n <= b for n, b in zip(needed, self.free_pages())):
+            raise OutOfPages(f"request {handle.request_id!r} needs {needed} pages, "
+                             f"free are {self.free_pages()}")
+        for g, count in enumerate(needed):
+            for _ in range(count):
+                handle.tables[g].append(self._allocate(g))
+
+    def commit(self, handle: RequestCache, n_new: int) -> None:
+        handle.length += n_new
+        for g, group in enumerate(self.groups):
+            window = group.need.window
+            if window <= 0:
+                continue
+            # the next query sits at position `length` and sees keys > length - window
+            first_needed = handle.length - window + 1
+            table = handle.tables[g]
+            for block in range(min(len(table), max(0, first_needed) // self.page_size)):
+                if table[block] >= 0:
+                    self.pools[g].free(table[block])
+                    table[block] = -1
+
+    def _allocate(self, g: int) -> int:
+        if self.pools[g].num_free == 0:
+            self._evict_one()
+        return self.pools[g].allocate()
+
+    # -------------------------------------------------------------- prefix cache
+    def acquire_prefix(self, handle: RequestCache, tokens: Sequence[int]) -> int:
+        """Share the leading full pages of `tokens` that are cached; returns tokens shared.
+        Only for a request that holds nothing yet (src/kvcache/block_manager.cpp:132-173)."""
+        if not self.prefix_enabled or handle.length != 0 or any(handle.tables):
+            return 0
+        ps = self.page_size
+        parent = 0
+        matched = 0
+        for b in range(len(tokens) // ps):
+            span = tuple(tokens[b * ps:(b + 1) * ps])
+            h = _hash_block(parent, span)
+            found = None
+            for entry in self._prefix.get(h, ()):
+                if entry.parent == parent and entry.tokens == span:
+                    found = entry
+                    break
+            if found is None:
+                break
+            self._tick += 1
+            found.last_used = self._tick
+            for g, page in enumerate(found.pages):
+                self.pools[g].incref(page)
+                handle.tables[g].append(page)
+            parent = h
+            matched += ps
+        handle.length = matched
+        handle.shared_tokens = matched
+        if matched:
+            self.prefix_hits += 1
+        return matched
+
+    def register_prefix(self, handle: RequestCache, tokens: Sequence[int]) -> None:
+        """Remember the request's full pages covering `tokens` for later requests
+        (src/kvcache/block_manager.cpp:175-204); the cache holds its own reference."""
+        if not self.prefix_enabled:
+            return
+        ps = self.page_size
+        full = min(min(len(t) for t in handle.tables) if handle.tables else 0,
+                   min(len(tokens), handle.length) // ps)
+        parent = 0
+        for b in range(full):
+            span = tuple(tokens[b * ps:(b + 1) * ps])
+            h = _hash_block(parent, span)
+            entries = self._prefix.setdefault(h, [])
+            if not any(e.parent == parent and e.tokens == span for e in entries):
+                pages = tuple(table[b] for table in handle.tables)
+                for g, page in enumerate(pages):
+                    self.pools[g].incref(page)
+                self._tick += 1
+                entries.append(_PrefixEntry(parent, span, pages, self._tick))
+            parent = h
+
+    def _evict_one(self) -> bool:
+        victim = None
+        for h, entries in self._prefix.items():
+            for index, entry in enumerate(entries):
+                if all(self.pools[g].ref_count(p) == 1 for g, p in enumerate(entry.pages)):
+                    if victim is None or entry.last_used < victim[2].last_used:
+                        victim = (h, index, entry)
+        if victim is None:
+            return False
+        h, index, entry = victim
+        for g, page in enumerate(entry.pages):
+            self.pools[g].free(page)
+        del self._prefix[h][index]
+        if not self._prefix[h]:
+            del self._prefix[h]
+        return True
+
+    def clear_prefix_cache(self) -> None:
+        for entries in self._prefix.values():
+            for entry in entries:
+                for g, page in enumerate(entry.pages):
+                    self.pools[g].free(page)
+        self._prefix.clear()
+
+    # ----------------------------------------------------------------- checking
+    def check(self) -> None:
+        """No page lost, none held twice without a matching reference count."""
+        for g, pool in enumerate(self.pools):
+            pool.check()
+            holders = [0] * pool.num_pages
+            for handle in self.live.values():
+                for page in handle.tables[g]:
+                    if page >= 0:
+                        holders[page] += 1
+            for entries in self._prefix.values():
+                for entry in entries:
+                    holders[entry.pages[g]] += 1
+            for page, count in enumerate(holders):
+                if count != pool.ref_count(page):
+                    raise AssertionError(f"group {g} page {page}: {count} holders but "
+                                         f"reference count {pool.ref_count(page)}")

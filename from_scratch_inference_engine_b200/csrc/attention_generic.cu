@@ -1,0 +1,254 @@
+// Causal grouped-query attention over the paged cache, for any head size, group size
+// and page size, in 32-bit arithmetic on CUDA cores.  It is the attention of the
+// float32 path (storage float) and the fallback of the bfloat16 path (storage bf16)
+// for head sizes the tensor-core kernel does not take.
+//
+// Work is cut into tiles of ROWS query rows of one request and one kv head, where a
+// row is a (new token, query head of the group) pair: row = token * group + g.  So a
+// prompt portion and a single decoded token are the same case with different row
+// counts, and all heads of a group share each key/value tile.  A tile's key range may
+// be split over blockIdx.z; split results are merged by attn_combine_kernel.
+//
+// Mathematics as the reference's attention (src/model/nn.cpp:151-226): scores
+// (q.k)/sqrt(head_dim) over keys 0..position (inclusive, optionally only the last
+// `window` of them), softmax, weighted sum of values; here as a running softmax in
+// 32-bit like the reference GPU kernel does in 64-bit (src/cuda/device.cu:139-190).
+#include "common.cuh"
+#include <math.h>
+
+namespace fsie {
+
+constexpr int ROWS = 32;          // query rows per tile
+constexpr int WARPS = 8;          // warps per block; each owns ROWS / WARPS rows
+constexpr int RPW = ROWS / WARPS;
+constexpr int KT = 32;            // keys per shared-memory tile (one per lane)
+constexpr int MAX_DPL = 8;        // head_dim <= 32 * MAX_DPL
+
+struct AttnParams {
+    const void* q; int q_ld;                 // [tokens, q_ld]; head h of token t at t*q_ld + h*head_dim
+    const void* k_pages; const void* v_pages;
+    long long page_stride; int page_size;    // elements between pages; slots per page
+    const int* block_tables; int bt_stride;  // [items, bt_stride] page ids (-1 = released)
+    const int* tile_item; const int* tile_row0;   // [tiles]
+    const int* item_qstart; const int* item_qlen; const int* item_pos0;   // [items]
+    void* out; int out_ld;                   // [tokens, out_ld]
+    float* part_o; float* part_ml;           // [nsplit, tokens, heads, head_dim], [nsplit, tokens, heads, 2]
+    int tokens, heads, kv_heads, head_dim, window, nsplit;
+    float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+attn_generic_kernel(const AttnParams p) {
+    extern __shared__ float smem[];
+    const int hd = p.head_dim;
+    float* qs = smem;                         // [ROWS][hd]
+    float* ks = qs + ROWS * hd;               // [KT][hd + 1]
+    float* vs = ks + KT * (hd + 1);           // [KT][hd]
+    __shared__ long long key_base[KT];
+
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int group = p.heads / p.kv_heads;
+    const int item = p.tile_item[tile];
+    const int row0 = p.tile_row0[tile];
+    const int qstart = p.item_qstart[item], qlen = p.item_qlen[item], pos0 = p.item_pos0[item];
+    const int nrows = min(ROWS, qlen * group - row0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const T* q = (const T*)p.q;
+    const T* kp = (const T*)p.k_pages;
+    const T* vp = (const T*)p.v_pages;
+    const int* bt = p.block_tables + (size_t)item * p.bt_stride;
+
+    // stage the tile's query rows, pre-multiplied by the scale
+    for (int e = tid; e < nrows * hd; e += blockDim.x) {
+        const int r = e / hd, d = e - r * hd;
+        const int row = row0 + r;
+        const int tok = qstart + row / group, h = kvh * group + row % group;
+        qs[r * hd + d] = to_float(q[(size_t)tok * p.q_ld + h * hd + d]) * p.scale;
+    }
+
+    // key range of the tile: up to the last row's position, from the first row's window start
+    const int pos_first = pos0 + row0 / group;
+    const int pos_last = pos0 + (row0 + nrows - 1) / group;
+    int kbegin = 0;
+    if (p.window > 0) kbegin = max(0, pos_first - p.window + 1);
+    int kend = pos_last + 1;
+    if (p.nsplit > 1) {
+        const int span = kend - kbegin;
+        int chunk = (span + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + KT - 1) / KT) * KT;
+        const int b = kbegin + split * chunk;
+        kend = min(kend, b + chunk);
+        kbegin = b;
+    }
+
+    float m[RPW], l[RPW], acc[RPW][MAX_DPL];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        m[i] = -INFINITY; l[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < MAX_DPL; ++c) acc[i][c] = 0.f;
+    }
+
+    for (int k0 = kbegin; k0 < kend; k0 += KT) {
+        __syncthreads();   // previous tile fully consumed (and qs staged, first time)
+        if (tid < KT) {
+            const int kj = k0 + tid;
+            long long base = -1;
+            if (kj < kend) {
+                const int page = bt[kj / p.page_size];
+                if (page >= 0)
+                    base = (long long)page * p.page_stride +
+                           ((long long)kvh * p.page_size + kj % p.page_size) * hd;
+            }
+            key_base[tid] = base;
+        }
+        __syncthreads();
+        for (int e = tid; e < KT * hd; e += blockDim.x) {
+            const int j = e / hd, d = e - j * hd;
+            const long long base = key_base[j];
+            ks[j * (hd + 1) + d] = base >= 0 ? to_float(kp[base + d]) : 0.f;
+            vs[j * hd + d] = base >= 0 ? to_float(vp[base + d]) : 0.f;
+        }
+        __syncthreads();
+        const int kj = k0 + lane;
+        const bool key_ok = kj < kend && key_base[lane] >= 0;
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {
+            const int r = warp * RPW + i;
+            if (r >= nrows) continue;                 // uniform per warp
+            const int pos = pos0 + (row0 + r) / group;
+            if (k0 > pos) continue;                   // whole tile is in this row's future
+            const bool seen = key_ok && kj <= pos && (p.window <= 0 || kj > pos - p.window);
+            float s = 0.f;
+            const float* qr = qs + r * hd;
+            const float* kr = ks + lane * (hd + 1);
+            for (int d = 0; d < hd; ++d) s = fmaf(qr[d], kr[d], s);
+            s = seen ? s : -INFINITY;
+            const float m_new = fmaxf(m[i], warp_max(s));
+            if (m_new == -INFINITY) continue;         // nothing visible yet
+            const float corr = expf(m[i] - m_new);  // m[i] = -inf gives 0
+            const float pj = seen ? expf(s - m_new) : 0.f;
+            l[i] = l[i] * corr + warp_sum(pj);
+            m[i] = m_new;
+#pragma unroll
+            for (int c = 0; c < MAX_DPL; ++c) acc[i][c] *= corr;
+            for (int j = 0; j < KT; ++j) {
+                const float pw = __shfl_sync(0xffffffffu, pj, j);
+                const float* vr = vs + j * hd;
+#pragma unroll
+                for (int c = 0; c < MAX_DPL; ++c) {
+                    const int d = lane + 32 * c;
+                    if (d < hd) acc[i][c] = fmaf(pw, vr[d], acc[i][c]);
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        const int r = warp * RPW + i;
+        if (r >= nrows) continue;
+        const int row = row0 + r;
+        const int tok = qstart + row / group, h = kvh * group + row % group;
+        if (p.nsplit == 1) {
+            T* o = (T*)p.out + (size_t)tok * p.out_ld + h * hd;
+            const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+#pragma unroll
+            for (int c = 0; c < MAX_DPL; ++c) {
+                const int d = lane + 32 * c;
+                if (d < hd) o[d] = from_float<T>(acc[i][c] * inv);
+            }
+        } else {
+            const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
+            float* o = p.part_o + idx * hd;
+#pragma unroll
+            for (int c = 0; c < MAX_DPL; ++c) {
+                const int d = lane + 32 * c;
+                if (d < hd) o[d] = acc[i][c];
+            }
+            if (lane == 0) { p.part_ml[idx * 2] = m[i]; p.part_ml[idx * 2 + 1] = l[i]; }
+        }
+    }
+}
+
+// Merge the splits of one (token, head): o = sum_z acc_z e^(m_z - M) / sum_z l_z e^(m_z - M).
+template <typename T>
+__global__ void attn_combine_kernel(const float* __restrict__ part_o,
+                                    const float* __restrict__ part_ml, T* __restrict__ out,
+                                    int out_ld, int tokens, int heads, int hd, int nsplit) {
+    const int tok = blockIdx.x, h = blockIdx.y;
+    float mmax = -INFINITY;
+    for (int z = 0; z < nsplit; ++z)
+        mmax = fmaxf(mmax, part_ml[(((size_t)z * tokens + tok) * heads + h) * 2]);
+    float denom = 0.f;
+    for (int z = 0; z < nsplit; ++z) {
+        const size_t idx = ((size_t)z * tokens + tok) * heads + h;
+        const float mz = part_ml[idx * 2];
+        if (mz != -INFINITY) denom += part_ml[idx * 2 + 1] * expf(mz - mmax);
+    }
+    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.f;
+        for (int z = 0; z < nsplit; ++z) {
+            const size_t idx = ((size_t)z * tokens + tok) * heads + h;
+            const float mz = part_ml[idx * 2];
+            if (mz != -INFINITY) o += part_o[idx * hd + d] * expf(mz - mmax);
+        }
+        out[(size_t)tok * out_ld + h * hd + d] = from_float<T>(o * inv);
+    }
+}
+
+}  // namespace fsie
+
+using namespace fsie;
+
+extern "C" {
+
+int fsie_attn_generic_rows() { return ROWS; }
+
+// Launch over `tiles` row tiles.  With nsplit > 1 the caller provides part_o
+// [nsplit, tokens, heads, head_dim] and part_ml [nsplit, tokens, heads, 2] in float.
+int fsie_attn_generic(const void* q, int q_ld, const void* k_pages, const void* v_pages,
+                      long long page_stride, int page_size, const int* block_tables, int bt_stride,
+                      const int* tile_item, const int* tile_row0, int tiles,
+                      const int* item_qstart, const int* item_qlen, const int* item_pos0,
+                      void* out, int out_ld, float* part_o, float* part_ml, int tokens, int heads,
+                      int kv_heads, int head_dim, int window, int nsplit, float scale, int dtype,
+                      cudaStream_t stream) {
+    if (tiles <= 0 || tokens <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 32 * MAX_DPL || kv_heads <= 0 || heads % kv_heads != 0 ||
+        nsplit < 1 || page_size <= 0)
+        return ERR_BAD_ARGUMENT;
+    if (nsplit > 1 && (!part_o || !part_ml)) return ERR_BAD_ARGUMENT;
+    AttnParams p;
+    p.q = q; p.q_ld = q_ld; p.k_pages = k_pages; p.v_pages = v_pages;
+    p.page_stride = page_stride; p.page_size = page_size;
+    p.block_tables = block_tables; p.bt_stride = bt_stride;
+    p.tile_item = tile_item; p.tile_row0 = tile_row0;
+    p.item_qstart = item_qstart; p.item_qlen = item_qlen; p.item_pos0 = item_pos0;
+    p.out = out; p.out_ld = out_ld; p.part_o = part_o; p.part_ml = part_ml;
+    p.tokens = tokens; p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
+    p.window = window; p.nsplit = nsplit; p.scale = scale;
+    const size_t smem = sizeof(float) * ((size_t)ROWS * head_dim + (size_t)KT * (head_dim + 1) +
+                                         (size_t)KT * head_dim);
+    dim3 grid(tiles, kv_heads, nsplit);
+    if (dtype == DTYPE_F32) {
+        cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_generic_kernel<float><<<grid, WARPS * 32, smem, stream>>>(p);
+    } else {
+        cudaFuncSetAttribute(attn_generic_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_generic_kernel<bf16><<<grid, WARPS * 32, smem, stream>>>(p);
+    }
+    int rc = FSIE_LAUNCH_CHECK();
+    if (rc != 0 || nsplit == 1) return rc;
+    dim3 cgrid(tokens, heads);
+    const int threads = head_dim >= 128 ? 128 : (head_dim >= 64 ? 64 : 32);
+    if (dtype == DTYPE_F32)
+        attn_combine_kernel<float><<<cgrid, threads, 0, stream>>>(part_o, part_ml, (float*)out, out_ld, tokens, heads, head_dim, nsplit);
+    else
+        attn_combine_kernel<bf16><<<cgrid, threads, 0, stream>>>(part_o, part_ml, (bf16*)out, out_ld, tokens, heads, head_dim, nsplit);
+    return FSIE_LAUNCH_CHECK();
+}
+
+}  // extern "C"

@@ -1,0 +1,129 @@
+"""The step context: the batch of one step as device arrays every part can read.
+
+It is mixer-agnostic: tokens packed end to end, their absolute positions, one record
+per request (where its tokens start, how many, its first position, its state slot), and
+per cache group the block tables and the physical slot of every new token.  All of it
+reaches the device in one copy from pinned host memory.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+
+@dataclass
+class GroupStep:
+    page_size: int
+    block_tables: torch.Tensor      # int32 [items, max_blocks], -1 where no page is held
+    slot_of: torch.Tensor           # int32 [tokens], page * page_size + offset of each new token
+
+
+@dataclass
+class Tiles:
+    item: torch.Tensor              # int32 [count]
+    row0: torch.Tensor              # int32 [count]
+    count: int
+
+
+class PinnedRing:
+    """A few pinned staging buffers used in turn; a buffer is reused only after the copy
+    that last read it has finished."""
+
+    def __init__(self, depth: int = 4):
+        self.depth = depth
+        self.buffers: List[Optional[torch.Tensor]] = [None] * depth
+        self.events: List[Optional[torch.cuda.Event]] = [None] * depth
+        self.next = 0
+
+    def stage(self, host: np.ndarray, device: torch.device) -> torch.Tensor:
+        i = self.next
+        self.next = (i + 1) % self.depth
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        n = host.size
+        if self.buffers[i] is None or self.buffers[i].numel() < n:
+            self.buffers[i] = torch.empty(max(n, 1024) * 2, dtype=torch.int32).pin_memory()
+        staging = self.buffers[i][:n]
+        staging.numpy()[:] = host
+        out = staging.to(device, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.events[i] = event
+        return out
+
+
+class StepContext:
+    def __init__(self, runtime, ring: PinnedRing, scratch: Dict[str, torch.Tensor],
+                 error: torch.Tensor, token_ids: Sequence[int], q_start: Sequence[int],
+                 q_len: Sequence[int], pos0: Sequence[int], slots: Sequence[int],
+                 group_tables: Sequence[Tuple[int, List[List[int]]]]):
+        """group_tables: per cache group (page_size, block table of each item)."""
+        self.runtime = runtime
+        self._ring, self._scratch, self.error = ring, scratch, error
+        self.num_tokens = T = len(token_ids)
+        self.num_items = I = len(q_len)
+        self.h_qstart = np.asarray(q_start, dtype=np.int32)
+        self.h_qlen = np.asarray(q_len, dtype=np.int32)
+        self.h_pos0 = np.asarray(pos0, dtype=np.int32)
+        self.h_slots = np.asarray(slots, dtype=np.int32)
+        self.max_context = int((self.h_pos0 + self.h_qlen).max()) if I else 0
+        positions = np.concatenate([np.arange(p, p + n, dtype=np.int32)
+                                    for p, n in zip(pos0, q_len)]) if I else np.zeros(0, np.int32)
+        token_item = np.repeat(np.arange(I, dtype=np.int32), self.h_qlen)
+        parts = [np.asarray(token_ids, dtype=np.int32), positions, self.h_qstart, self.h_qlen,
+                 self.h_pos0, self.h_slots]
+        shapes = []
+        for page_size, tables in group_tables:
+            width = max(1, max((len(t) for t in tables), default=1))
+            table = np.full((I, width), -1, dtype=np.int32)
+            for i, row in enumerate(tables):
+                table[i, :len(row)] = row
+            block = positions // page_size
+            page = table[token_item, block] if T else np.zeros(0, np.int32)
+            slot_of = np.where(page >= 0, page * page_size + positions % page_size, -1)
+            parts += [table.reshape(-1), slot_of.astype(np.int32)]
+            shapes.append((page_size, width))
+        flat = np.concatenate(parts) if parts else np.zeros(0, np.int32)
+        dev = ring.stage(flat, runtime.device)
+        cut = 0
+
+        def take(n):
+            nonlocal cut
+            view = dev[cut:cut + n]
+            cut += n
+            return view
+        self.token_ids, self.positions = take(T), take(T)
+        self.item_qstart, self.item_qlen = take(I), take(I)
+        self.item_pos0, self.item_slots = take(I), take(I)
+        self.groups: List[GroupStep] = []
+        for page_size, width in shapes:
+            tables = take(I * width).view(I, width)
+            self.groups.append(GroupStep(page_size, tables, take(T)))
+        self._tiles: Dict[Tuple[int, int], Tiles] = {}
+
+    def attention_tiles(self, group_size: int, rows_per_tile: int) -> Tiles:
+        """Tiles of `rows_per_tile` query rows, a row being (token, head of the group):
+        row = token_in_item * group_size + head_in_group.  No tile spans two items."""
+        key = (group_size, rows_per_tile)
+        if key not in self._tiles:
+            counts = (self.h_qlen.astype(np.int64) * group_size + rows_per_tile - 1) // rows_per_tile
+            item = np.repeat(np.arange(self.num_items, dtype=np.int32), counts)
+            first = np.cumsum(counts) - counts
+            row0 = (np.arange(int(counts.sum())) - np.repeat(first, counts)) * rows_per_tile
+            dev = self._ring.stage(np.concatenate([item, row0.astype(np.int32)]),
+                                   self.runtime.device)
+            n = item.size
+            self._tiles[key] = Tiles(dev[:n], dev[n:2 * n], n)
+        return self._tiles[key]
+
+    def scratch(self, name: str, numel: int) -> torch.Tensor:
+        """Float32 scratch memory that lives across steps (grown when a step needs more)."""
+        have = self._scratch.get(name)
+        if have is None or have.numel() < numel:
+            have = torch.empty(max(numel, 1), dtype=torch.float32, device=self.runtime.device)
+            self._scratch[name] = have
+        return have

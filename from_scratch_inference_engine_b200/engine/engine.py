@@ -1,0 +1,148 @@
+"""The engine a user drives: requests in, tokens out, one GPU step at a time.
+
+Same control surface as the reference's `Engine` (include/engine/engine.hpp:39-89,
+bindings/module.cpp:104-147): add_request, step, has_work, output, status, preemptions,
+prefix_hits, generate - with the same option names and defaults (block_size, num_blocks,
+seed, max_batch, enable_prefix_cache; max_tokens = 16, eos_id = -1 disables the stop).
+"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..config.registry import load_config
+from ..parts.model import DecoderModel
+from ..sampling.sampler import Sampler, SamplingParams, request_seed
+from ..weights.loader import load_checkpoint
+from .runner import ModelRunner, StepEntry
+from .runtime import Runtime, parse_dtype
+from .scheduler import Scheduler, SeqStatus
+
+
+class LoadedModel:
+    """A model bound to its weights on one GPU (the reference's `Model.from_pretrained`,
+    bindings/module.cpp:66-79)."""
+
+    def __init__(self, config, model: DecoderModel, runtime: Runtime):
+        self.config, self.model, self.runtime = config, model, runtime
+
+    @classmethod
+    def from_pretrained(cls, model_dir, dtype="bfloat16", device="cuda:0",
+                        max_positions: int = 0) -> "LoadedModel":
+        """Read config.json (which names the architecture) and model.safetensors."""
+        config = load_config(model_dir)
+        return cls.from_tensors(config, load_checkpoint(model_dir), dtype, device, max_positions)
+
+    @classmethod
+    def from_tensors(cls, config, tensors, dtype="bfloat16", device="cuda:0",
+                     max_positions: int = 0) -> "LoadedModel":
+        spec = config.build_spec()
+        limit = spec.max_position if spec.max_position > 0 else (max_positions or 32768)
+        runtime = Runtime(device, parse_dtype(dtype), max_positions=limit)
+        model = DecoderModel(spec)
+        model.bind(tensors, runtime)
+        return cls(config, model, runtime)
+
+    def forward(self, ids: Sequence[int]) -> torch.Tensor:
+        """Logits [len(ids), vocab] of one whole sequence (bindings/module.cpp:70-76)."""
+        pages = -(-len(ids) // 16) + 1
+        runner = ModelRunner(self.model, self.runtime, page_size=16, num_pages=pages,
+                             max_requests=1)
+        handle = runner.cache.open(0)
+        logits = runner.step([StepEntry(handle, list(ids), list(range(len(ids))))])
+        runner.raise_on_device_error()
+        return logits
+
+
+class Engine:
+    def __init__(self, model: LoadedModel, block_size: int = 16, num_blocks: int = 2048,
+                 seed: int = 0, max_batch: int = 256, enable_prefix_cache: bool = False,
+                 max_step_tokens: int = 2048):
+        self.model = model
+        self.runner = ModelRunner(model.model, model.runtime, page_size=block_size,
+                                  num_pages=num_blocks, max_requests=max_batch,
+                                  enable_prefix_cache=enable_prefix_cache)
+        self.scheduler = Scheduler(self.runner.cache, max_batch, max_step_tokens,
+                                   self.runner.max_positions)
+        self.sampler = Sampler(model.runtime.device)
+        self.seed = int(seed)
+        self.steps = 0
+        self.tokens_prefilled = 0
+        self.tokens_decoded = 0
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    max_tokens: int = 16, eos_id: int = -1) -> int:
+        params = params or SamplingParams()
+        vocab = self.runner.vocab_size
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise IndexError(f"Engine: token id out of range [0, {vocab})")
+        rid = self.scheduler.next_id
+        seed = params.seed if params.seed is not None else request_seed(self.seed, rid)
+        return self.scheduler.add(prompt, params, max_tokens, eos_id, seed)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def output(self, request_id: int) -> List[int]:
+        return self.scheduler.sequences[request_id].output
+
+    def status(self, request_id: int) -> SeqStatus:
+        return self.scheduler.sequences[request_id].status
+
+    def preemptions(self) -> int:
+        return self.scheduler.preemptions
+
+    def prefix_hits(self) -> int:
+        return self.runner.cache.prefix_hits
+
+    # ---------------------------------------------------------------------- step
+    def step(self) -> int:
+        """One batched step; returns the number of tokens it ran (0 = nothing could run)."""
+        items = self.scheduler.plan()
+        if not items:
+            return 0
+        entries = [StepEntry(item.seq.handle, item.tokens,
+                             [len(item.tokens) - 1] if item.samples else [])
+                   for item in items]
+        logits = self.runner.step(entries)
+        sampling = [item for item in items if item.samples]
+        tokens: List[Optional[int]] = [None] * len(items)
+        if sampling:
+            picked = self.sampler.sample(logits, [i.seq.params for i in sampling],
+                                         [i.seq.seed for i in sampling],
+                                         [len(i.seq.output) for i in sampling])
+            picked_iter = iter(picked)
+            tokens = [next(picked_iter) if item.samples else None for item in items]
+        self.scheduler.finish_step(items, tokens)
+        self.steps += 1
+        for item in items:
+            if item.was_prefill:
+                self.tokens_prefilled += len(item.tokens)
+            else:
+                self.tokens_decoded += 1
+        return sum(len(item.tokens) for item in items)
+
+    def generate(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                 max_tokens: int = 16, eos_id: int = -1) -> List[int]:
+        """Drive the engine until one fresh request completes; returns its tokens."""
+        rid = self.add_request(prompt, params, max_tokens, eos_id)
+        while self.status(rid) is not SeqStatus.Finished:
+            if self.step() == 0:
+                raise RuntimeError("Engine: no request can make progress")
+        return list(self.output(rid))
+
+    def run_until_done(self) -> None:
+        while self.has_work():
+            if self.step() == 0:
+                raise RuntimeError("Engine: no request can make progress")
+
+    def stats(self) -> dict:
+        return {"steps": self.steps, "tokens_prefilled": self.tokens_prefilled,
+                "tokens_decoded": self.tokens_decoded, "preemptions": self.preemptions(),
+                "prefix_hits": self.prefix_hits(),
+                "free_pages": self.runner.cache.free_pages()}

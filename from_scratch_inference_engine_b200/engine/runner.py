@@ -1,0 +1,142 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+`ModelRunner.step` takes portions of prompts and single decoded tokens alike, cut
+anywhere.  It runs only the tokens it is given, as one batch, on top of what earlier
+steps left in the cache, and returns float32 logits at the places asked for.  It owns
+the cache manager and the device memory of the pages and of per-request state.
+Counterpart in the reference: Model::forward_batch (src/model/model.cpp:159-281), which
+returns the last row of each item only.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, RequestCache
+from ..parts.base import LayerCache
+from ..parts.model import DecoderModel
+from .context import PinnedRing, StepContext
+from .runtime import Runtime
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places (indices into these
+    tokens) whose logits are wanted."""
+
+    handle: RequestCache
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class DeviceFault(RuntimeError):
+    """A kernel met an input it had to refuse (token id or position out of range)."""
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, runtime: Runtime, page_size: int = 16,
+                 num_pages=2048, max_requests: int = 256, enable_prefix_cache: bool = False):
+        self.model, self.runtime = model, runtime
+        needs = model.cache_needs()
+        self.cache = CacheManager(needs, page_size, num_pages, max_requests, enable_prefix_cache)
+        device, dtype = runtime.device, runtime.dtype
+        # pages of group g: [page, entry in group, K or V, kv_head, slot, head_dim]
+        self.pages: List[torch.Tensor] = []
+        for group in self.cache.groups:
+            need = group.need
+            self.pages.append(torch.zeros((group.num_pages, len(group.entries), 2, need.kv_heads,
+                                           page_size, need.head_dim), dtype=dtype, device=device))
+        self.states: List[Optional[torch.Tensor]] = []
+        for need in model.state_needs():
+            self.states.append(None if need is None else torch.zeros(
+                (max_requests, *need.shape), dtype=need.dtype, device=device))
+        self.layer_caches: List[LayerCache] = []
+        for index, (_, entry, writes) in enumerate(model.schedule):
+            cache = LayerCache(writes=writes, state=self.states[index])
+            if needs[entry] is not None:
+                g, position = self.cache.entry_group[entry]
+                pages = self.pages[g]
+                cache.group = g
+                cache.k_pages = pages[:, position, 0]
+                cache.v_pages = pages[:, position, 1]
+                cache.page_stride = pages.stride(0)
+            self.layer_caches.append(cache)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        self._ring = PinnedRing()
+        self._scratch: Dict[str, torch.Tensor] = {}
+        self.vocab_size = model.spec.vocab_size
+        limit = model.spec.max_position
+        self.max_positions = limit if limit > 0 else self.cache.max_tokens_per_request()
+
+    # ------------------------------------------------------------------- checks
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise ValueError("step: empty batch")
+        seen = set()
+        for entry in entries:
+            if entry.handle.closed:
+                raise ValueError(f"step: request {entry.handle.request_id!r} is closed")
+            if id(entry.handle) in seen:
+                raise ValueError(f"step: request {entry.handle.request_id!r} appears twice")
+            seen.add(id(entry.handle))
+            n = len(entry.tokens)
+            if n == 0:
+                raise ValueError(f"step: request {entry.handle.request_id!r} brings no tokens")
+            low, high = min(entry.tokens), max(entry.tokens)
+            if low < 0 or high >= self.vocab_size:
+                raise IndexError(f"step: token id out of range [0, {self.vocab_size}) in request "
+                                 f"{entry.handle.request_id!r}")
+            if entry.handle.length + n > self.max_positions:
+                raise ValueError(f"step: request {entry.handle.request_id!r} would reach position "
+                                 f"{entry.handle.length + n}, the limit is {self.max_positions}")
+            for w in entry.want:
+                if not 0 <= w < n:
+                    raise IndexError(f"step: wanted place {w} outside the {n} tokens brought")
+
+    # --------------------------------------------------------------------- step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch; returns float32 logits [wanted places, vocab] in the order of the
+        entries and of their `want`, or None when nothing is wanted."""
+        self._validate(entries)
+        cache = self.cache
+        for entry in entries:
+            cache.reserve(entry.handle, len(entry.tokens))
+        token_ids: List[int] = []
+        q_start, q_len, pos0, slots, want_rows = [], [], [], [], []
+        fresh_slots = []
+        for entry in entries:
+            q_start.append(len(token_ids))
+            q_len.append(len(entry.tokens))
+            pos0.append(entry.handle.length)
+            slots.append(entry.handle.slot)
+            if entry.handle.length == 0:
+                fresh_slots.append(entry.handle.slot)
+            want_rows += [len(token_ids) + w for w in entry.want]
+            token_ids += list(entry.tokens)
+        tables = [(cache.page_size, [e.handle.tables[g] for e in entries])
+                  for g in range(len(cache.groups))]
+        ctx = StepContext(self.runtime, self._ring, self._scratch, self.error, token_ids, q_start,
+                          q_len, pos0, slots, tables)
+        if fresh_slots and any(s is not None for s in self.states):
+            index = torch.tensor(fresh_slots, dtype=torch.long, device=self.runtime.device)
+            for state in self.states:
+                if state is not None:
+                    state.index_fill_(0, index, 0)
+        rows = None
+        if want_rows:
+            rows = self._ring.stage(np.asarray(want_rows, dtype=np.int32), self.runtime.device)
+        logits = self.model.forward(ctx, self.layer_caches, rows)
+        for entry in entries:
+            cache.commit(entry.handle, len(entry.tokens))
+        return logits
+
+    def raise_on_device_error(self) -> None:
+        code = int(self.error.item())
+        if code:
+            self.error.zero_()
+            what = {1: "token id outside the vocabulary", 2: "position outside the table"}
+            raise DeviceFault(what.get(code, f"device error flag {code}"))

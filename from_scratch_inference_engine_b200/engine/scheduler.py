@@ -1,0 +1,203 @@
+"""Continuous batching: admission, prompt portions under a token budget, decoding,
+finishing, and what happens when pages run out.
+
+Policy (the reference's, src/engine/engine.cpp:53-178, plus portions):
+
+* Admission is first come first served: the head of the waiting queue is admitted while
+  fewer than `max_batch` requests run, a state slot is free and the pages of its first
+  portion are free; nothing behind a blocked head is looked at.
+* A step gives one token to every running request that is decoding, then fills what is
+  left of `max_step_tokens` with portions of the prompts (or recomputed contexts) of the
+  running requests that are not yet prefilled, oldest first.  All items draw pages from
+  one budget; a request whose pages do not fit is left out of this step.
+* When no running request can be given anything and more than one is running, the
+  youngest request that holds pages is preempted: everything it holds is given back, it
+  returns to the front of the waiting queue, and when it is admitted again it recomputes
+  prompt + output so far in portions.  Its output continues identically.
+* A request that could never fit (prompt + max_tokens beyond one request's share of the
+  pool or beyond the position limit) is refused when it is added, instead of spinning
+  as the reference does (src/engine/engine.cpp:120-126).
+
+This file decides only; `Engine` in engine.py runs the plans on the GPU.
+"""
+
+from __future__ import annotations
+
+import enum
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence
+
+from ..cache.manager import CacheManager, RequestCache
+from ..sampling.sampler import SamplingParams
+
+
+class SeqStatus(enum.Enum):
+    Waiting = 0
+    Running = 1
+    Finished = 2
+
+
+@dataclass
+class Sequence_:
+    id: int
+    prompt: List[int]
+    params: SamplingParams
+    max_tokens: int
+    eos_id: int
+    seed: int
+    output: List[int] = field(default_factory=list)
+    status: SeqStatus = SeqStatus.Waiting
+    prefilled: bool = False
+    handle: Optional[RequestCache] = None
+    preempted: int = 0
+
+    def context(self) -> List[int]:
+        return self.prompt + self.output
+
+
+@dataclass
+class PlanItem:
+    seq: Sequence_
+    tokens: List[int]
+    samples: bool          # the portion ends the context: logits of its last token are wanted
+    was_prefill: bool
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_batch: int = 256, max_step_tokens: int = 2048,
+                 max_positions: int = 0):
+        if max_step_tokens <= 0 or max_batch <= 0:
+            raise ValueError("max_batch and max_step_tokens must be positive")
+        self.cache = cache
+        self.max_batch, self.max_step_tokens = max_batch, max_step_tokens
+        self.max_positions = max_positions
+        self.waiting: Deque[int] = deque()
+        self.running: List[int] = []
+        self.sequences: Dict[int, Sequence_] = {}
+        self.next_id = 0
+        self.preemptions = 0
+
+    # ------------------------------------------------------------------ requests
+    def add(self, prompt: Sequence[int], params: SamplingParams, max_tokens: int, eos_id: int,
+            seed: int) -> int:
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("Engine: empty prompt")
+        if max_tokens <= 0:
+            raise ValueError("Engine: max_tokens must be positive")
+        total = len(prompt) + max_tokens
+        share = self.cache.max_tokens_per_request()
+        if total - 1 > share:
+            raise ValueError(f"Engine: request needs up to {total - 1} cached tokens, the page "
+                             f"pool holds {share} for one request")
+        if self.max_positions and total - 1 > self.max_positions:
+            raise ValueError(f"Engine: request would reach position {total - 1}, the model's "
+                             f"limit is {self.max_positions}")
+        seq = Sequence_(self.next_id, prompt, params, max_tokens, eos_id, seed)
+        self.sequences[seq.id] = seq
+        self.waiting.append(seq.id)
+        self.next_id += 1
+        return seq.id
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ planning
+    def _admit(self) -> None:
+        cache = self.cache
+        while self.waiting and len(self.running) < self.max_batch and cache.can_open():
+            seq = self.sequences[self.waiting[0]]
+            first = min(len(seq.context()), self.max_step_tokens)
+            # pages the first portion needs, seen against what is free before this step
+            if any(cache.blocks_for(first) > free for free in cache.free_pages()):
+                break
+            self.waiting.popleft()
+            seq.handle = cache.open(seq.id)
+            seq.status = SeqStatus.Running
+            self.running.append(seq.id)
+
+    def plan(self) -> List[PlanItem]:
+        """Admit, then choose this step's items.  May preempt.  Returns [] when nothing can
+        run (then nothing is running, or a single request waits for nothing: cannot happen
+        for requests that passed `add`)."""
+        self._admit()
+        cache = self.cache
+        while True:
+            items: List[PlanItem] = []
+            tokens_left = self.max_step_tokens
+            pages_left = cache.free_pages()
+
+            def take(handle, n) -> bool:
+                need = cache.pages_needed(handle, n)
+                if any(k > left for k, left in zip(need, pages_left)):
+                    return False
+                for g, k in enumerate(need):
+                    pages_left[g] -= k
+                return True
+
+            for sid in self.running:                      # decodes first
+                seq = self.sequences[sid]
+                if seq.prefilled and tokens_left > 0 and take(seq.handle, 1):
+                    items.append(PlanItem(seq, [seq.output[-1]], True, False))
+                    tokens_left -= 1
+            for sid in self.running:                      # then prompt portions
+                seq = self.sequences[sid]
+                if seq.prefilled or tokens_left <= 0:
+                    continue
+                context = seq.context()
+                handle = seq.handle
+                if handle.length == 0 and not any(handle.tables):
+                    cap = ((len(context) - 1) // cache.page_size) * cache.page_size
+                    if cap > 0:
+                        cache.acquire_prefix(handle, context[:cap])
+                        pages_left = [min(a, b) for a, b in zip(pages_left, cache.free_pages())]
+                remaining = len(context) - handle.length
+                chunk = min(remaining, tokens_left)
+                # shrink the portion to the pages that are left
+                room = min((len(t) + left) * cache.page_size - handle.length
+                           for t, left in zip(handle.tables, pages_left)) if handle.tables \
+                    else chunk
+                chunk = min(chunk, room)
+                if chunk <= 0 or not take(handle, chunk):
+                    continue
+                portion = context[handle.length:handle.length + chunk]
+                items.append(PlanItem(seq, portion, chunk == remaining, True))
+                tokens_left -= chunk
+            if items or len(self.running) <= 1 or not self._preempt_youngest():
+                return items
+
+    def _preempt_youngest(self) -> bool:
+        for sid in reversed(self.running):
+            seq = self.sequences[sid]
+            if not any(page >= 0 for table in seq.handle.tables for page in table):
+                continue              # holds no pages; preempting it would free nothing
+            self.cache.close(seq.handle)
+            seq.handle = None
+            seq.prefilled = False
+            seq.status = SeqStatus.Waiting
+            seq.preempted += 1
+            self.running.remove(sid)
+            self.waiting.appendleft(sid)
+            self.preemptions += 1
+            return True
+        return False
+
+    # ------------------------------------------------------------------- results
+    def finish_step(self, items: Sequence[PlanItem], tokens: Sequence[Optional[int]]) -> None:
+        """Record the sampled token of every item that sampled (None for the others), retire
+        what is finished and register freshly prefilled pages for sharing."""
+        for item, token in zip(items, tokens):
+            seq = item.seq
+            if not item.samples:
+                continue
+            seq.prefilled = True
+            seq.output.append(int(token))
+            hit_eos = seq.eos_id >= 0 and token == seq.eos_id
+            if hit_eos or len(seq.output) >= seq.max_tokens:
+                seq.status = SeqStatus.Finished
+                self.cache.close(seq.handle)
+                seq.handle = None
+                self.running.remove(seq.id)
+            elif item.was_prefill:
+                self.cache.register_prefix(seq.handle, seq.context()[:seq.handle.length])

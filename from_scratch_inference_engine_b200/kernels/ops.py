@@ -1,0 +1,262 @@
+"""Typed Python entry points of the hand-written CUDA kernels.
+
+Each function checks what the kernel assumes (device, dtype, contiguity, sizes),
+passes raw pointers and the current CUDA stream to the C entry point, and raises on
+any non-zero return.  There is no other implementation behind these functions: on a
+machine without the compiled library or without a GPU they raise.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc import build
+
+DTYPE_F32, DTYPE_BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _tag(dtype: torch.dtype) -> int:
+    if dtype is torch.float32:
+        return DTYPE_F32
+    if dtype is torch.bfloat16:
+        return DTYPE_BF16
+    raise KernelError(f"kernels take float32 or bfloat16 storage, not {dtype}")
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(tensor: torch.Tensor, dtype, name: str, contiguous: bool = True) -> None:
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must live on the GPU (the engine has no CPU path)")
+    if dtype is not None and tensor.dtype is not dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    if contiguous and not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: argument refused by the kernel launcher")
+    if code == -2:
+        raise KernelError(f"{what}: size not supported by this kernel")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+_core = None
+
+
+def core():
+    """The core kernel library, compiled at first use."""
+    global _core
+    if _core is None:
+        lib = build.load_library("core")
+        i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_embed_gather.argtypes = [p, p, p, i, i, i, i, p, p]
+        lib.fsie_add_rmsnorm.argtypes = [p, p, p, i, p, p, i, i, f, i, i, p]
+        lib.fsie_rope_kv_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p]
+        lib.fsie_swiglu.argtypes = [p, p, ll, i, i, p]
+        lib.fsie_gemm_f32.argtypes = [p, p, p, p, i, i, i, i, i, p]
+        lib.fsie_attn_generic.argtypes = [p, i, p, p, ll, i, p, i, p, p, i, p, p, p, p, i, p, p,
+                                          i, i, i, i, i, i, f, i, p]
+        lib.fsie_attn_generic_rows.argtypes = []
+        lib.fsie_argmax.argtypes = [p, i, i, p, p]
+        lib.fsie_sample.argtypes = [p, i, i, p, p, p, p, p, p]
+        for name in ("fsie_embed_gather", "fsie_add_rmsnorm", "fsie_rope_kv_write", "fsie_swiglu",
+                     "fsie_gemm_f32", "fsie_attn_generic", "fsie_attn_generic_rows",
+                     "fsie_argmax", "fsie_sample"):
+            getattr(lib, name).restype = ctypes.c_int
+        _core = lib
+    return _core
+
+
+# ------------------------------------------------------------------------- embedding
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+                 error: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[ids[t]] widened to float32; an id outside the table sets error[0]."""
+    _need(ids, torch.int32, "ids")
+    _need(table, None, "table")
+    _need(out, torch.float32, "out")
+    _need(error, torch.int32, "error")
+    tokens, (vocab, hidden) = ids.numel(), table.shape
+    if out.shape[-1] != hidden or out.numel() < tokens * hidden:
+        raise KernelError("embed_gather: out is too small")
+    _check(core().fsie_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, hidden, vocab,
+                                    _tag(table.dtype), _ptr(error), _stream()), "embed_gather")
+    return out
+
+
+# ---------------------------------------------------------------------- add + RMSNorm
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                write_x: bool = True) -> torch.Tensor:
+    """x (float32 residual) += delta; out = rmsnorm(x) * gain in out's dtype.
+
+    With `rows` (int32 indices) only those rows are normed, into out[0..len(rows)), and
+    x is left untouched unless write_x.
+    """
+    _need(x, torch.float32, "x")
+    _need(out, None, "out")
+    hidden = x.shape[-1]
+    if delta is not None:
+        _need(delta, out.dtype, "delta")
+        if delta.shape[-1] != hidden:
+            raise KernelError("add_rmsnorm: delta width differs from x")
+    _need(gain, None, "gain")
+    if gain.numel() != hidden:
+        raise KernelError("add_rmsnorm: gain width differs from x")
+    if gain.dtype not in (torch.float32, out.dtype):
+        raise KernelError(f"add_rmsnorm: gain must be float32 or {out.dtype}")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        count = rows.numel()
+    else:
+        count = x.numel() // hidden
+    if out.numel() < count * hidden:
+        raise KernelError("add_rmsnorm: out is too small")
+    _check(core().fsie_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(gain),
+                                   int(gain.dtype is torch.float32), _ptr(out), _ptr(rows), count,
+                                   hidden, float(eps), int(write_x), _tag(out.dtype), _stream()),
+           "add_rmsnorm")
+    return out
+
+
+# ------------------------------------------------------- rotary + paged cache write
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+                  slot_of: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
+                  v_pages: Optional[torch.Tensor], page_stride: int, page_size: int,
+                  heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
+                  error: torch.Tensor) -> None:
+    """Rotate q in place in the fused projection rows; rotate k and store k, v in their pages.
+
+    k_pages / v_pages are views whose first element is page 0 of this cache entry;
+    page p of it starts page_stride elements further per page.
+    """
+    _need(qkv, None, "qkv")
+    _need(positions, torch.int32, "positions")
+    _need(cos_sin, torch.float32, "cos_sin")
+    tokens, ld = qkv.shape
+    if ld < (heads + 2 * kv_heads) * head_dim:
+        raise KernelError("rope_kv_write: projection rows are narrower than q, k and v")
+    if rotary_dim > 0 and cos_sin.shape[-1] != rotary_dim:
+        raise KernelError("rope_kv_write: cos/sin table width differs from rotary_dim")
+    write = k_pages is not None
+    if write:
+        _need(slot_of, torch.int32, "slot_of")
+        if k_pages.dtype is not qkv.dtype or v_pages.dtype is not qkv.dtype:
+            raise KernelError("rope_kv_write: cache dtype differs from the projection dtype")
+    _check(core().fsie_rope_kv_write(_ptr(qkv), ld, _ptr(positions), _ptr(cos_sin),
+                                     cos_sin.shape[0], _ptr(slot_of), _ptr(k_pages), _ptr(v_pages),
+                                     page_stride, page_size, tokens, heads, kv_heads, head_dim,
+                                     rotary_dim, int(write), _tag(qkv.dtype), _ptr(error),
+                                     _stream()), "rope_kv_write")
+
+
+# ----------------------------------------------------------------------------- SwiGLU
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i]."""
+    _need(gate_up, None, "gate_up")
+    _need(out, gate_up.dtype, "out")
+    tokens, two_inter = gate_up.shape
+    inter = two_inter // 2
+    if two_inter != 2 * inter or out.numel() < tokens * inter:
+        raise KernelError("swiglu: shapes do not fit")
+    _check(core().fsie_swiglu(_ptr(gate_up), _ptr(out), tokens, inter, _tag(out.dtype), _stream()),
+           "swiglu")
+    return out
+
+
+# --------------------------------------------------------------------- float32 product
+def gemm_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x @ weight.T (+ bias), all float32, plain FFMA (no tensor-core mode)."""
+    _need(x, torch.float32, "x", contiguous=False)
+    _need(weight, torch.float32, "weight")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("gemm_f32: x must be 2-D with unit inner stride")
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError("gemm_f32: inner sizes differ")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    _need(out, torch.float32, "out")
+    _check(core().fsie_gemm_f32(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), m, n, k,
+                                x.stride(0), n, _stream()), "gemm_f32")
+    return out
+
+
+# -------------------------------------------------------------------------- attention
+def attention_rows_per_tile() -> int:
+    return int(core().fsie_attn_generic_rows())
+
+
+def attention_generic(q: torch.Tensor, q_ld: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      page_stride: int, page_size: int, block_tables: torch.Tensor,
+                      tile_item: torch.Tensor, tile_row0: torch.Tensor, num_tiles: int,
+                      item_qstart: torch.Tensor, item_qlen: torch.Tensor, item_pos0: torch.Tensor,
+                      out: torch.Tensor, tokens: int, heads: int, kv_heads: int, head_dim: int,
+                      window: int, scale: float, nsplit: int = 1,
+                      part_o: Optional[torch.Tensor] = None,
+                      part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+    for name, t in (("block_tables", block_tables), ("tile_item", tile_item),
+                    ("tile_row0", tile_row0), ("item_qstart", item_qstart),
+                    ("item_qlen", item_qlen), ("item_pos0", item_pos0)):
+        _need(t, torch.int32, name)
+    _need(q, None, "q", contiguous=False)
+    _need(out, q.dtype, "out")
+    if k_pages.dtype is not q.dtype or v_pages.dtype is not q.dtype:
+        raise KernelError("attention: cache dtype differs from q")
+    if nsplit > 1:
+        _need(part_o, torch.float32, "part_o")
+        _need(part_ml, torch.float32, "part_ml")
+        if part_o.numel() < nsplit * tokens * heads * head_dim or \
+                part_ml.numel() < nsplit * tokens * heads * 2:
+            raise KernelError("attention: split scratch is too small")
+    _check(core().fsie_attn_generic(_ptr(q), q_ld, _ptr(k_pages), _ptr(v_pages), page_stride,
+                                    page_size, _ptr(block_tables), block_tables.stride(0),
+                                    _ptr(tile_item), _ptr(tile_row0), num_tiles,
+                                    _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0),
+                                    _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), tokens,
+                                    heads, kv_heads, head_dim, window, nsplit, float(scale),
+                                    _tag(q.dtype), _stream()), "attention_generic")
+    return out
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(logits, torch.float32, "logits")
+    _need(out, torch.int32, "out")
+    rows, vocab = logits.shape
+    _check(core().fsie_argmax(_ptr(logits), rows, vocab, _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(logits, torch.float32, "logits")
+    _need(temperature, torch.float32, "temperature")
+    _need(top_k, torch.int32, "top_k")
+    _need(top_p, torch.float32, "top_p")
+    _need(uniform, torch.float32, "uniform")
+    _need(out, torch.int32, "out")
+    rows, vocab = logits.shape
+    _check(core().fsie_sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(top_k),
+                              _ptr(top_p), _ptr(uniform), _ptr(out), _stream()), "sample")
+    return out

@@ -1,0 +1,103 @@
+"""Grouped-query attention over the paged cache."""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from ..cache.manager import CacheNeed
+from ..config.spec import PartSpec
+from ..kernels import ops
+from ..weights.tensor_spec import TensorSpec
+from .base import LayerCache, Mixer, build_part, register_part
+
+
+@register_part("mixer", "gqa_attention")
+class GqaAttention(Mixer):
+    """q, k, v projections (optional bias), position encoding on q and k, causal attention of
+    each query head over the kv head of its group (head h uses kv head h // group), output
+    projection without bias.  Scale 1/sqrt(head_dim); keys 0..position inclusive, or the last
+    `window` of them.  Reference: src/model/model.cpp:111-132, src/model/nn.cpp:151-226.
+
+    The three projections are one matrix product over the concatenated weight
+    [q_width + 2 kv_width, hidden], made at bind.
+    """
+
+    def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int,
+                 head_dim: int, qkv_bias: bool, position: PartSpec, window: int = 0):
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if head_dim > 256:
+            raise ValueError(f"head_dim {head_dim} is beyond the attention kernels (256)")
+        self.prefix = prefix
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.qkv_bias, self.window = head_dim, bool(qkv_bias), int(window)
+        self.q_width, self.kv_width = num_heads * head_dim, num_kv_heads * head_dim
+        self.position = build_part("position", position, prefix)
+        if self.position.rotary_dim > head_dim:
+            raise ValueError("rotary_dim exceeds head_dim")
+        self.scale = 1.0 / math.sqrt(head_dim)
+        self.w_qkv = self.b_qkv = self.w_o = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, h = self.prefix, self.hidden_size
+        specs = [TensorSpec(p + "q_proj.weight", (self.q_width, h)),
+                 TensorSpec(p + "k_proj.weight", (self.kv_width, h)),
+                 TensorSpec(p + "v_proj.weight", (self.kv_width, h)),
+                 TensorSpec(p + "o_proj.weight", (h, self.q_width))]
+        if self.qkv_bias:
+            specs += [TensorSpec(p + "q_proj.bias", (self.q_width,)),
+                      TensorSpec(p + "k_proj.bias", (self.kv_width,)),
+                      TensorSpec(p + "v_proj.bias", (self.kv_width,))]
+        return specs + self.position.tensor_specs()
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
+        self.runtime = runtime
+        p = self.prefix
+        self.w_qkv = torch.cat([tensors[p + f"{n}_proj.weight"] for n in "qkv"]).contiguous()
+        self.b_qkv = (torch.cat([tensors[p + f"{n}_proj.bias"] for n in "qkv"]).contiguous()
+                      if self.qkv_bias else None)
+        self.w_o = tensors[p + "o_proj.weight"].contiguous()
+        self.position.bind(tensors, runtime)
+
+    def forward(self, ctx, y: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+        rt = self.runtime
+        tokens = y.shape[0]
+        group = ctx.groups[cache.group]
+        qkv = rt.linear(y, self.w_qkv, self.b_qkv)
+        ops.rope_kv_write(qkv, ctx.positions, self.position.table,
+                          group.slot_of if cache.writes else None,
+                          cache.k_pages if cache.writes else None,
+                          cache.v_pages if cache.writes else None,
+                          cache.page_stride, group.page_size, self.num_heads, self.num_kv_heads,
+                          self.head_dim, self.position.rotary_dim, ctx.error)
+        out = torch.empty((tokens, self.q_width), dtype=qkv.dtype, device=qkv.device)
+        self._attend(ctx, qkv, group, cache, out)
+        return rt.linear(out, self.w_o, None)
+
+    def _attend(self, ctx, qkv: torch.Tensor, group, cache: LayerCache, out: torch.Tensor) -> None:
+        """Attention of the step's tokens over the pages: row tiles of (token, head) pairs, the
+        key range split over several blocks when the batch alone would not fill the GPU."""
+        tokens = qkv.shape[0]
+        group_size = self.num_heads // self.num_kv_heads
+        tiles = ctx.attention_tiles(group_size, ops.attention_rows_per_tile())
+        blocks = tiles.count * self.num_kv_heads
+        nsplit = 1
+        if blocks < ctx.runtime.sm_count:
+            by_fill = -(-2 * ctx.runtime.sm_count // blocks)
+            by_length = max(1, ctx.max_context // 128)
+            nsplit = max(1, min(by_fill, by_length, 32))
+        part_o = part_ml = None
+        if nsplit > 1:
+            part_o = ctx.scratch("attention.part_o", nsplit * tokens * self.q_width)
+            part_ml = ctx.scratch("attention.part_ml", nsplit * tokens * self.num_heads * 2)
+        ops.attention_generic(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, cache.page_stride,
+                              group.page_size, group.block_tables, tiles.item, tiles.row0,
+                              tiles.count, ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out,
+                              tokens, self.num_heads, self.num_kv_heads, self.head_dim,
+                              self.window, self.scale, nsplit, part_o, part_ml)

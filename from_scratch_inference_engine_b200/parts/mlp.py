@@ -1,0 +1,44 @@
+"""Dense SwiGLU feed-forward."""
+
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..kernels import ops
+from ..weights.tensor_spec import TensorSpec
+from .base import Part, register_part
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGluMlp(Part):
+    """down( silu(gate(y)) * up(y) ), no biases (reference: src/model/model.cpp:136-140,
+    src/model/nn.cpp:74-88).  gate and up are one product over the stacked weight
+    [2 * intermediate, hidden]: gate rows first, then up rows."""
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int):
+        self.prefix, self.hidden_size = prefix, int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, h, i = self.prefix, self.hidden_size, self.intermediate_size
+        return [TensorSpec(p + "gate_proj.weight", (i, h)),
+                TensorSpec(p + "up_proj.weight", (i, h)),
+                TensorSpec(p + "down_proj.weight", (h, i))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
+        self.runtime = runtime
+        p = self.prefix
+        self.w_gate_up = torch.cat([tensors[p + "gate_proj.weight"],
+                                    tensors[p + "up_proj.weight"]]).contiguous()
+        self.w_down = tensors[p + "down_proj.weight"].contiguous()
+
+    def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
+        rt = self.runtime
+        gate_up = rt.linear(y, self.w_gate_up, None)
+        act = torch.empty((y.shape[0], self.intermediate_size), dtype=gate_up.dtype,
+                          device=y.device)
+        ops.swiglu(gate_up, act)
+        return rt.linear(act, self.w_down, None)

@@ -1,0 +1,84 @@
+"""Greedy and temperature / top-k / top-p sampling on the device.
+
+Options as the reference's `SamplingParams` (include/engine/sampler.hpp:9-13):
+temperature (<= 0 selects the first largest logit), top_k (0 = off), top_p (>= 1 =
+off), applied in that order (src/sampler/sampler.cpp:25-88).  Unlike the reference,
+whose requests share one generator so that a request's tokens depend on what else is
+in the batch (src/engine/engine.cpp:131-135), every draw here is a function of
+(request seed, index of the output token): a request gives the same tokens alone, in
+any batch, and when it is recomputed after a preemption.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+
+_MASK = 0xFFFFFFFFFFFFFFFF
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0     # <= 0 selects greedy (argmax)
+    top_k: int = 0               # 0 disables top-k
+    top_p: float = 1.0           # >= 1 disables top-p (nucleus)
+    seed: Optional[int] = None   # None: derived from the engine seed and the request id
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0
+
+
+def _splitmix(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _MASK
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _MASK
+    return x ^ (x >> 31)
+
+
+def uniform_draw(seed: int, index: int) -> float:
+    """The uniform number in [0, 1) of output token `index` of a request with `seed`."""
+    bits = _splitmix(_splitmix(seed & _MASK) ^ ((index + 1) * 0xD6E8FEB86659FD93 & _MASK))
+    return float(np.float32((bits >> 40) / float(1 << 24)))   # 24 bits: exact in float32, < 1
+
+
+def request_seed(engine_seed: int, request_id: int) -> int:
+    return _splitmix((engine_seed & _MASK) ^ _splitmix(request_id + 0x51ED270B))
+
+
+class Sampler:
+    """Chooses one token per row of logits with the device kernels."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+               seeds: Sequence[int], indices: Sequence[int]) -> List[int]:
+        """logits float32 [rows, vocab]; row r is output token indices[r] of a request whose
+        seed is seeds[r].  Returns the chosen ids (one device-to-host copy of rows ints)."""
+        rows = logits.shape[0]
+        if rows != len(params):
+            raise ValueError("one SamplingParams per row of logits is needed")
+        picks = torch.empty((2, rows), dtype=torch.int32, device=self.device)
+        any_greedy = any(p.greedy for p in params)
+        any_random = any(not p.greedy for p in params)
+        if any_greedy:
+            ops.argmax(logits, picks[0])
+        if any_random:
+            host = np.empty((4, rows), dtype=np.float32)
+            for r, p in enumerate(params):
+                host[0, r] = p.temperature if not p.greedy else 0.0
+                host[1, r] = min(p.top_p, 1.0)
+                host[2, r] = uniform_draw(seeds[r], indices[r])
+                host[3, r] = 0.0
+            dev = torch.from_numpy(host).to(self.device)
+            top_k = torch.tensor([max(0, int(p.top_k)) for p in params], dtype=torch.int32,
+                                 device=self.device)
+            ops.sample(logits, dev[0], top_k, dev[1], dev[2], picks[1])
+        got = picks.cpu().numpy()
+        return [int(got[0, r] if params[r].greedy else got[1, r]) for r in range(rows)]
