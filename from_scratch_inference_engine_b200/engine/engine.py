@@ -41,7 +41,10 @@ class LoadedModel:
     def from_tensors(cls, config, tensors, dtype="bfloat16", device="cuda:0",
                      max_positions: int = 0) -> "LoadedModel":
         spec = config.build_spec()
-        limit = spec.max_position if spec.max_position > 0 else (max_positions or 32768)
+        # positions the engine can encode: what the configuration names (the reference parses
+        # max_position_embeddings and never enforces it, src/model/model_config.cpp:25) and
+        # at least what the caller's cache will hold
+        limit = max(spec.max_position, max_positions) or 32768
         runtime = Runtime(device, parse_dtype(dtype), max_positions=limit)
         model = DecoderModel(spec)
         model.bind(tensors, runtime)
@@ -50,6 +53,9 @@ class LoadedModel:
     def forward(self, ids: Sequence[int]) -> torch.Tensor:
         """Logits [len(ids), vocab] of one whole sequence (bindings/module.cpp:70-76)."""
         pages = -(-len(ids) // 16) + 1
+        if len(ids) > self.runtime.max_positions:
+            raise ValueError(f"forward: {len(ids)} tokens exceed the position table "
+                             f"({self.runtime.max_positions})")
         runner = ModelRunner(self.model, self.runtime, page_size=16, num_pages=pages,
                              max_requests=1)
         handle = runner.cache.open(0)

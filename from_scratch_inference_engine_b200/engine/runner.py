@@ -69,8 +69,7 @@ class ModelRunner:
         self._ring = PinnedRing()
         self._scratch: Dict[str, torch.Tensor] = {}
         self.vocab_size = model.spec.vocab_size
-        limit = model.spec.max_position
-        self.max_positions = limit if limit > 0 else self.cache.max_tokens_per_request()
+        self.max_positions = runtime.max_positions     # length of the position tables
 
     # ------------------------------------------------------------------- checks
     def _validate(self, entries: Sequence[StepEntry]) -> None:

@@ -35,8 +35,8 @@ class RotaryEncoding(Part):
 
     def bind(self, tensors, runtime) -> None:
         self.runtime = runtime
-        length = self.max_position if self.max_position > 0 else runtime.max_positions
-        length = max(length, 1)
+        # as long as the configuration says, and at least as long as the cache can hold
+        length = max(self.max_position, runtime.max_positions, 1)
         self.table = runtime.shared_table(
             ("rotary", self.theta, self.rotary_dim, length),
             lambda: torch.from_numpy(rotary_table(self.theta, self.rotary_dim, length)))

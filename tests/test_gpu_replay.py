@@ -1,0 +1,101 @@
+"""The engine against the plain implementation under every way of cutting the work."""
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+from helpers import TINY
+
+pytestmark = pytest.mark.gpu
+
+# float32: the engine's 32-bit sums against the plain 64-bit ones; bfloat16: activations
+# rounded to 8 bits of mantissa at every product, relative to the largest logit.
+TOLERANCE = {"float32": 1e-4, "bfloat16": 4e-2}
+
+REQUESTS = {
+    "A": {"a": 100, "b": 37, "c": 64, "d": 81, "e": 5, "f": 49},
+    "B": {"a": 130, "b": 33, "c": 100, "d": 64, "e": 7, "f": 1 + 32},
+    "C": {"a": 150, "b": 40, "c": 97, "d": 64, "e": 23},
+    "D": {"a": 70, "b": 35, "c": 48},
+}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {name: helpers.make_model_dir(root, name) for name in TINY}
+
+
+def requests_for(name):
+    vocab = TINY[name]["config"]["vocab_size"]
+    return {key: helpers.random_ids(vocab, n, seed=sum(map(ord, name + key)))
+            for key, n in REQUESTS[name].items()}
+
+
+def build_runner(folder, dtype, max_tokens, page_size):
+    from from_scratch_inference_engine_b200.engine import LoadedModel, ModelRunner
+    pages = -(-max_tokens // page_size)
+    model = LoadedModel.from_pretrained(folder, dtype=dtype, max_positions=pages * page_size)
+    return ModelRunner(model.model, model.runtime, page_size=page_size, num_pages=pages,
+                       max_requests=8)
+
+
+FAMILIES = {
+    "whole": lambda r, seed: helpers.trace_whole(r),
+    "tail": lambda r, seed: helpers.trace_tail_by_one(r),
+    "portions": lambda r, seed: helpers.trace_portions(r, seed),
+    "mixed": lambda r, seed: helpers.trace_mixed(r, seed),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("family", list(FAMILIES))
+@pytest.mark.parametrize("name,page_size", [("A", 4), ("B", 8), ("C", 16), ("D", 16)])
+def test_replay_matches_plain(folders, name, page_size, family, dtype):
+    requests = requests_for(name)
+    steps = FAMILIES[family](requests, 11)
+    # the pool holds exactly what the live requests need, so pages are used again
+    need = helpers.live_tokens_needed(steps, round_to=page_size)
+    runner = build_runner(folders[name], dtype, need, page_size)
+    rows = helpers.run_trace_in_process(runner, steps)
+    assert len(rows) == sum(len(v) for v in requests.values())
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], TOLERANCE[dtype])
+    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+    assert all(pool.num_free == pool.num_pages for pool in runner.cache.pools)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(folders, dtype):
+    """Positions 0, 1, 2 alone: one key, no history, the first page."""
+    requests = {"x": helpers.random_ids(256, 3, 5)}
+    for steps in (helpers.trace_whole(requests), helpers.trace_tail_by_one(requests, tail=2)):
+        runner = build_runner(folders["A"], dtype, 64, 4)
+        rows = helpers.run_trace_in_process(runner, steps)
+        _, _, bad = helpers.compare_rows(rows, requests, folders["A"], TOLERANCE[dtype])
+        assert not bad
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, dtype):
+    """A short prompt, then 200 tokens one by one across many pages."""
+    ids = helpers.random_ids(384, 230, 9)
+    requests = {"x": ids}
+    steps = helpers.trace_tail_by_one(requests, tail=200)
+    runner = build_runner(folders["B"], dtype, 256, 8)
+    rows = helpers.run_trace_in_process(runner, steps)
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders["B"], TOLERANCE[dtype])
+    assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
+
+
+def test_cutting_does_not_change_float32_beyond_rounding(folders):
+    """The same request whole and in portions: rows agree far inside the tolerance."""
+    requests = {"x": helpers.random_ids(384, 90, 3)}
+    results = []
+    for steps in (helpers.trace_whole(requests), helpers.trace_portions(requests, 4),
+                  helpers.trace_tail_by_one(requests)):
+        runner = build_runner(folders["B"], "float32", 128, 8)
+        results.append(helpers.run_trace_in_process(runner, steps))
+    for other in results[1:]:
+        for key, row in results[0].items():
+            assert np.abs(row - other[key]).max() < 2e-5
