@@ -1,0 +1,206 @@
+"""The scheduler's decisions, without a GPU: a stand-in executor reserves and commits
+what each plan holds and answers with made-up tokens (reference behaviour:
+tests/cpp/test_engine.cpp:50-162)."""
+
+import pytest
+
+from from_scratch_inference_engine_b200.cache import CacheManager, CacheNeed
+from from_scratch_inference_engine_b200.engine.scheduler import Scheduler, SeqStatus
+from from_scratch_inference_engine_b200.sampling import SamplingParams
+
+NEED = CacheNeed(kv_heads=1, head_dim=16)
+GREEDY = SamplingParams(temperature=0.0)
+
+
+def make(num_pages, page_size=4, max_batch=8, max_step_tokens=16, prefix=False, needs=None):
+    cache = CacheManager(needs or [NEED], page_size, num_pages, max_batch, prefix)
+    return Scheduler(cache, max_batch, max_step_tokens), cache
+
+
+def next_token(seq):
+    """Stand-in model: the next token depends on the whole context only."""
+    context = seq.context()
+    return (sum(context) * 31 + len(context)) % 97
+
+
+def run_step(s, cache, log=None):
+    items = s.plan()
+    tokens = []
+    for item in items:
+        cache.reserve(item.seq.handle, len(item.tokens))
+        # the portion must continue exactly where the cache stands
+        context = item.seq.context()
+        at = item.seq.handle.length
+        assert context[at:at + len(item.tokens)] == item.tokens
+        cache.commit(item.seq.handle, len(item.tokens))
+        tokens.append(next_token(item.seq) if item.samples else None)
+    if log is not None:
+        log.append([(i.seq.id, len(i.tokens), i.was_prefill) for i in items])
+    s.finish_step(items, tokens)
+    cache.check()
+    return items
+
+
+def run_all(s, cache, log=None, limit=10_000):
+    for _ in range(limit):
+        if not s.has_work():
+            return
+        assert run_step(s, cache, log), "no progress"
+    raise AssertionError("did not finish")
+
+
+def alone(prompt, max_tokens, eos_id=-1):
+    s, cache = make(num_pages=64)
+    rid = s.add(prompt, GREEDY, max_tokens, eos_id, seed=0)
+    run_all(s, cache)
+    return s.sequences[rid].output
+
+
+def test_single_request_prefills_in_portions_then_decodes():
+    s, cache = make(num_pages=64, max_step_tokens=16)
+    rid = s.add(list(range(40)), GREEDY, 5, -1, 0)
+    log = []
+    run_all(s, cache, log)
+    assert [step[0][1] for step in log] == [16, 16, 8, 1, 1, 1, 1]
+    assert [step[0][2] for step in log] == [True, True, True, False, False, False, False]
+    assert len(s.sequences[rid].output) == 5 and s.sequences[rid].status is SeqStatus.Finished
+    assert cache.free_pages() == [64] and cache.slots.num_free == 8
+
+
+def test_decodes_go_first_and_portions_fill_the_rest_of_the_budget():
+    s, cache = make(num_pages=64, max_step_tokens=16)
+    a = s.add(list(range(6)), GREEDY, 20, -1, 0)
+    run_step(s, cache)                                    # a is prefilled
+    b = s.add(list(range(50)), GREEDY, 3, -1, 0)
+    log = []
+    run_step(s, cache, log)
+    assert log[0] == [(a, 1, False), (b, 15, True)]       # one decode token + 15 of the budget
+    run_step(s, cache, log)
+    assert log[1] == [(a, 1, False), (b, 15, True)]
+    run_all(s, cache, log)
+    assert s.sequences[b].output == alone(list(range(50)), 3)
+    assert s.sequences[a].output == alone(list(range(6)), 20)
+
+
+def test_two_concurrent_equal_each_alone():
+    s, cache = make(num_pages=64)
+    a = s.add([3, 1, 4, 1, 5], GREEDY, 9, -1, 0)
+    b = s.add([2, 7, 1, 8, 2, 8, 1], GREEDY, 6, -1, 0)
+    run_all(s, cache)
+    assert s.sequences[a].output == alone([3, 1, 4, 1, 5], 9)
+    assert s.sequences[b].output == alone([2, 7, 1, 8, 2, 8, 1], 6)
+
+
+def test_admission_is_fcfs_and_capped_by_max_batch():
+    s, cache = make(num_pages=64, max_batch=2)
+    ids = [s.add([1, 2, 3], GREEDY, 4, -1, 0) for _ in range(4)]
+    run_step(s, cache)
+    assert s.running == ids[:2] and list(s.waiting) == ids[2:]
+    run_all(s, cache)
+    assert all(s.sequences[i].status is SeqStatus.Finished for i in ids)
+
+
+def test_head_of_the_queue_blocks_those_behind_it():
+    s, cache = make(num_pages=6, page_size=4, max_step_tokens=64)
+    a = s.add(list(range(12)), GREEDY, 4, -1, 0)          # 3 pages now, 4 at the end
+    run_step(s, cache)
+    big = s.add(list(range(16)), GREEDY, 2, -1, 0)        # needs 4 pages at once: 3 are free
+    small = s.add([1], GREEDY, 2, -1, 0)                  # would fit, but is behind `big`
+    run_step(s, cache)
+    assert s.running == [a] and list(s.waiting) == [big, small]
+    run_all(s, cache)
+    assert s.sequences[small].status is SeqStatus.Finished
+
+
+def test_tight_pool_serialises():
+    # one request's worth of pages: the second waits until the first is done
+    s, cache = make(num_pages=2, page_size=4)
+    a = s.add([1, 2, 3, 4, 5], GREEDY, 3, -1, 0)
+    b = s.add([9, 8, 7, 6, 5], GREEDY, 3, -1, 0)
+    log = []
+    run_all(s, cache, log)
+    assert all(len(step) == 1 for step in log)
+    first_b = next(i for i, step in enumerate(log) if step[0][0] == b)
+    assert all(step[0][0] == a for step in log[:first_b])
+    assert s.sequences[a].output == alone([1, 2, 3, 4, 5], 3)
+    assert s.sequences[b].output == alone([9, 8, 7, 6, 5], 3)
+
+
+def test_pages_run_out_preempts_the_youngest_which_recomputes():
+    # both fit at first; growing, they exhaust the pool; the younger one is preempted
+    s, cache = make(num_pages=4, page_size=4, max_step_tokens=32)
+    a = s.add([5, 6, 7], GREEDY, 12, -1, 0)               # ends at 14 tokens: 4 pages
+    b = s.add([8, 9, 10], GREEDY, 12, -1, 0)
+    log = []
+    run_all(s, cache, log)
+    assert s.preemptions > 0 and s.sequences[b].preempted > 0 and s.sequences[a].preempted == 0
+    assert s.sequences[a].output == alone([5, 6, 7], 12)
+    assert s.sequences[b].output == alone([8, 9, 10], 12)
+    # after the preemption b's recompute covers prompt + output so far, as a prefill
+    recomputes = [n for step in log for (rid, n, prefill) in step if rid == b and prefill]
+    assert len(recomputes) >= 2 and max(recomputes[1:]) > 3
+    assert cache.free_pages() == [4]
+
+
+def test_preempted_request_returns_to_the_front_of_the_queue():
+    s, cache = make(num_pages=4, page_size=4, max_step_tokens=32)
+    a = s.add([5, 6, 7], GREEDY, 12, -1, 0)
+    b = s.add([8, 9, 10], GREEDY, 12, -1, 0)
+    c = s.add([1], GREEDY, 2, -1, 0)
+    while s.preemptions == 0:
+        run_step(s, cache)
+    assert s.waiting[0] == b and s.sequences[b].status is SeqStatus.Waiting
+    assert s.sequences[b].handle is None
+    run_all(s, cache)
+    assert s.sequences[c].output == alone([1], 2)
+
+
+def test_eos_stops_and_is_kept():
+    prompt = [4, 4, 4]
+    free_run = alone(prompt, 10)
+    eos = free_run[3]
+    out = alone(prompt, 10, eos_id=eos)
+    stop = free_run.index(eos)
+    assert out == free_run[:stop + 1] and out[-1] == eos
+
+
+def test_requests_that_can_never_fit_are_refused():
+    s, _ = make(num_pages=4, page_size=4)
+    with pytest.raises(ValueError, match="page pool holds 16"):
+        s.add(list(range(10)), GREEDY, 8, -1, 0)          # 17 cached tokens at the end
+    s.add(list(range(10)), GREEDY, 7, -1, 0)              # 16: fits exactly
+    with pytest.raises(ValueError, match="empty prompt"):
+        s.add([], GREEDY, 4, -1, 0)
+    with pytest.raises(ValueError, match="max_tokens"):
+        s.add([1], GREEDY, 0, -1, 0)
+
+
+def test_prefix_cache_on_equals_off_with_hits():
+    prompt = list(range(30, 43))                          # 13 tokens: three full pages
+    outs = {}
+    for prefix in (False, True):
+        s, cache = make(num_pages=32, prefix=prefix)
+        first = s.add(prompt, GREEDY, 4, -1, 0)
+        run_all(s, cache)
+        log = []
+        second = s.add(prompt + [7, 7], GREEDY, 4, -1, 0)
+        run_all(s, cache, log)
+        outs[prefix] = (s.sequences[first].output, s.sequences[second].output)
+        if prefix:
+            assert cache.prefix_hits == 1
+            assert log[0] == [(second, 3, True)]          # 12 of 15 tokens came from the cache
+        else:
+            assert log[0] == [(second, 15, True)]
+    assert outs[False] == outs[True]
+
+
+def test_windowed_group_bounds_what_a_request_holds():
+    needs = [NEED, CacheNeed(1, 16, window=8)]
+    s, cache = make(num_pages=[40, 6], page_size=4, needs=needs, max_step_tokens=8)
+    rid = s.add(list(range(60)), GREEDY, 30, -1, 0)
+    peak = 0
+    while s.has_work():
+        run_step(s, cache)
+        if s.sequences[rid].handle is not None:
+            peak = max(peak, sum(p >= 0 for p in s.sequences[rid].handle.tables[1]))
+    assert len(s.sequences[rid].output) == 30 and peak <= 5
