@@ -93,7 +93,8 @@ __device__ Located locate(const RowView& r, float target, float* scratch, unsign
             float mass = 0.f;
             for (int i = threadIdx.x; i < r.vocab; i += blockDim.x)
                 if (order_key(r.row[i]) >= cand) mass += weight_of(r, i);
-            reached = block_sum(mass, scratch) >= target;
+            const float total = block_sum(mass, scratch);
+            reached = total >= target && total > 0.f;   // target 0 stops at the first token
         }
         if (reached) prefix = cand;
     }

@@ -206,3 +206,28 @@ def compare_rows(rows, requests, model_dir, rel: float):
         if diff > rel * max(1.0, float(np.abs(want).max())):
             mismatched.append((key, pos, diff))
     return worst, scale, mismatched
+
+
+# ----------------------------------------------------------------- one part on the GPU
+class OnePartModel:
+    """Stands where a DecoderModel stands in a ModelRunner, but runs a single callable on
+    the step's inputs: lets a test step one mixer (or block) through the real cache
+    manager, step context and pages without a model around it."""
+
+    def __init__(self, mixer, run, vocab=1 << 20):
+        from types import SimpleNamespace
+        self.mixer, self.run = mixer, run
+        self.schedule = [(0, 0, True)]
+        self.spec = SimpleNamespace(vocab_size=vocab, max_position=0)
+        self.inputs = None
+        self.outputs = None
+
+    def cache_needs(self):
+        return [self.mixer.cache_need()]
+
+    def state_needs(self):
+        return [self.mixer.state_need()]
+
+    def forward(self, ctx, caches, rows):
+        self.outputs = self.run(ctx, self.inputs, caches[0])
+        return None

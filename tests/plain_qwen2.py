@@ -24,8 +24,11 @@ import torch
 
 # ----------------------------------------------------------------------------- loading
 def read_config(model_dir):
+    return read_config_dict(json.loads((Path(model_dir) / "config.json").read_text()))
+
+
+def read_config_dict(j):
     """Keys and defaults of src/model/model_config.cpp:9-33."""
-    j = json.loads((Path(model_dir) / "config.json").read_text())
     heads = j["num_attention_heads"]
     c = {
         "hidden": j["hidden_size"], "layers": j["num_hidden_layers"], "heads": heads,
@@ -127,27 +130,46 @@ def silu_mul(gate, up):
 
 
 # ------------------------------------------------------------------------------- model
-def forward(config, weights, ids):
-    """Logits [len(ids), vocab] of one whole sequence, src/model/model.cpp:90-149."""
+def decoder_layer(config, weights, l, x, positions, shared_kv=None):
+    """One pre-norm layer on a whole sequence, src/model/model.cpp:107-141.  Returns the new
+    residual stream and this layer's (k, v).  With `shared_kv` the layer attends over those
+    keys and values instead of its own (a run order in which a layer reads another layer's
+    cache; not in the reference)."""
+    c, w = config, weights
+    p = f"model.layers.{l}."
+    normed = rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
+
+    def project(name):
+        bias = w[p + f"self_attn.{name}_proj.bias"] if c["bias"] else None
+        return linear(normed, w[p + f"self_attn.{name}_proj.weight"], bias)
+    q = rope(project("q"), c["heads"], c["head_dim"], c["theta"], positions)
+    if shared_kv is None:
+        k = rope(project("k"), c["kv_heads"], c["head_dim"], c["theta"], positions)
+        v = project("v")
+    else:
+        k, v = shared_kv
+    attn = attention(q, k, v, c["heads"], c["kv_heads"], c["head_dim"], 0, c["windows"][l])
+    x = x + linear(attn, w[p + "self_attn.o_proj.weight"])
+    normed2 = rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
+    act = silu_mul(linear(normed2, w[p + "mlp.gate_proj.weight"]),
+                   linear(normed2, w[p + "mlp.up_proj.weight"]))
+    return x + linear(act, w[p + "mlp.down_proj.weight"]), (k, v)
+
+
+def forward(config, weights, ids, schedule=None):
+    """Logits [len(ids), vocab] of one whole sequence, src/model/model.cpp:90-149.
+    `schedule` (not in the reference) is a run order [(layer, cache entry, writes)]; the
+    default runs every layer once on its own keys."""
     c, w = config, weights
     positions = list(range(len(ids)))
     x = embedding(w["model.embed_tokens.weight"], ids)
-    for l in range(c["layers"]):
-        p = f"model.layers.{l}."
-        normed = rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
-
-        def project(name):
-            bias = w[p + f"self_attn.{name}_proj.bias"] if c["bias"] else None
-            return linear(normed, w[p + f"self_attn.{name}_proj.weight"], bias)
-        q, k, v = project("q"), project("k"), project("v")
-        q = rope(q, c["heads"], c["head_dim"], c["theta"], positions)
-        k = rope(k, c["kv_heads"], c["head_dim"], c["theta"], positions)
-        attn = attention(q, k, v, c["heads"], c["kv_heads"], c["head_dim"], 0, c["windows"][l])
-        x = x + linear(attn, w[p + "self_attn.o_proj.weight"])
-        normed2 = rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
-        act = silu_mul(linear(normed2, w[p + "mlp.gate_proj.weight"]),
-                       linear(normed2, w[p + "mlp.up_proj.weight"]))
-        x = x + linear(act, w[p + "mlp.down_proj.weight"])
+    if schedule is None:
+        schedule = [(l, l, True) for l in range(c["layers"])]
+    stored = {}
+    for l, entry, writes in schedule:
+        x, kv = decoder_layer(c, w, l, x, positions, None if writes else stored[entry])
+        if writes:
+            stored[entry] = kv
     normed = rms_norm(x, w["model.norm.weight"], c["eps"])
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return linear(normed, head)

@@ -1,0 +1,168 @@
+"""Generation through the Python entry point and the engine's scheduling on the GPU
+(reference behaviour: tests/cpp/test_engine.cpp:38-162, tests/cpp/test_cuda_engine.cpp:45-79)."""
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_qwen2 as plain
+from helpers import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {name: helpers.make_model_dir(root, name) for name in ("A", "B", "C")}
+
+
+def assert_greedy_agrees(folder, prompt, got, gap_allowed):
+    """Token for token, or up to a first difference that is a near tie of the plain logits."""
+    config, weights = plain.load(folder)
+    ids = list(prompt)
+    for index, token in enumerate(got):
+        row = plain.forward(config, weights, ids)[-1]
+        want = plain.sample(row, 0.0, 0, 1.0, 0.0)
+        if token != want:
+            gap = float(row[want] - row[token])
+            assert gap <= gap_allowed * max(1.0, float(row.abs().max())), \
+                f"token {index}: engine chose {token}, plain {want}, gap {gap:.3e}"
+            return index
+        ids.append(token)
+    return len(got)
+
+
+@pytest.mark.parametrize("name,block_size", [("A", 4), ("B", 8)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_llm(folders, name, block_size, dtype):
+    from from_scratch_inference_engine_b200 import LLM, GenerationConfig
+    llm = LLM(folders[name], block_size=block_size, num_blocks=64, dtype=dtype, max_batch=4,
+              eos_id=-1)
+    vocab = TINY[name]["config"]["vocab_size"]
+    for n, seed in ((5, 1), (17, 2), (1, 3)):
+        prompt = helpers.random_ids(vocab, n, seed)
+        out = llm.generate_ids(prompt, GenerationConfig(max_tokens=8))
+        assert len(out) == 8
+        agreed = assert_greedy_agrees(folders[name], prompt, out,
+                                      1e-5 if dtype == "float32" else 2e-2)
+        if dtype == "float32":
+            assert agreed == 8
+    assert llm.engine.runner.cache.free_pages()[0] + 0 >= 0
+    llm.engine.runner.cache.check()
+
+
+def test_model_forward_entry_point(folders):
+    from from_scratch_inference_engine_b200 import LoadedModel
+    model = LoadedModel.from_pretrained(folders["B"], dtype="float32")
+    ids = helpers.random_ids(384, 21, 4)
+    got = model.forward(ids).cpu().numpy()
+    want = helpers.plain_logits(folders["B"], ids)
+    assert got.shape == want.shape and np.abs(got - want).max() < 1e-4
+    with pytest.raises(IndexError):
+        model.forward([1, 2, 384])
+
+
+def engine_for(folder, dtype="float32", **kwargs):
+    from from_scratch_inference_engine_b200 import Engine, LoadedModel
+    options = dict(block_size=4, num_blocks=64, seed=0, max_batch=8, max_step_tokens=16)
+    options.update(kwargs)
+    blocks = options["num_blocks"]
+    blocks = max(blocks) if isinstance(blocks, list) else blocks
+    model = LoadedModel.from_pretrained(folder, dtype=dtype,
+                                        max_positions=options["block_size"] * blocks)
+    return Engine(model, **options)
+
+
+def test_two_concurrent_requests_equal_each_alone(folders):
+    from from_scratch_inference_engine_b200 import SamplingParams
+    greedy = SamplingParams(temperature=0.0)
+    p1, p2 = helpers.random_ids(256, 11, 1), helpers.random_ids(256, 23, 2)
+    alone = [engine_for(folders["A"]).generate(p, greedy, 10) for p in (p1, p2)]
+    engine = engine_for(folders["A"])
+    a = engine.add_request(p1, greedy, 10)
+    b = engine.add_request(p2, greedy, 10)
+    engine.run_until_done()
+    assert engine.output(a) == alone[0] and engine.output(b) == alone[1]
+    assert engine.stats()["tokens_prefilled"] == 34
+
+
+def test_pages_run_out_preemption_recomputes_to_the_same_tokens(folders):
+    from from_scratch_inference_engine_b200 import SamplingParams
+    greedy = SamplingParams(temperature=0.0)
+    prompts = [helpers.random_ids(256, 3, s) for s in (5, 6)]
+    alone = [engine_for(folders["A"]).generate(p, greedy, 12) for p in prompts]
+    engine = engine_for(folders["A"], num_blocks=4)          # 16 tokens of cache in all
+    ids = [engine.add_request(p, greedy, 12) for p in prompts]
+    engine.run_until_done()
+    assert engine.preemptions() > 0
+    assert [engine.output(i) for i in ids] == alone
+    assert engine.runner.cache.free_pages() == [4]
+
+
+def test_temperature_sampling_does_not_depend_on_batching_or_preemption(folders):
+    from from_scratch_inference_engine_b200 import SamplingParams
+    params = [SamplingParams(temperature=0.8, seed=11),
+              SamplingParams(temperature=1.3, top_k=20, top_p=0.9, seed=12),
+              SamplingParams(temperature=0.0)]
+    prompts = [helpers.random_ids(384, n, s) for n, s in ((7, 1), (30, 2), (12, 3))]
+    alone = [engine_for(folders["B"], block_size=8).generate(p, q, 12)
+             for p, q in zip(prompts, params)]
+    assert len({tuple(o) for o in alone}) == 3
+    together = engine_for(folders["B"], block_size=8)
+    ids = [together.add_request(p, q, 12) for p, q in zip(prompts, params)]
+    together.run_until_done()
+    assert [together.output(i) for i in ids] == alone
+    tight = engine_for(folders["B"], block_size=8, num_blocks=8)      # 64 tokens: forces preemption
+    ids = [tight.add_request(p, q, 12) for p, q in zip(prompts, params)]
+    tight.run_until_done()
+    assert tight.preemptions() > 0 and [tight.output(i) for i in ids] == alone
+    # another seed gives another continuation
+    other = engine_for(folders["B"], block_size=8).generate(
+        prompts[0], SamplingParams(temperature=0.8, seed=99), 12)
+    assert other != alone[0]
+
+
+def test_eos_stops_and_is_kept(folders):
+    from from_scratch_inference_engine_b200 import SamplingParams
+    greedy = SamplingParams(temperature=0.0)
+    prompt = helpers.random_ids(256, 9, 8)
+    free_run = engine_for(folders["A"]).generate(prompt, greedy, 10)
+    eos = free_run[4]
+    out = engine_for(folders["A"]).generate(prompt, greedy, 10, eos_id=eos)
+    assert out == free_run[:free_run.index(eos) + 1]
+
+
+def test_prefix_cache_on_equals_off_with_hits(folders):
+    from from_scratch_inference_engine_b200 import SamplingParams
+    greedy = SamplingParams(temperature=0.0)
+    shared = helpers.random_ids(256, 26, 9)
+    tails = [helpers.random_ids(256, 5, s) for s in (1, 2, 3)]
+    outs = {}
+    for on in (False, True):
+        engine = engine_for(folders["A"], enable_prefix_cache=on)
+        outs[on] = [engine.generate(shared + tail, greedy, 6) for tail in tails]
+        assert (engine.prefix_hits() > 0) == on
+        engine.runner.cache.check()
+    assert outs[True] == outs[False]
+
+
+def test_windowed_model_generates_within_a_small_window_pool(folders):
+    """Config C: one full layer and two layers with a window of 21 keys.  The windowed
+    group gets 6 pages of 8; a 100-token context passes through them."""
+    from from_scratch_inference_engine_b200 import SamplingParams
+    greedy = SamplingParams(temperature=0.0)
+    prompt = helpers.random_ids(331, 70, 4)
+    engine = engine_for(folders["C"], block_size=8, num_blocks=[16, 6])
+    out = engine.generate(prompt, greedy, 30)
+    assert assert_greedy_agrees(folders["C"], prompt, out, 1e-5) == 30
+    assert engine.runner.cache.free_pages() == [16, 6]
+
+
+def test_requests_beyond_the_pool_are_refused(folders):
+    engine = engine_for(folders["A"], num_blocks=4)
+    with pytest.raises(ValueError, match="page pool"):
+        engine.add_request(list(range(10)), None, 8)
+    with pytest.raises(IndexError):
+        engine.add_request([1, 256], None, 2)

@@ -1,0 +1,345 @@
+"""Each CUDA kernel alone against a plain PyTorch reference, at sizes other than the
+engine's test models (the reference does the same for its kernels,
+tests/cpp/test_cuda_kernels.cpp:26-235)."""
+
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 2e-5 if dtype is torch.float32 else 1.6e-2       # bf16: 2^-8 relative + slack
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from from_scratch_inference_engine_b200.kernels import ops
+    ops.core()
+    return ops
+
+
+def dev(t, dtype=None):
+    t = t.to("cuda")
+    return t if dtype is None else t.to(dtype)
+
+
+# --------------------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather(ops, dtype):
+    torch.manual_seed(0)
+    table = dev(torch.randn(1000, 300), dtype)
+    ids = dev(torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32))
+    out = torch.empty(5, 300, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed_gather(ids, table, out, error)
+    assert torch.equal(out, table[ids.long()].float()) and error.item() == 0
+    ops.embed_gather(dev(torch.tensor([3, 1000], dtype=torch.int32)), table, out, error)
+    assert error.item() == 1 and out[1].abs().max().item() == 0.0     # refused, not read
+
+
+# ----------------------------------------------------------------------- add + RMSNorm
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [64, 777, 3584, 9000])
+def test_add_rmsnorm(ops, dtype, hidden):
+    torch.manual_seed(1)
+    rows, eps = 7, 1e-5
+    x0 = torch.randn(rows, hidden) * 3
+    delta = (torch.randn(rows, hidden) * 0.5).to(dtype)
+    gain = (1 + 0.1 * torch.randn(hidden))
+    for gain_dtype in {torch.float32, dtype}:
+        x = dev(x0.clone())
+        y = torch.empty(rows, hidden, dtype=dtype, device="cuda")
+        g = gain.to(gain_dtype)
+        ops.add_rmsnorm(x, dev(delta), dev(g), eps, y)
+        summed = x0.double() + delta.double()
+        want = plain.rms_norm(summed, g.double(), eps)
+        assert torch.allclose(x.cpu().double(), summed, atol=1e-6)          # residual in 32-bit
+        err = (y.cpu().double() - want).abs().max().item()
+        assert err < tol(dtype) * want.abs().max().item()
+    # no delta; rows gathered; x untouched
+    x = dev(x0.clone())
+    pick = dev(torch.tensor([6, 0, 3], dtype=torch.int32))
+    y = torch.empty(3, hidden, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(x, dev(delta), dev(gain), eps, y, rows=pick, write_x=False)
+    want = plain.rms_norm(x0.double() + delta.double(), gain.double(), eps)[[6, 0, 3]]
+    assert torch.equal(x.cpu(), x0)
+    assert (y.cpu().double() - want).abs().max().item() < tol(dtype) * want.abs().max().item()
+
+
+# ----------------------------------------------------- rotary encoding + cache write
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,hd,rotary,theta", [(5, 5, 16, 16, 1e4), (6, 2, 48, 32, 5e5),
+                                                            (7, 1, 128, 128, 1e6)])
+def test_rope_kv_write(ops, dtype, heads, kv_heads, hd, rotary, theta):
+    from from_scratch_inference_engine_b200.parts.rope import rotary_table
+    torch.manual_seed(2)
+    tokens, page_size, num_pages, entries = 9, 4, 11, 2
+    positions = [0, 1, 2, 3, 17, 4095, 30000, 31, 32]
+    width = (heads + 2 * kv_heads) * hd
+    qkv0 = torch.randn(tokens, width).to(dtype)
+    qkv = dev(qkv0.clone())
+    table = dev(torch.from_numpy(rotary_table(theta, rotary, 30001)))
+    pages = torch.zeros(num_pages, entries, 2, kv_heads, page_size, hd, dtype=dtype, device="cuda")
+    slots = [5 * page_size + 0, 5 * page_size + 1, 2 * page_size + 3, 0, 10 * page_size + 2,
+             -1, 7 * page_size + 1, 3 * page_size + 0, 3 * page_size + 1]
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.rope_kv_write(qkv, dev(torch.tensor(positions, dtype=torch.int32)), table,
+                      dev(torch.tensor(slots, dtype=torch.int32)), pages[:, 1, 0], pages[:, 1, 1],
+                      pages.stride(0), page_size, heads, kv_heads, hd, rotary, error)
+    assert error.item() == 0
+
+    def rotate(x, n):      # plain rope over the first `rotary` dims of each head
+        xh = x.double().reshape(tokens, n, hd)
+        rot = plain.rope(xh[..., :rotary].reshape(tokens, n * rotary), n, rotary, theta, positions)
+        return torch.cat([rot.reshape(tokens, n, rotary), xh[..., rotary:]], -1)
+    q_want = rotate(qkv0[:, :heads * hd], heads)
+    k_want = rotate(qkv0[:, heads * hd:(heads + kv_heads) * hd], kv_heads)
+    v_want = qkv0[:, (heads + kv_heads) * hd:].double().reshape(tokens, kv_heads, hd)
+    got_q = qkv[:, :heads * hd].cpu().double().reshape(tokens, heads, hd)
+    assert (got_q - q_want).abs().max().item() < tol(dtype) * q_want.abs().max().item()
+    cache = pages.cpu().double()
+    assert cache[:, 0].abs().max().item() == 0.0                      # the other entry is untouched
+    written = 0
+    for t, slot in enumerate(slots):
+        if slot < 0:
+            continue
+        page, off = divmod(slot, page_size)
+        assert (cache[page, 1, 0, :, off] - k_want[t]).abs().max().item() \
+            < tol(dtype) * k_want.abs().max().item()
+        assert torch.equal(cache[page, 1, 1, :, off], v_want[t])
+        written += 1
+    assert (cache[:, 1, 0].abs().sum((1, 3)) > 0).sum().item() == written   # nothing else written
+    # a position beyond the table is refused
+    ops.rope_kv_write(qkv, dev(torch.tensor([40000] * tokens, dtype=torch.int32)), table, None,
+                      None, None, 0, page_size, heads, kv_heads, hd, rotary, error)
+    assert error.item() == 2
+
+
+# ------------------------------------------------------------------------------ SwiGLU
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(ops, dtype):
+    torch.manual_seed(3)
+    gu = (torch.randn(13, 2 * 333) * 3).to(dtype)
+    out = torch.empty(13, 333, dtype=dtype, device="cuda")
+    ops.swiglu(dev(gu), out)
+    want = plain.silu_mul(gu[:, :333].double(), gu[:, 333:].double())
+    assert (out.cpu().double() - want).abs().max().item() < tol(dtype) * want.abs().max().item()
+
+
+# ---------------------------------------------------------------------- float32 product
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (37, 101, 203), (64, 64, 16), (130, 70, 1000)])
+def test_gemm_f32(ops, m, n, k):
+    torch.manual_seed(4)
+    x, w, b = torch.randn(m, k), torch.randn(n, k), torch.randn(n)
+    want = x.double() @ w.double().T + b.double()
+    got = ops.gemm_f32(dev(x), dev(w), dev(b))
+    assert (got.cpu().double() - want).abs().max().item() < 1e-5 * math.sqrt(k) * 4
+    got = ops.gemm_f32(dev(x), dev(w), None)
+    assert (got.cpu().double() - (want - b.double())).abs().max().item() < 1e-5 * math.sqrt(k) * 4
+    # a row's result does not depend on the other rows of the launch
+    alone = ops.gemm_f32(dev(x[m // 2:m // 2 + 1]), dev(w), dev(b))
+    both = ops.gemm_f32(dev(x), dev(w), dev(b))
+    assert torch.equal(alone[0], both[m // 2])
+
+
+# --------------------------------------------------------------------------- attention
+class PagedCase:
+    """Requests with history and new tokens over shuffled pages, and the plain answer."""
+
+    def __init__(self, dtype, heads, kv_heads, hd, page_size, items, window=0, seed=0,
+                 peak=None):
+        g = torch.Generator().manual_seed(seed)
+        self.heads, self.kv_heads, self.hd, self.page_size, self.window = \
+            heads, kv_heads, hd, page_size, window
+        self.items = items                                   # [(past, new)]
+        total_pages = sum(-(-(p + n) // page_size) for p, n in items) + 3
+        order = list(range(total_pages))
+        random.Random(seed).shuffle(order)
+        self.pages = torch.zeros(total_pages, 1, 2, kv_heads, page_size, hd, dtype=dtype)
+        width = max(-(-(p + n) // page_size) for p, n in items)
+        self.tables = torch.full((len(items), width), -1, dtype=torch.int32)
+        qs, self.want = [], []
+        for i, (past, new) in enumerate(items):
+            total = past + new
+            k = torch.randn(total, kv_heads * hd, generator=g).to(dtype)
+            v = torch.randn(total, kv_heads * hd, generator=g).to(dtype)
+            q = torch.randn(new, heads * hd, generator=g).to(dtype)
+            if peak is not None:
+                # one far key stands out for the last query: scale the pair so its score wins
+                key_at = peak(past, new)
+                q[-1] = q[-1] * 0 + 1.0
+                k[key_at] = k[key_at] * 0 + 3.0
+            blocks = -(-total // page_size)
+            mine = [order.pop() for _ in range(blocks)]
+            self.tables[i, :blocks] = torch.tensor(mine, dtype=torch.int32)
+            for t in range(total):
+                page, off = mine[t // page_size], t % page_size
+                self.pages[page, 0, 0, :, off] = k[t].reshape(kv_heads, hd)
+                self.pages[page, 0, 1, :, off] = v[t].reshape(kv_heads, hd)
+            if window > 0:      # pages the window has left behind are gone
+                for b in range(max(0, past - window + 1) // page_size):
+                    self.pages[mine[b]] = float("nan")
+                    self.tables[i, b] = -1
+            qs.append(q)
+            self.want.append(plain.attention(q.double(), k.double(), v.double(), heads, kv_heads,
+                                             hd, query_offset=past, window=window))
+        self.q = torch.cat(qs)
+        self.want = torch.cat(self.want)
+
+    def run(self, ops, nsplit=1):
+        group = self.heads // self.kv_heads
+        rows = ops.attention_rows_per_tile()
+        tile_item, tile_row0, qstart = [], [], []
+        at = 0
+        for i, (past, new) in enumerate(self.items):
+            qstart.append(at)
+            at += new
+            for r0 in range(0, new * group, rows):
+                tile_item.append(i)
+                tile_row0.append(r0)
+        i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+        pages = dev(self.pages)
+        q = dev(self.q)
+        tokens = q.shape[0]
+        out = torch.full((tokens, self.heads * self.hd), float("nan"), dtype=q.dtype, device="cuda")
+        part_o = part_ml = None
+        if nsplit > 1:
+            part_o = torch.full((nsplit * tokens * self.heads * self.hd,), float("nan"),
+                                device="cuda")
+            part_ml = torch.full((nsplit * tokens * self.heads * 2,), float("nan"), device="cuda")
+        ops.attention_generic(q, q.stride(0), pages[:, 0, 0], pages[:, 0, 1], pages.stride(0),
+                              self.page_size, dev(self.tables), i32(tile_item), i32(tile_row0),
+                              len(tile_item), i32(qstart), i32([n for _, n in self.items]),
+                              i32([p for p, _ in self.items]), out, tokens, self.heads,
+                              self.kv_heads, self.hd, self.window, 1.0 / math.sqrt(self.hd),
+                              nsplit, part_o, part_ml)
+        return out.cpu().double()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,hd,page_size", [
+    (4, 4, 16, 4), (6, 2, 48, 8), (7, 1, 80, 16), (28, 4, 128, 16), (3, 1, 256, 32),
+    (40, 1, 32, 5)])
+def test_attention_sizes(ops, dtype, heads, kv_heads, hd, page_size):
+    case = PagedCase(dtype, heads, kv_heads, hd, page_size,
+                     items=[(0, 37), (45, 1), (19, 6), (0, 1), (63, 2)], seed=heads)
+    got = case.run(ops)
+    assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nsplit", [2, 5, 32])
+def test_attention_split_keys(ops, dtype, nsplit):
+    case = PagedCase(dtype, 14, 2, 64, 16, items=[(700, 1), (0, 3), (301, 1), (33, 2)], seed=5)
+    whole, split = case.run(ops, 1), case.run(ops, nsplit)
+    assert (split - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+    assert (split - whole).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key_at", ["first", "page_edge", "far", "self"])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype, key_at):
+    pick = {"first": lambda p, n: 0, "page_edge": lambda p, n: 16 * 7 - 1,
+            "far": lambda p, n: 131, "self": lambda p, n: p + n - 1}[key_at]
+    case = PagedCase(dtype, 8, 2, 64, 16, items=[(600, 1), (500, 5)], seed=6, peak=pick)
+    # the scaled pair has score 3 * 64 / 8 = 24 over scores of order 1: the last query's
+    # output is that key's value, so a wrong page or offset shows at full size
+    got = case.run(ops, nsplit=1)
+    assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+    got = case.run(ops, nsplit=4)
+    assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 16, 21])
+def test_attention_window_edge(ops, dtype, window):
+    # the key just outside the window carries the peak: it must not be seen;
+    # pages wholly behind the window hold NaN and have no table entry
+    outside = lambda p, n: p + n - 1 - window
+    case = PagedCase(dtype, 6, 3, 32, 8, items=[(90, 1), (64, 7), (0, 30)], window=window,
+                     seed=7, peak=outside if window < 30 else None)
+    got = case.run(ops)
+    assert torch.isfinite(got).all()
+    assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+    inside = lambda p, n: p + n - window
+    case = PagedCase(dtype, 6, 3, 32, 8, items=[(90, 1), (64, 7)], window=window, seed=8,
+                     peak=inside)
+    got = case.run(ops, nsplit=2)
+    assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+
+
+def test_attention_refuses_what_it_cannot_take(ops):
+    from from_scratch_inference_engine_b200.kernels.ops import KernelError
+    case = PagedCase(torch.float32, 2, 2, 16, 4, items=[(0, 2)])
+    case.hd = 272
+    with pytest.raises(KernelError):
+        case.run(ops)
+
+
+# ---------------------------------------------------------------------------- sampling
+def test_argmax_ties_go_to_the_smallest_index(ops):
+    logits = torch.zeros(3, 151936)
+    logits[0, [70000, 5, 150000]] = 4.0
+    logits[1, 151935] = 1.0
+    logits[2] = -1.0
+    out = torch.empty(3, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(logits), out)
+    assert out.tolist() == [5, 151935, 0]
+
+
+@pytest.mark.parametrize("vocab", [1000, 151936])
+def test_sample_matches_plain_sampler(ops, vocab):
+    rng = random.Random(vocab)
+    torch.manual_seed(vocab)
+    cases = []
+    for temperature in (0.7, 1.0, 1.5):
+        for top_k in (0, 1, 5, 50):
+            for top_p in (1.0, 0.9, 0.3):
+                cases.append((temperature, top_k, top_p, rng.random()))
+    cases += [(1.0, 0, 1.0, 0.0), (1.0, 0, 1.0, 0.99999994), (0.8, 3, 0.95, 0.5)]
+    logits = torch.randn(len(cases), vocab) * 3
+    logits[:, 17] = logits[:, 400]                 # ties inside every row
+    logits[3, :] = 0.25                            # a row of equal logits
+    f32 = lambda v: dev(torch.tensor(v, dtype=torch.float32))
+    out = torch.empty(len(cases), dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), f32([c[0] for c in cases]),
+               dev(torch.tensor([c[1] for c in cases], dtype=torch.int32)),
+               f32([c[2] for c in cases]), f32([c[3] for c in cases]), out)
+    got = out.tolist()
+    mismatches = 0
+    for r, (temperature, top_k, top_p, u) in enumerate(cases):
+        want = plain.sample(logits[r].tolist(), temperature, top_k, top_p,
+                            float(np.float32(u)))
+        if got[r] != want:
+            # allowed only when u lands within float32 rounding of a step of the CDF: the
+            # running probability between the two tokens is then below 2e-6
+            order = sorted(range(vocab), key=lambda i: (-logits[r, i].item(), i))
+            w = np.exp((logits[r, order].double().numpy() - logits[r].max().item())
+                       / temperature)
+            cdf = np.cumsum(w) / w.sum()
+            lo, hi = sorted((order.index(got[r]), order.index(want)))
+            assert cdf[hi] - cdf[lo] < 2e-6, (r, cases[r], got[r], want)
+            mismatches += 1
+    assert mismatches <= 2
+
+
+def test_sample_frequencies(ops):
+    """2,000 draws from three tokens with probabilities 0.7 / 0.2 / 0.1."""
+    probs = torch.tensor([0.2, 0.7, 0.1])
+    logits = probs.log().repeat(2000, 1)
+    rng = random.Random(1)
+    u = torch.tensor([rng.random() for _ in range(2000)], dtype=torch.float32)
+    out = torch.empty(2000, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), dev(torch.ones(2000)), dev(torch.zeros(2000, dtype=torch.int32)),
+               dev(torch.ones(2000)), dev(u), out)
+    counts = torch.bincount(out.cpu().long(), minlength=3).tolist()
+    assert abs(counts[1] - 1400) < 90 and abs(counts[0] - 400) < 70 and abs(counts[2] - 200) < 55
