@@ -1,0 +1,314 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at the Qwen2.5-7B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl engine|reference]
+
+A step is one decode step of a batch of 8 requests whose contexts end at 4,096 tokens
+(random bf16 weights, uniform random token ids).  One JSON line comes out:
+
+  value     decoded tokens per second, timed on the device with CUDA events over K steps
+            of the step function with device-side argmax (no host round trip inside)
+  e2e       the same through the Python entry point (`Engine.step`): every step copies
+            its inputs from pinned host memory and reads the chosen tokens back
+  prefill   one 2,048-token prompt through the step function: tokens/s, ms and the
+            fraction of the measured bf16 matrix peak
+  roofline  bytes the decode step must read (every weight once + the live requests'
+            keys and values) / its time, against the measured copy bandwidth
+  points    decode tokens/s at batch 1 and 64
+
+Between timed steps nothing flushes L2: every step streams 15 GB of weights, far more
+than the 126 MB of L2.  The reference cannot be installed offline (its CMake build
+fetches Eigen, nlohmann/json and GoogleTest from the network), so `--impl reference`
+reports that and exits 0.  This engine runs on one GPU only: --gpus N > 1 exits 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPE_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=28,
+                hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                intermediate_size=18944, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, max_position_embeddings=32768,
+                use_sliding_window=False)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    source = "fallback"
+    values = dict(FALLBACK_PEAKS)
+    if path.exists():
+        try:
+            data = json.loads(path.read_text())
+            for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if key in data:
+                    values[key] = float(data[key])
+            source = "measured"
+        except (OSError, ValueError):
+            pass
+    return values, source
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.process, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.samples.append([field.strip() for field in line.split(",")])
+
+    def stop(self):
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, reasons, max_mhz = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for sample in self.samples:
+            if len(sample) < 7:
+                continue
+            try:
+                clocks.append(float(sample[0]))
+                max_mhz = float(sample[1])
+            except ValueError:
+                continue
+            for name, field in zip(names, sample[3:7]):
+                if field.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_mhz,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def weight_bytes(config, layers):
+    h, i = config.hidden_size, config.intermediate_size
+    per_layer = (config.q_width + 2 * config.kv_width) * h + h * config.q_width + 3 * i * h
+    return 2 * (layers * per_layer + config.vocab_size * h)
+
+
+def kv_bytes_per_token(config, layers):
+    return 2 * 2 * config.kv_width * layers
+
+
+def prefill_flops(config, layers, tokens):
+    h, i = config.hidden_size, config.intermediate_size
+    per_layer = (config.q_width + 2 * config.kv_width) * h + h * config.q_width + 3 * i * h
+    linear = 2.0 * tokens * (layers * per_layer + config.vocab_size * h / tokens)   # head: 1 row
+    attention = layers * 4.0 * config.q_width * tokens * (tokens + 1) / 2           # causal half
+    return linear + attention
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__,
+                                     formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=4096)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has")
+    parser.add_argument("--prefill-tokens", type=int, default=2048)
+    parser.add_argument("--points", default="1,64", help="extra decode batch sizes ('' = none)")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference cannot be installed offline: its CMake build fetches "
+                          "Eigen, nlohmann/json and GoogleTest from the network (pip install "
+                          "--no-index fails at FetchContent), and its CUDA path has no Python "
+                          "binding"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
+        return 2
+
+    import numpy as np
+    import torch
+    from from_scratch_inference_engine_b200 import (Engine, LoadedModel, ModelRunner,
+                                                    SamplingParams, StepEntry)
+    from from_scratch_inference_engine_b200.config import config_from_dict
+    from from_scratch_inference_engine_b200.kernels import ops
+
+    shape = dict(SHAPE_7B)
+    full_layers = shape["num_hidden_layers"]
+    layers = args.layers or full_layers
+    shape["num_hidden_layers"] = layers
+    config = config_from_dict(shape)
+    peak, peak_source = peaks()
+    steps, warmup = args.steps, max(args.warmup, 3)
+    page = 16
+    rng = np.random.default_rng(0)
+    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16",
+                                    max_positions=args.context + 64)
+    device = model.runtime.device
+
+    def timed(fn, count):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for index in range(count):
+            fn(index)
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / count          # ms per call
+
+    def fill(runner, batch, length):
+        """Prefill `batch` requests of `length` tokens through the step function."""
+        handles = []
+        for r in range(batch):
+            handle = runner.cache.open(r)
+            ids = rng.integers(0, config.vocab_size, size=length).tolist()
+            for at in range(0, length, 2048):
+                runner.step([StepEntry(handle, ids[at:at + 2048])])
+            handles.append(handle)
+        return handles
+
+    def decode_rate(batch, count, warm):
+        """Device-timed decode: `count` steps of `batch` single tokens with device argmax."""
+        start_len = args.context - (count + warm)
+        pages = batch * (-(-args.context // page) + 1)
+        runner = ModelRunner(model.model, model.runtime, page_size=page, num_pages=pages,
+                             max_requests=batch)
+        handles = fill(runner, batch, start_len)
+        tokens = rng.integers(0, config.vocab_size, size=(count + warm, batch))
+        picks = torch.empty(batch, dtype=torch.int32, device=device)
+
+        def step(index):
+            logits = runner.step([StepEntry(h, [int(tokens[index, b])], [0])
+                                  for b, h in enumerate(handles)])
+            ops.argmax(logits, picks)
+        for index in range(warm):
+            step(index)
+        before = ops.launches
+        ms = timed(lambda index: step(warm + index), count)
+        launches = ops.launches - before
+        runner.raise_on_device_error()
+        del runner
+        torch.cuda.empty_cache()
+        return ms, launches
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms_step, launches = decode_rate(args.batch, steps, warmup)
+    clock_record = clocks.stop()
+    value = args.batch * 1000.0 / ms_step
+
+    # ---- end to end through the Python entry point
+    slack = 64           # requests that finish their prompt early decode while others prefill
+    start_len = args.context - (steps + warmup + slack) - 1
+    engine = Engine(model, block_size=page, num_blocks=args.batch * (-(-args.context // page) + 1),
+                    max_batch=args.batch, max_step_tokens=2048)
+    for _ in range(args.batch):
+        engine.add_request(rng.integers(0, config.vocab_size, size=start_len).tolist(),
+                           SamplingParams(temperature=0.0),
+                           max_tokens=steps + warmup + slack + 1)
+    while not all(seq.prefilled for seq in engine.scheduler.sequences.values()):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    ring, sampler = engine.runner._ring, engine.sampler
+    h2d0, d2h0 = ring.bytes_staged + sampler.bytes_to_device, sampler.bytes_to_host
+    wall = time.perf_counter()
+    ms_e2e = timed(lambda index: engine.step(), steps)
+    wall = (time.perf_counter() - wall) * 1000.0 / steps
+    ms_e2e = max(ms_e2e, wall)
+    h2d = (ring.bytes_staged + sampler.bytes_to_device - h2d0) / steps
+    d2h = (sampler.bytes_to_host - d2h0) / steps
+    del engine
+    torch.cuda.empty_cache()
+
+    # ---- prefill of one prompt
+    tokens = args.prefill_tokens
+    runner = ModelRunner(model.model, model.runtime, page_size=page,
+                         num_pages=4 * (tokens // page + 1), max_requests=4)
+    prompts = [rng.integers(0, config.vocab_size, size=tokens).tolist() for _ in range(4)]
+
+    def prefill(index):
+        handle = runner.cache.open(("p", index))
+        runner.step([StepEntry(handle, prompts[index % 4], [tokens - 1])])
+        runner.cache.close(handle)
+    prefill(0)
+    ms_prefill = min(timed(prefill, 1) for _ in range(3))
+    flops = prefill_flops(config, layers, tokens)
+    prefill_record = {"value": tokens * 1000.0 / ms_prefill, "tokens": tokens,
+                      "ms": ms_prefill,
+                      "frac": flops / (ms_prefill * 1e-3) / (peak["bf16_tflops"] * 1e12)}
+    del runner
+    torch.cuda.empty_cache()
+
+    # ---- roofline of the decode step
+    context_mid = args.context - (steps + 1) / 2
+    step_bytes = weight_bytes(config, layers) + args.batch * context_mid * \
+        kv_bytes_per_token(config, layers)
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peak["hbm_gbs"], "peaks": peak_source}
+
+    points = {}
+    for batch in [int(b) for b in args.points.split(",") if b]:
+        count = max(8, steps // 4)
+        ms, _ = decode_rate(batch, count, 3)
+        points[f"decode_b{batch}"] = batch * 1000.0 / ms
+
+    record = {
+        "metric": "decode tok/s @ batch 8, context 4,096 (Qwen2.5-7B shape)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random bf16 weights N(0,0.02), uniform random token ids",
+        "impl": "engine",
+        "config": {"model": "Qwen2.5-7B shape", "global_batch": args.batch,
+                   "seq_len": args.context, "parallelism": "single GPU", "layers": layers,
+                   "layers_of_shape": full_layers, "hidden": config.hidden_size,
+                   "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
+                   "head_dim": config.head_dim, "intermediate": config.intermediate_size,
+                   "vocab": config.vocab_size, "kv_page": page,
+                   "prefill_tokens": tokens,
+                   "l2": "not flushed: each step streams 15 GB of weights, L2 is 126 MB"},
+        "e2e": {"value": args.batch * 1000.0 / ms_e2e, "unit": "tokens/s",
+                "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": prefill_record,
+        "roofline": roofline,
+        "points": points,
+        "clocks": clock_record,
+    }
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -38,6 +38,7 @@ class PinnedRing:
         self.buffers: List[Optional[torch.Tensor]] = [None] * depth
         self.events: List[Optional[torch.cuda.Event]] = [None] * depth
         self.next = 0
+        self.bytes_staged = 0        # host-to-device bytes so far (benchmarks read this)
 
     def stage(self, host: np.ndarray, device: torch.device) -> torch.Tensor:
         i = self.next
@@ -49,6 +50,7 @@ class PinnedRing:
             self.buffers[i] = torch.empty(max(n, 1024) * 2, dtype=torch.int32).pin_memory()
         staging = self.buffers[i][:n]
         staging.numpy()[:] = host
+        self.bytes_staged += n * 4
         out = staging.to(device, non_blocking=True)
         event = torch.cuda.Event()
         event.record()

@@ -50,6 +50,26 @@ class LoadedModel:
         model.bind(tensors, runtime)
         return cls(config, model, runtime)
 
+    @classmethod
+    def from_random(cls, config, seed: int = 0, std: float = 0.02, dtype="bfloat16",
+                    device="cuda:0", max_positions: int = 0) -> "LoadedModel":
+        """Random weights drawn on the device (no folder is written): N(0, std) matrices and
+        biases, gains 1 + N(0, std), rounded to bfloat16 first so that both compute dtypes see
+        the same numbers.  For benchmarks at sizes whose checkpoint would take minutes to
+        write and read back."""
+        spec = config.build_spec()
+        generator = torch.Generator(device=device).manual_seed(seed)
+        tensors = {}
+        for item in DecoderModel(spec).tensor_specs():
+            if item.optional:
+                continue
+            values = torch.randn(item.shape, generator=generator, device=device,
+                                 dtype=torch.float32) * std
+            if item.init == "gain":
+                values += 1.0
+            tensors[item.name] = values.to(torch.bfloat16)
+        return cls.from_tensors(config, tensors, dtype, device, max_positions)
+
     def forward(self, ids: Sequence[int]) -> torch.Tensor:
         """Logits [len(ids), vocab] of one whole sequence (bindings/module.cpp:70-76)."""
         pages = -(-len(ids) // 16) + 1

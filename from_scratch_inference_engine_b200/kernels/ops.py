@@ -47,7 +47,12 @@ def _need(tensor: torch.Tensor, dtype, name: str, contiguous: bool = True) -> No
         raise KernelError(f"{name} must be contiguous")
 
 
+launches = 0      # kernel launches issued through this module (benchmarks read this)
+
+
 def _check(code: int, what: str) -> None:
+    global launches
+    launches += 1
     if code == 0:
         return
     if code == -1:

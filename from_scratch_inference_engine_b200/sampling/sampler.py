@@ -56,6 +56,8 @@ class Sampler:
 
     def __init__(self, device):
         self.device = torch.device(device)
+        self.bytes_to_device = 0     # sampling parameters copied in (benchmarks read these)
+        self.bytes_to_host = 0       # chosen ids copied out
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                seeds: Sequence[int], indices: Sequence[int]) -> List[int]:
@@ -77,8 +79,10 @@ class Sampler:
                 host[2, r] = uniform_draw(seeds[r], indices[r])
                 host[3, r] = 0.0
             dev = torch.from_numpy(host).to(self.device)
+            self.bytes_to_device += host.nbytes + 4 * rows
             top_k = torch.tensor([max(0, int(p.top_k)) for p in params], dtype=torch.int32,
                                  device=self.device)
             ops.sample(logits, dev[0], top_k, dev[1], dev[2], picks[1])
         got = picks.cpu().numpy()
+        self.bytes_to_host += got.nbytes
         return [int(got[0, r] if params[r].greedy else got[1, r]) for r in range(rows)]
