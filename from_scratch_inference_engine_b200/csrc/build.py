@@ -66,7 +66,7 @@ def _build_dir() -> Path:
 
 def _digest(sources: Iterable[Path], defines: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for header in sorted(CSRC.glob("*.cuh")):
+    for header in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(header.name.encode())
         h.update(header.read_bytes())
     for source in sources:
