@@ -252,3 +252,78 @@ int fsie_attn_generic(const void* q, int q_ld, const void* k_pages, const void* 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// The same launch for callers that cannot allocate: the split results live in a fixed
+// array of this library instead of caller-provided buffers (see attention_static_scratch.h).
+#include "attention_static_scratch.h"
+
+namespace fsie {
+
+static __device__ __align__(256) float static_scratch[FSIE_STATIC_SCRATCH_FLOATS];
+
+// Device address of static_scratch per device ordinal, looked up once per device.  In host
+// code the array's name is only a handle for the runtime, not an address a kernel can use.
+constexpr int MAX_DEVICES = 64;
+static float* scratch_address[MAX_DEVICES] = {};
+
+static int static_scratch_for_current_device(float** address) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES)
+        return FSIE_ERR_SCRATCH_SETUP;
+    if (scratch_address[device] == nullptr) {
+        float* found = nullptr;
+        if (cudaGetSymbolAddress((void**)&found, static_scratch) != cudaSuccess || !found)
+            return FSIE_ERR_SCRATCH_SETUP;
+        scratch_address[device] = found;
+    }
+    *address = scratch_address[device];
+    return 0;
+}
+
+}  // namespace fsie
+
+extern "C" {
+
+long long fsie_attn_static_scratch_floats(int tokens, int heads, int head_dim, int nsplit) {
+    if (nsplit <= 1) return 0;
+    return (long long)nsplit * tokens * heads * ((long long)head_dim + 2);
+}
+
+const char* fsie_attn_static_scratch_error(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case FSIE_ERR_SCRATCH_TOO_SMALL:
+            return "the launch needs more split scratch than the library's fixed array holds "
+                   "(nsplit * tokens * heads * (head_dim + 2) floats > FSIE_STATIC_SCRATCH_FLOATS); "
+                   "use fewer splits or fewer tokens per call, or fsie_attn_generic with your own buffers";
+        case FSIE_ERR_SCRATCH_SETUP:
+            return "the device address of the library's scratch array could not be looked up "
+                   "on the current device";
+        case fsie::ERR_BAD_ARGUMENT: return "an argument was refused by the launcher";
+        default: return "CUDA error (the code is a cudaError_t)";
+    }
+}
+
+int fsie_attn_generic_static_scratch(
+    const void* q, int q_ld, const void* k_pages, const void* v_pages, long long page_stride,
+    int page_size, const int* block_tables, int bt_stride, const int* tile_item,
+    const int* tile_row0, int tiles, const int* item_qstart, const int* item_qlen,
+    const int* item_pos0, void* out, int out_ld, int tokens, int heads, int kv_heads,
+    int head_dim, int window, int nsplit, float scale, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || heads <= 0 || head_dim <= 0 || nsplit < 1) return fsie::ERR_BAD_ARGUMENT;
+    const long long need = fsie_attn_static_scratch_floats(tokens, heads, head_dim, nsplit);
+    if (need > (long long)FSIE_STATIC_SCRATCH_FLOATS) return FSIE_ERR_SCRATCH_TOO_SMALL;
+    float* scratch = nullptr;
+    const int rc = fsie::static_scratch_for_current_device(&scratch);
+    if (rc != 0) return rc;
+    // [nsplit, tokens, heads, head_dim] partial sums, then [nsplit, tokens, heads, 2] (max, sum)
+    float* part_o = scratch;
+    float* part_ml = scratch + (long long)nsplit * tokens * heads * head_dim;
+    return fsie_attn_generic(q, q_ld, k_pages, v_pages, page_stride, page_size, block_tables,
+                             bt_stride, tile_item, tile_row0, tiles, item_qstart, item_qlen,
+                             item_pos0, out, out_ld, part_o, part_ml, tokens, heads, kv_heads,
+                             head_dim, window, nsplit, scale, dtype, stream);
+}
+
+}  // extern "C"
