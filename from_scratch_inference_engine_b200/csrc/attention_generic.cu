@@ -14,6 +14,7 @@
 // `window` of them), softmax, weighted sum of values; here as a running softmax in
 // 32-bit like the reference GPU kernel does in 64-bit (src/cuda/device.cu:139-190).
 #include "common.cuh"
+#include "attention_params.cuh"
 #include <math.h>
 
 namespace fsie {
@@ -24,18 +25,6 @@ constexpr int RPW = ROWS / WARPS;
 constexpr int KT = 32;            // keys per shared-memory tile (one per lane)
 constexpr int MAX_DPL = 8;        // head_dim <= 32 * MAX_DPL
 
-struct AttnParams {
-    const void* q; int q_ld;                 // [tokens, q_ld]; head h of token t at t*q_ld + h*head_dim
-    const void* k_pages; const void* v_pages;
-    long long page_stride; int page_size;    // elements between pages; slots per page
-    const int* block_tables; int bt_stride;  // [items, bt_stride] page ids (-1 = released)
-    const int* tile_item; const int* tile_row0;   // [tiles]
-    const int* item_qstart; const int* item_qlen; const int* item_pos0;   // [items]
-    void* out; int out_ld;                   // [tokens, out_ld]
-    float* part_o; float* part_ml;           // [nsplit, tokens, heads, head_dim], [nsplit, tokens, heads, 2]
-    int tokens, heads, kv_heads, head_dim, window, nsplit;
-    float scale;
-};
 
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)

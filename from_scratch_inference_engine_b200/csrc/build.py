@@ -32,7 +32,11 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 # library name -> sources; a library may also be requested with -D defines (specialisations)
 LIBRARIES: Dict[str, Sequence[str]] = {
     "core": ("elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "sampling.cu"),
+    # tensor-core attention, one build per head size: defines=("-DHEAD_DIM=128",)
+    "attn_mma": ("attention_mma.cu",),
 }
+# specialisations compiled by build_all() beside the default form of every library
+DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)]}
 
 _loaded: Dict[Tuple[str, Tuple[str, ...]], ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -154,4 +158,5 @@ def load_library(name: str, defines: Sequence[str] = ()) -> ctypes.CDLL:
 def build_all() -> None:
     """Compile every library in its default form (the build check of the package)."""
     for name in LIBRARIES:
-        library_path(name)
+        for defines in DEFAULT_SPECIALISATIONS.get(name, [()]):
+            library_path(name, defines)

@@ -122,6 +122,44 @@ class StepContext:
             self._tiles[key] = Tiles(dev[:n], dev[n:2 * n], n)
         return self._tiles[key]
 
+    def attention_row_classes(self, group_size: int, class_rows):
+        """Requests sorted into row classes by their number of query rows (new tokens x
+        group size): class c takes those that fit one tile of class_rows[c] rows, the last
+        class takes the rest in as many tiles as needed.  Returns, per non-empty class,
+        (class index, Tiles, int32 device list of the class's tokens, their count, the
+        longest context in the class)."""
+        key = ("classes", group_size, tuple(class_rows))
+        if key in self._tiles:
+            return self._tiles[key]
+        rows = self.h_qlen.astype(np.int64) * group_size
+        last = len(class_rows) - 1
+        which = np.full(self.num_items, last, dtype=np.int64)
+        for c in range(last - 1, -1, -1):
+            which[rows <= class_rows[c]] = c
+        host, layout = [], []
+        for c, per_tile in enumerate(class_rows):
+            members = np.nonzero(which == c)[0]
+            if members.size == 0:
+                continue
+            counts = (rows[members] + per_tile - 1) // per_tile
+            item = np.repeat(members.astype(np.int32), counts)
+            first = np.cumsum(counts) - counts
+            row0 = ((np.arange(int(counts.sum())) - np.repeat(first, counts)) * per_tile)
+            tokens = np.concatenate([np.arange(self.h_qstart[i], self.h_qstart[i] + self.h_qlen[i],
+                                               dtype=np.int32) for i in members])
+            longest = int((self.h_pos0[members] + self.h_qlen[members]).max())
+            layout.append((c, item.size, tokens.size, longest))
+            host += [item, row0.astype(np.int32), tokens]
+        dev = self._ring.stage(np.concatenate(host), self.runtime.device)
+        out, cut = [], 0
+        for c, n_tiles, n_tokens, longest in layout:
+            tiles = Tiles(dev[cut:cut + n_tiles], dev[cut + n_tiles:cut + 2 * n_tiles], n_tiles)
+            cut += 2 * n_tiles
+            out.append((c, tiles, dev[cut:cut + n_tokens], n_tokens, longest))
+            cut += n_tokens
+        self._tiles[key] = out
+        return out
+
     def scratch(self, name: str, numel: int) -> torch.Tensor:
         """Float32 scratch memory that lives across steps (grown when a step needs more)."""
         have = self._scratch.get(name)

@@ -244,6 +244,64 @@ def attention_generic(q: torch.Tensor, q_ld: int, k_pages: torch.Tensor, v_pages
     return out
 
 
+_attn_mma = {}
+
+
+def attn_mma(head_dim: int):
+    """The tensor-core attention library for one head size, compiled at first use."""
+    if head_dim not in _attn_mma:
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise KernelError(f"tensor-core attention takes head sizes 16..256 in steps of 16, "
+                              f"not {head_dim}")
+        lib = build.load_library("attn_mma", (f"-DHEAD_DIM={head_dim}",))
+        i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_attn_mma.argtypes = [i, p, i, p, p, ll, i, p, i, p, p, i, p, p, p, p, i, p, p,
+                                      i, i, i, i, i, i, f, p, i, p]
+        lib.fsie_attn_mma.restype = i
+        lib.fsie_attn_mma_rows.argtypes = [i]
+        lib.fsie_attn_mma_rows.restype = i
+        _attn_mma[head_dim] = lib
+    return _attn_mma[head_dim]
+
+
+ATTENTION_ROW_CLASSES = (16, 32, 64)      # rows per tile of row class 0, 1, 2
+
+
+def attention_mma(row_class: int, q: torch.Tensor, q_ld: int, k_pages: torch.Tensor,
+                  v_pages: torch.Tensor, page_stride: int, page_size: int,
+                  block_tables: torch.Tensor, tile_item: torch.Tensor, tile_row0: torch.Tensor,
+                  num_tiles: int, item_qstart: torch.Tensor, item_qlen: torch.Tensor,
+                  item_pos0: torch.Tensor, out: torch.Tensor, tokens: int, heads: int,
+                  kv_heads: int, head_dim: int, window: int, scale: float, nsplit: int = 1,
+                  part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                  combine_tokens: Optional[torch.Tensor] = None, num_combine: int = 0
+                  ) -> torch.Tensor:
+    """bfloat16 attention of one row class (tiles of 16, 32 or 64 rows) on the tensor cores."""
+    for name, t in (("block_tables", block_tables), ("tile_item", tile_item),
+                    ("tile_row0", tile_row0), ("item_qstart", item_qstart),
+                    ("item_qlen", item_qlen), ("item_pos0", item_pos0)):
+        _need(t, torch.int32, name)
+    _need(q, torch.bfloat16, "q", contiguous=False)
+    _need(out, torch.bfloat16, "out")
+    if k_pages.dtype is not torch.bfloat16 or v_pages.dtype is not torch.bfloat16:
+        raise KernelError("attention_mma: the cache must be bfloat16")
+    if nsplit > 1:
+        _need(part_o, torch.float32, "part_o")
+        _need(part_ml, torch.float32, "part_ml")
+        if part_o.numel() < nsplit * tokens * heads * head_dim or \
+                part_ml.numel() < nsplit * tokens * heads * 2:
+            raise KernelError("attention_mma: split scratch is too small")
+        if combine_tokens is not None:
+            _need(combine_tokens, torch.int32, "combine_tokens")
+    _check(attn_mma(head_dim).fsie_attn_mma(
+        row_class, _ptr(q), q_ld, _ptr(k_pages), _ptr(v_pages), page_stride, page_size,
+        _ptr(block_tables), block_tables.stride(0), _ptr(tile_item), _ptr(tile_row0), num_tiles,
+        _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0), _ptr(out), out.stride(0),
+        _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, head_dim, window, nsplit,
+        float(scale), _ptr(combine_tokens), num_combine, _stream()), "attention_mma")
+    return out
+
+
 # --------------------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _need(logits, torch.float32, "logits")

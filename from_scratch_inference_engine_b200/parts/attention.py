@@ -81,23 +81,43 @@ class GqaAttention(Mixer):
         return rt.linear(out, self.w_o, None)
 
     def _attend(self, ctx, qkv: torch.Tensor, group, cache: LayerCache, out: torch.Tensor) -> None:
-        """Attention of the step's tokens over the pages: row tiles of (token, head) pairs, the
-        key range split over several blocks when the batch alone would not fill the GPU."""
+        """Attention of the step's tokens over the pages.  Work is cut into tiles of query
+        rows, a row being a (token, head of the group) pair; a tile's key range is split
+        over several blocks when the batch alone would not fill the GPU.  bfloat16 runs on
+        the tensor cores (one launch per row class present in the batch: single decoded
+        tokens, short portions, long portions); float32 runs the 32-bit kernel."""
         tokens = qkv.shape[0]
         group_size = self.num_heads // self.num_kv_heads
+        sms = ctx.runtime.sm_count
+
+        def splits(blocks: int, longest: int) -> int:
+            if blocks >= sms:
+                return 1
+            return max(1, min(-(-2 * sms // blocks), longest // 128, 32))
+
+        common = (cache.k_pages, cache.v_pages, cache.page_stride, group.page_size,
+                  group.block_tables)
+        if qkv.dtype is torch.bfloat16 and self.head_dim % 16 == 0:
+            for row_class, tiles, class_tokens, count, longest in \
+                    ctx.attention_row_classes(group_size, ops.ATTENTION_ROW_CLASSES):
+                nsplit = splits(tiles.count * self.num_kv_heads, longest)
+                part_o = part_ml = None
+                if nsplit > 1:
+                    part_o = ctx.scratch("attention.part_o", nsplit * tokens * self.q_width)
+                    part_ml = ctx.scratch("attention.part_ml", nsplit * tokens * self.num_heads * 2)
+                ops.attention_mma(row_class, qkv, qkv.stride(0), *common, tiles.item, tiles.row0,
+                                  tiles.count, ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out,
+                                  tokens, self.num_heads, self.num_kv_heads, self.head_dim,
+                                  self.window, self.scale, nsplit, part_o, part_ml,
+                                  class_tokens, count)
+            return
         tiles = ctx.attention_tiles(group_size, ops.attention_rows_per_tile())
-        blocks = tiles.count * self.num_kv_heads
-        nsplit = 1
-        if blocks < ctx.runtime.sm_count:
-            by_fill = -(-2 * ctx.runtime.sm_count // blocks)
-            by_length = max(1, ctx.max_context // 128)
-            nsplit = max(1, min(by_fill, by_length, 32))
+        nsplit = splits(tiles.count * self.num_kv_heads, ctx.max_context)
         part_o = part_ml = None
         if nsplit > 1:
             part_o = ctx.scratch("attention.part_o", nsplit * tokens * self.q_width)
             part_ml = ctx.scratch("attention.part_ml", nsplit * tokens * self.num_heads * 2)
-        ops.attention_generic(qkv, qkv.stride(0), cache.k_pages, cache.v_pages, cache.page_stride,
-                              group.page_size, group.block_tables, tiles.item, tiles.row0,
-                              tiles.count, ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out,
-                              tokens, self.num_heads, self.num_kv_heads, self.head_dim,
-                              self.window, self.scale, nsplit, part_o, part_ml)
+        ops.attention_generic(qkv, qkv.stride(0), *common, tiles.item, tiles.row0, tiles.count,
+                              ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out, tokens,
+                              self.num_heads, self.num_kv_heads, self.head_dim, self.window,
+                              self.scale, nsplit, part_o, part_ml)

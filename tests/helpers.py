@@ -38,7 +38,7 @@ TINY = {
                           vocab_size=331, rope_theta=50000.0, rms_norm_eps=3e-6,
                           tie_word_embeddings=False, max_position_embeddings=512,
                           use_sliding_window=True, sliding_window=21, max_window_layers=1),
-              seed=2, std=0.12),
+              seed=2, std=0.08),
     # explicit head_dim: q width 4 * 32 = 128 differs from hidden 96
     "D": dict(config=dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2",
                           num_hidden_layers=2, hidden_size=96, num_attention_heads=4,

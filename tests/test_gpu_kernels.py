@@ -225,55 +225,101 @@ class PagedCase:
         return out.cpu().double()
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+    def run_mma(self, ops, nsplit=1):
+        """The tensor-core kernel: requests sorted into row classes as the engine does."""
+        group = self.heads // self.kv_heads
+        i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
+        qstart, at = [], 0
+        for _, new in self.items:
+            qstart.append(at)
+            at += new
+        pages, q = dev(self.pages), dev(self.q)
+        tokens = q.shape[0]
+        out = torch.full((tokens, self.heads * self.hd), float("nan"), dtype=q.dtype, device="cuda")
+        part_o = part_ml = None
+        if nsplit > 1:
+            part_o = torch.full((nsplit * tokens * self.heads * self.hd,), float("nan"), device="cuda")
+            part_ml = torch.full((nsplit * tokens * self.heads * 2,), float("nan"), device="cuda")
+        classes = ops.ATTENTION_ROW_CLASSES
+        for c, per_tile in enumerate(classes):
+            tile_item, tile_row0, toks = [], [], []
+            for i, (_, new) in enumerate(self.items):
+                rows = new * group
+                fits = [k for k, r in enumerate(classes) if rows <= r]
+                if (fits[0] if fits else len(classes) - 1) != c:
+                    continue
+                toks += list(range(qstart[i], qstart[i] + new))
+                for r0 in range(0, rows, per_tile):
+                    tile_item.append(i)
+                    tile_row0.append(r0)
+            if not tile_item:
+                continue
+            ops.attention_mma(c, q, q.stride(0), pages[:, 0, 0], pages[:, 0, 1], pages.stride(0),
+                              self.page_size, dev(self.tables), i32(tile_item), i32(tile_row0),
+                              len(tile_item), i32(qstart), i32([n for _, n in self.items]),
+                              i32([p for p, _ in self.items]), out, tokens, self.heads,
+                              self.kv_heads, self.hd, self.window, 1.0 / math.sqrt(self.hd),
+                              nsplit, part_o, part_ml, i32(toks), len(toks))
+        return out.cpu().double()
+
+
+def run_kernel(case, ops, kernel, nsplit=1):
+    return case.run_mma(ops, nsplit) if kernel == "mma" else case.run(ops, nsplit)
+
+
+KERNELS = [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16)]
+
+
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("heads,kv_heads,hd,page_size", [
     (4, 4, 16, 4), (6, 2, 48, 8), (7, 1, 80, 16), (28, 4, 128, 16), (3, 1, 256, 32),
     (40, 1, 32, 5)])
-def test_attention_sizes(ops, dtype, heads, kv_heads, hd, page_size):
+def test_attention_sizes(ops, kernel, dtype, heads, kv_heads, hd, page_size):
     case = PagedCase(dtype, heads, kv_heads, hd, page_size,
-                     items=[(0, 37), (45, 1), (19, 6), (0, 1), (63, 2)], seed=heads)
-    got = case.run(ops)
+                     items=[(0, 37), (45, 1), (19, 6), (0, 1), (63, 2), (130, 70)], seed=heads)
+    got = run_kernel(case, ops, kernel)
     assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("nsplit", [2, 5, 32])
-def test_attention_split_keys(ops, dtype, nsplit):
-    case = PagedCase(dtype, 14, 2, 64, 16, items=[(700, 1), (0, 3), (301, 1), (33, 2)], seed=5)
-    whole, split = case.run(ops, 1), case.run(ops, nsplit)
+def test_attention_split_keys(ops, kernel, dtype, nsplit):
+    case = PagedCase(dtype, 14, 2, 64, 16, items=[(700, 1), (0, 3), (301, 1), (33, 2), (400, 20)],
+                     seed=5)
+    whole, split = run_kernel(case, ops, kernel, 1), run_kernel(case, ops, kernel, nsplit)
     assert (split - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
     assert (split - whole).abs().max().item() < tol(dtype) * case.want.abs().max().item()
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("key_at", ["first", "page_edge", "far", "self"])
-def test_attention_finds_one_far_key_among_hundreds(ops, dtype, key_at):
+def test_attention_finds_one_far_key_among_hundreds(ops, kernel, dtype, key_at):
     pick = {"first": lambda p, n: 0, "page_edge": lambda p, n: 16 * 7 - 1,
             "far": lambda p, n: 131, "self": lambda p, n: p + n - 1}[key_at]
     case = PagedCase(dtype, 8, 2, 64, 16, items=[(600, 1), (500, 5)], seed=6, peak=pick)
     # the scaled pair has score 3 * 64 / 8 = 24 over scores of order 1: the last query's
     # output is that key's value, so a wrong page or offset shows at full size
-    got = case.run(ops, nsplit=1)
+    got = run_kernel(case, ops, kernel, nsplit=1)
     assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
-    got = case.run(ops, nsplit=4)
+    got = run_kernel(case, ops, kernel, nsplit=4)
     assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("window", [1, 16, 21])
-def test_attention_window_edge(ops, dtype, window):
+def test_attention_window_edge(ops, kernel, dtype, window):
     # the key just outside the window carries the peak: it must not be seen;
     # pages wholly behind the window hold NaN and have no table entry
     outside = lambda p, n: p + n - 1 - window
     case = PagedCase(dtype, 6, 3, 32, 8, items=[(90, 1), (64, 7), (0, 30)], window=window,
                      seed=7, peak=outside if window < 30 else None)
-    got = case.run(ops)
+    got = run_kernel(case, ops, kernel)
     assert torch.isfinite(got).all()
     assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
     inside = lambda p, n: p + n - window
     case = PagedCase(dtype, 6, 3, 32, 8, items=[(90, 1), (64, 7)], window=window, seed=8,
                      peak=inside)
-    got = case.run(ops, nsplit=2)
+    got = run_kernel(case, ops, kernel, nsplit=2)
     assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
 
 
@@ -283,6 +329,8 @@ def test_attention_refuses_what_it_cannot_take(ops):
     case.hd = 272
     with pytest.raises(KernelError):
         case.run(ops)
+    with pytest.raises(KernelError, match="head sizes"):
+        ops.attn_mma(24)
 
 
 # ---------------------------------------------------------------------------- sampling
