@@ -69,6 +69,60 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int vocab, int* 
     }
 }
 
+// The same in two stages for wide vocabularies: `parts` blocks per row each reduce a
+// segment to (value, index), one warp per row picks among them.
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, int vocab, int parts,
+                                      float* __restrict__ part_v, int* __restrict__ part_i) {
+    __shared__ float best_v[8];
+    __shared__ int best_i[8];
+    const int row = blockIdx.y, part = blockIdx.x;
+    const float* src = logits + (size_t)row * vocab;
+    const int seg = (vocab + parts - 1) / parts;
+    const int begin = part * seg, end = min(vocab, begin + seg);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll 4
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = src[i];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int warps = (blockDim.x + 31) >> 5;
+        for (int w = 1; w < warps; ++w)
+            if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+        part_v[(size_t)row * parts + part] = bv;
+        part_i[(size_t)row * parts + part] = bi;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                    int parts, int* __restrict__ out) {
+    const int row = blockIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int p = threadIdx.x; p < parts; p += 32) {
+        const float v = part_v[(size_t)row * parts + p];
+        const int i = part_i[(size_t)row * parts + p];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
 struct RowView {
     const float* row; int vocab; float inv_temp; float maxl;
     unsigned kept_key;     // top-k boundary: every key above it is kept ...
@@ -218,6 +272,18 @@ int fsie_argmax(const float* logits, int rows, int vocab, int* out, cudaStream_t
     if (rows <= 0) return 0;
     if (vocab <= 0) return fsie::ERR_BAD_ARGUMENT;
     fsie::argmax_kernel<<<rows, 1024, 0, stream>>>(logits, vocab, out);
+    return FSIE_LAUNCH_CHECK();
+}
+
+// Two-stage argmax; `scratch` holds rows * parts floats followed by rows * parts ints.
+int fsie_argmax_staged(const float* logits, int rows, int vocab, int* out, void* scratch, int parts,
+                       cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || parts <= 0 || !scratch) return fsie::ERR_BAD_ARGUMENT;
+    float* part_v = (float*)scratch;
+    int* part_i = (int*)scratch + (size_t)rows * parts;
+    fsie::argmax_partial_kernel<<<dim3(parts, rows), 256, 0, stream>>>(logits, vocab, parts, part_v, part_i);
+    fsie::argmax_final_kernel<<<rows, 32, 0, stream>>>(part_v, part_i, parts, out);
     return FSIE_LAUNCH_CHECK();
 }
 

@@ -80,10 +80,11 @@ def core():
                                           i, i, i, i, i, i, f, i, p]
         lib.fsie_attn_generic_rows.argtypes = []
         lib.fsie_argmax.argtypes = [p, i, i, p, p]
+        lib.fsie_argmax_staged.argtypes = [p, i, i, p, p, i, p]
         lib.fsie_sample.argtypes = [p, i, i, p, p, p, p, p, p]
         for name in ("fsie_embed_gather", "fsie_add_rmsnorm", "fsie_rope_kv_write", "fsie_swiglu",
                      "fsie_gemm_f32", "fsie_attn_generic", "fsie_attn_generic_rows",
-                     "fsie_argmax", "fsie_sample"):
+                     "fsie_argmax", "fsie_argmax_staged", "fsie_sample"):
             getattr(lib, name).restype = ctypes.c_int
         _core = lib
     return _core
@@ -303,10 +304,24 @@ def attention_mma(row_class: int, q: torch.Tensor, q_ld: int, k_pages: torch.Ten
 
 
 # --------------------------------------------------------------------------- sampling
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+ARGMAX_PARTS = 32      # blocks per row of the two-stage argmax
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor,
+           scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = index of the largest logit of row r, ties to the smallest index.  With
+    `scratch` (float32, at least 2 * rows * ARGMAX_PARTS elements) a wide row is reduced by
+    ARGMAX_PARTS blocks and a second small kernel; without it one block takes each row."""
     _need(logits, torch.float32, "logits")
     _need(out, torch.int32, "out")
     rows, vocab = logits.shape
+    if scratch is not None and vocab >= 8192:
+        _need(scratch, torch.float32, "scratch")
+        if scratch.numel() < 2 * rows * ARGMAX_PARTS:
+            raise KernelError("argmax: scratch is too small")
+        _check(core().fsie_argmax_staged(_ptr(logits), rows, vocab, _ptr(out), _ptr(scratch),
+                                         ARGMAX_PARTS, _stream()), "argmax")
+        return out
     _check(core().fsie_argmax(_ptr(logits), rows, vocab, _ptr(out), _stream()), "argmax")
     return out
 

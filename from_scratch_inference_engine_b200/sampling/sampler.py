@@ -56,6 +56,7 @@ class Sampler:
 
     def __init__(self, device):
         self.device = torch.device(device)
+        self._scratch = None
         self.bytes_to_device = 0     # sampling parameters copied in (benchmarks read these)
         self.bytes_to_host = 0       # chosen ids copied out
 
@@ -70,7 +71,11 @@ class Sampler:
         any_greedy = any(p.greedy for p in params)
         any_random = any(not p.greedy for p in params)
         if any_greedy:
-            ops.argmax(logits, picks[0])
+            need = 2 * rows * ops.ARGMAX_PARTS
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(max(need, 4096), dtype=torch.float32,
+                                            device=self.device)
+            ops.argmax(logits, picks[0], self._scratch)
         if any_random:
             host = np.empty((4, rows), dtype=np.float32)
             for r, p in enumerate(params):

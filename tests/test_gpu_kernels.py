@@ -36,19 +36,20 @@ def dev(t, dtype=None):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_embed_gather(ops, dtype):
     torch.manual_seed(0)
-    table = dev(torch.randn(1000, 300), dtype)
-    ids = dev(torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32))
-    out = torch.empty(5, 300, device="cuda")
-    error = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ops.embed_gather(ids, table, out, error)
-    assert torch.equal(out, table[ids.long()].float()) and error.item() == 0
-    ops.embed_gather(dev(torch.tensor([3, 1000], dtype=torch.int32)), table, out, error)
-    assert error.item() == 1 and out[1].abs().max().item() == 0.0     # refused, not read
+    for hidden in (300, 301, 3584):
+        table = dev(torch.randn(1000, hidden), dtype)
+        ids = dev(torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32))
+        out = torch.empty(5, hidden, device="cuda")
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.embed_gather(ids, table, out, error)
+        assert torch.equal(out, table[ids.long()].float()) and error.item() == 0
+        ops.embed_gather(dev(torch.tensor([3, 1000], dtype=torch.int32)), table, out, error)
+        assert error.item() == 1 and out[1].abs().max().item() == 0.0     # refused, not read
 
 
 # ----------------------------------------------------------------------- add + RMSNorm
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden", [64, 777, 3584, 9000])
+@pytest.mark.parametrize("hidden", [64, 777, 3584, 9000, 8 * 1500, 8 * 3000, 8 * 5000])
 def test_add_rmsnorm(ops, dtype, hidden):
     torch.manual_seed(1)
     rows, eps = 7, 1e-5
@@ -78,7 +79,8 @@ def test_add_rmsnorm(ops, dtype, hidden):
 # ----------------------------------------------------- rotary encoding + cache write
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,hd,rotary,theta", [(5, 5, 16, 16, 1e4), (6, 2, 48, 32, 5e5),
-                                                            (7, 1, 128, 128, 1e6)])
+                                                            (7, 1, 128, 128, 1e6), (3, 3, 20, 12, 1e4),
+                                                            (28, 4, 128, 64, 1e6)])
 def test_rope_kv_write(ops, dtype, heads, kv_heads, hd, rotary, theta):
     from from_scratch_inference_engine_b200.parts.rope import rotary_table
     torch.manual_seed(2)
@@ -128,11 +130,12 @@ def test_rope_kv_write(ops, dtype, heads, kv_heads, hd, rotary, theta):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(ops, dtype):
     torch.manual_seed(3)
-    gu = (torch.randn(13, 2 * 333) * 3).to(dtype)
-    out = torch.empty(13, 333, dtype=dtype, device="cuda")
-    ops.swiglu(dev(gu), out)
-    want = plain.silu_mul(gu[:, :333].double(), gu[:, 333:].double())
-    assert (out.cpu().double() - want).abs().max().item() < tol(dtype) * want.abs().max().item()
+    for inter in (333, 18944 // 8, 8):
+        gu = (torch.randn(13, 2 * inter) * 3).to(dtype)
+        out = torch.empty(13, inter, dtype=dtype, device="cuda")
+        ops.swiglu(dev(gu), out)
+        want = plain.silu_mul(gu[:, :inter].double(), gu[:, inter:].double())
+        assert (out.cpu().double() - want).abs().max().item() < tol(dtype) * want.abs().max().item()
 
 
 # ---------------------------------------------------------------------- float32 product
@@ -342,6 +345,15 @@ def test_argmax_ties_go_to_the_smallest_index(ops):
     out = torch.empty(3, dtype=torch.int32, device="cuda")
     ops.argmax(dev(logits), out)
     assert out.tolist() == [5, 151935, 0]
+    staged = torch.full((3,), -7, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(logits), staged, torch.empty(2 * 3 * ops.ARGMAX_PARTS, device="cuda"))
+    assert staged.tolist() == [5, 151935, 0]
+    torch.manual_seed(9)
+    wide = torch.randn(5, 100003)
+    ops.argmax(dev(wide), staged.new_empty(5), None)
+    got = torch.empty(5, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(wide), got, torch.empty(2 * 5 * ops.ARGMAX_PARTS, device="cuda"))
+    assert got.tolist() == wide.argmax(-1).tolist()
 
 
 @pytest.mark.parametrize("vocab", [1000, 151936])
