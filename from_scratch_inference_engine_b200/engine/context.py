@@ -40,7 +40,10 @@ class PinnedRing:
         self.next = 0
         self.bytes_staged = 0        # host-to-device bytes so far (benchmarks read this)
 
-    def stage(self, host: np.ndarray, device: torch.device) -> torch.Tensor:
+    def stage(self, host: np.ndarray, device: torch.device,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Copy `host` (int32) to the device; into the front of `out` when given (a fixed
+        buffer that a captured graph reads), else into fresh device memory."""
         i = self.next
         self.next = (i + 1) % self.depth
         if self.events[i] is not None:
@@ -51,7 +54,11 @@ class PinnedRing:
         staging = self.buffers[i][:n]
         staging.numpy()[:] = host
         self.bytes_staged += n * 4
-        out = staging.to(device, non_blocking=True)
+        if out is None:
+            out = staging.to(device, non_blocking=True)
+        else:
+            out = out[:n]
+            out.copy_(staging, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self.events[i] = event
@@ -62,8 +69,13 @@ class StepContext:
     def __init__(self, runtime, ring: PinnedRing, scratch: Dict[str, torch.Tensor],
                  error: torch.Tensor, token_ids: Sequence[int], q_start: Sequence[int],
                  q_len: Sequence[int], pos0: Sequence[int], slots: Sequence[int],
-                 group_tables: Sequence[Tuple[int, List[List[int]]]]):
-        """group_tables: per cache group (page_size, block table of each item)."""
+                 group_tables: Sequence[Tuple[int, List[List[int]]]],
+                 table_width: int = 0, out: Optional[torch.Tensor] = None,
+                 max_context: int = 0):
+        """group_tables: per cache group (page_size, block table of each item).
+        table_width forces the width of the device block tables, `out` is a fixed device
+        buffer to fill instead of fresh memory, max_context overrides the longest context
+        (all three serve captured graphs, whose shapes and launch choices must not vary)."""
         self.runtime = runtime
         self._ring, self._scratch, self.error = ring, scratch, error
         self.num_tokens = T = len(token_ids)
@@ -72,7 +84,8 @@ class StepContext:
         self.h_qlen = np.asarray(q_len, dtype=np.int32)
         self.h_pos0 = np.asarray(pos0, dtype=np.int32)
         self.h_slots = np.asarray(slots, dtype=np.int32)
-        self.max_context = int((self.h_pos0 + self.h_qlen).max()) if I else 0
+        self.max_context = max_context or (int((self.h_pos0 + self.h_qlen).max()) if I else 0)
+        self.fixed_context = max_context
         positions = np.concatenate([np.arange(p, p + n, dtype=np.int32)
                                     for p, n in zip(pos0, q_len)]) if I else np.zeros(0, np.int32)
         token_item = np.repeat(np.arange(I, dtype=np.int32), self.h_qlen)
@@ -80,7 +93,7 @@ class StepContext:
                  self.h_pos0, self.h_slots]
         shapes = []
         for page_size, tables in group_tables:
-            width = max(1, max((len(t) for t in tables), default=1))
+            width = table_width or max(1, max((len(t) for t in tables), default=1))
             table = np.full((I, width), -1, dtype=np.int32)
             for i, row in enumerate(tables):
                 table[i, :len(row)] = row
@@ -90,7 +103,8 @@ class StepContext:
             parts += [table.reshape(-1), slot_of.astype(np.int32)]
             shapes.append((page_size, width))
         flat = np.concatenate(parts) if parts else np.zeros(0, np.int32)
-        dev = ring.stage(flat, runtime.device)
+        dev = ring.stage(flat, runtime.device, out)
+        self.staged_ints = flat.size
         cut = 0
 
         def take(n):
@@ -147,7 +161,7 @@ class StepContext:
             row0 = ((np.arange(int(counts.sum())) - np.repeat(first, counts)) * per_tile)
             tokens = np.concatenate([np.arange(self.h_qstart[i], self.h_qstart[i] + self.h_qlen[i],
                                                dtype=np.int32) for i in members])
-            longest = int((self.h_pos0[members] + self.h_qlen[members]).max())
+            longest = self.fixed_context or int((self.h_pos0[members] + self.h_qlen[members]).max())
             layout.append((c, item.size, tokens.size, longest))
             host += [item, row0.astype(np.int32), tokens]
         dev = self._ring.stage(np.concatenate(host), self.runtime.device)

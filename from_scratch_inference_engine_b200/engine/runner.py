@@ -37,9 +37,62 @@ class DeviceFault(RuntimeError):
     """A kernel met an input it had to refuse (token id or position out of range)."""
 
 
+DECODE_BATCHES = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+TABLE_STEP = 64          # block tables of captured steps grow in steps of this many pages
+
+
+class _DecodeGraph:
+    """One decode step (a single token per request) of a fixed batch size and block-table
+    width, captured in a CUDA graph.  Its inputs live in one fixed int32 device buffer that
+    every step refills with one copy from pinned host memory; requests fewer than the batch
+    size are padded with entries that store nothing and see no key."""
+
+    def __init__(self, runner: "ModelRunner", batch: int, width: int):
+        self.runner, self.batch, self.width = runner, batch, width
+        groups = len(runner.cache.groups)
+        ints = 6 * batch + groups * (batch * width + batch)
+        device = runner.runtime.device
+        self.buffer = torch.zeros(ints, dtype=torch.int32, device=device)
+        self.rows = torch.arange(batch, dtype=torch.int32, device=device)
+        # scratch of its own: the graph holds raw addresses, so what it uses must never be
+        # freed or regrown by later steps
+        self.scratch: Dict[str, torch.Tensor] = {}
+        self.context = self.fill([], [], [], [[] for _ in range(groups)])
+        # one plain run first: libraries initialise, tile lists and scratch get allocated
+        stream = torch.cuda.Stream(device=device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            runner.model.forward(self.context, runner.layer_caches, self.rows)
+        torch.cuda.current_stream().wait_stream(stream)
+        from ..kernels import ops
+        self.graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        with torch.cuda.graph(self.graph, pool=runner.graph_pool()):
+            self.logits = runner.model.forward(self.context, runner.layer_caches, self.rows)
+        self.launches = ops.launches - before
+
+    def fill(self, token_ids, pos0, slots, tables) -> StepContext:
+        """Write one step's inputs into the fixed buffer (padded to the batch size)."""
+        runner, pad = self.runner, self.batch - len(token_ids)
+        page = runner.cache.page_size
+        group_tables = [(page, list(t) + [[]] * pad) for t in tables]
+        return StepContext(runner.runtime, runner._ring, self.scratch, runner.error,
+                           list(token_ids) + [0] * pad, list(range(self.batch)),
+                           [1] * self.batch, list(pos0) + [0] * pad, list(slots) + [0] * pad,
+                           group_tables, table_width=self.width, out=self.buffer,
+                           max_context=self.width * page)
+
+    def replay(self) -> torch.Tensor:
+        from ..kernels import ops
+        self.graph.replay()
+        ops.launches += self.launches
+        return self.logits
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, runtime: Runtime, page_size: int = 16,
-                 num_pages=2048, max_requests: int = 256, enable_prefix_cache: bool = False):
+                 num_pages=2048, max_requests: int = 256, enable_prefix_cache: bool = False,
+                 cuda_graphs: bool = True):
         self.model, self.runtime = model, runtime
         needs = model.cache_needs()
         self.cache = CacheManager(needs, page_size, num_pages, max_requests, enable_prefix_cache)
@@ -68,6 +121,11 @@ class ModelRunner:
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
         self._ring = PinnedRing()
         self._scratch: Dict[str, torch.Tensor] = {}
+        # steps of single tokens replay a captured graph (not for mixers with state of their
+        # own, whose Python-side loops a graph would freeze)
+        self.cuda_graphs = cuda_graphs and all(s is None for s in self.states)
+        self._graphs: Dict[tuple, _DecodeGraph] = {}
+        self._graph_pool = None
         self.vocab_size = model.spec.vocab_size
         self.max_positions = runtime.max_positions     # length of the position tables
 
@@ -96,14 +154,51 @@ class ModelRunner:
                 if not 0 <= w < n:
                     raise IndexError(f"step: wanted place {w} outside the {n} tokens brought")
 
+    def graph_pool(self):
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
+
+    def _decode_step(self, entries: Sequence[StepEntry]):
+        """A step of single tokens through a captured graph: (whether it ran, logits)."""
+        cache = self.cache
+        count = len(entries)
+        batch = next((b for b in DECODE_BATCHES if b >= count), None)
+        if batch is None:
+            return False, None
+        blocks = max((len(t) for e in entries for t in e.handle.tables), default=1)
+        width = -(-max(blocks, 1) // TABLE_STEP) * TABLE_STEP
+        key = (batch, width)
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = self._graphs[key] = _DecodeGraph(self, batch, width)
+        graph.fill([e.tokens[0] for e in entries], [e.handle.length for e in entries],
+                   [e.handle.slot for e in entries],
+                   [[e.handle.tables[g] for e in entries] for g in range(len(cache.groups))])
+        logits = graph.replay()
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if not wanted:
+            return True, None
+        if wanted == list(range(len(wanted))):
+            return True, logits[:len(wanted)]
+        index = torch.tensor(wanted, dtype=torch.long, device=self.runtime.device)
+        return True, logits.index_select(0, index)
+
     # --------------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits [wanted places, vocab] in the order of the
-        entries and of their `want`, or None when nothing is wanted."""
+        entries and of their `want`, or None when nothing is wanted.  The returned tensor
+        may be reused by the next step: read it before stepping again."""
         self._validate(entries)
         cache = self.cache
         for entry in entries:
             cache.reserve(entry.handle, len(entry.tokens))
+        if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
+            ran, logits = self._decode_step(entries)
+            if ran:
+                for entry in entries:
+                    cache.commit(entry.handle, 1)
+                return logits
         token_ids: List[int] = []
         q_start, q_len, pos0, slots, want_rows = [], [], [], [], []
         fresh_slots = []
