@@ -129,28 +129,44 @@ attn_mma_kernel(const AttnParams p) {
     }
     cp_async_commit();
 
-    auto load_tile = [&](int stage, int k0) {
+    // Element offset of every key row of a tile inside the pages (-1: not to be read), worked
+    // out one loop iteration before the tile is fetched, so that the fetch itself is a
+    // shared-memory read and two 16-byte copies per thread and pass, all coalesced.
+    __shared__ long long key_base[STAGES][BN];
+    auto find_rows = [&](int stage, int k0) {
+        if (tid < BN) {
+            const int kj = k0 + tid;
+            long long base = -1;
+            if (kj < kend) {
+                const int block = kj / p.page_size;
+                const int page = bt[block];
+                if (page >= 0)
+                    base = (long long)page * p.page_stride +
+                           ((long long)kvh * p.page_size + (kj - block * p.page_size)) * HD;
+            }
+            key_base[stage][tid] = base;
+        }
+    };
+    auto load_tile = [&](int stage) {
         bf16* kd = Ks + (size_t)stage * BN * LDS;
         bf16* vd = Vs + (size_t)stage * BN * LDS;
+#pragma unroll 4
         for (int e = tid; e < BN * CHUNKS; e += THREADS) {
             const int j = e / CHUNKS, c = e - j * CHUNKS;
-            const int kj = k0 + j;
-            long long base = 0;
-            bool ok = kj < kend;
-            if (ok) {
-                const int page = bt[kj / p.page_size];
-                ok = page >= 0;
-                if (ok) base = (long long)page * p.page_stride +
-                               ((long long)kvh * p.page_size + kj % p.page_size) * HD + c * 8;
-            }
-            cp_async16(kd + j * LDS + c * 8, kp + base, ok);
-            cp_async16(vd + j * LDS + c * 8, vp + base, ok);
+            const long long base = key_base[stage][j];
+            const bool ok = base >= 0;
+            const long long src = (ok ? base : 0) + c * 8;
+            cp_async16(kd + j * LDS + c * 8, kp + src, ok);
+            cp_async16(vd + j * LDS + c * 8, vp + src, ok);
         }
     };
 
 #pragma unroll
+    for (int s = 0; s < STAGES; ++s) find_rows(s, kbegin + s * BN);
+    __syncthreads();
+#pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < ntiles) load_tile(s, kbegin + s * BN);
+        if (s < ntiles) load_tile(s);
         cp_async_commit();
     }
 
@@ -172,8 +188,9 @@ attn_mma_kernel(const AttnParams p) {
     for (int i = 0; i < ntiles; ++i) {
         cp_async_wait<STAGES - 2>();
         __syncthreads();
-        if (i + STAGES - 1 < ntiles) load_tile((i + STAGES - 1) % STAGES, kbegin + (i + STAGES - 1) * BN);
+        if (i + STAGES - 1 < ntiles) load_tile((i + STAGES - 1) % STAGES);
         cp_async_commit();
+        if (i + STAGES < ntiles) find_rows(i % STAGES, kbegin + (i + STAGES) * BN);   // read next round
         if (Q_IN_REGS && i == 0) {
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qf[ks], q_ld_addr + ks * 16);
@@ -337,29 +354,35 @@ attn_mma_kernel(const AttnParams p) {
     }
 }
 
-// Merge the key splits of one (token, head); same arithmetic as attention_generic.cu.
+// Merge the key splits of one (token, head); same arithmetic as attention_generic.cu.  The
+// weight e^(m_z - M) of split z is computed once by lane z (nsplit <= 32) and broadcast.
 __global__ void attn_mma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                         bf16* __restrict__ out, int out_ld, int tokens, int heads,
                                         int nsplit, const int* __restrict__ token_list) {
     const int tok = token_list ? token_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
-    float mmax = -INFINITY;
-    for (int z = 0; z < nsplit; ++z)
-        mmax = fmaxf(mmax, part_ml[(((size_t)z * tokens + tok) * heads + h) * 2]);
-    float denom = 0.f;
-    for (int z = 0; z < nsplit; ++z) {
-        const size_t idx = ((size_t)z * tokens + tok) * heads + h;
-        const float mz = part_ml[idx * 2];
-        if (mz != -INFINITY) denom += part_ml[idx * 2 + 1] * __expf(mz - mmax);
+    const int lane = threadIdx.x & 31;
+    const size_t stride = (size_t)tokens * heads;              // (token, head) slots per split
+    const size_t slot = (size_t)tok * heads + h;
+    float mz = -INFINITY, lz = 0.f;
+    if (lane < nsplit) {
+        mz = part_ml[(lane * stride + slot) * 2];
+        lz = part_ml[(lane * stride + slot) * 2 + 1];
     }
+    const float mmax = warp_max(mz);
+    const float wz = mz == -INFINITY ? 0.f : __expf(mz - mmax);
+    const float denom = warp_sum(lz * wz);
     const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float acc = 0.f;
+    for (int d = threadIdx.x * 2; d < HD; d += blockDim.x * 2) {
+        float a0 = 0.f, a1 = 0.f;
         for (int z = 0; z < nsplit; ++z) {
-            const size_t idx = ((size_t)z * tokens + tok) * heads + h;
-            const float mz = part_ml[idx * 2];
-            if (mz != -INFINITY) acc += part_o[idx * HD + d] * __expf(mz - mmax);
+            const float w = __shfl_sync(0xffffffffu, wz, z);
+            if (w != 0.f) {
+                const float2 v = *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d);
+                a0 += v.x * w; a1 += v.y * w;
+            }
         }
-        out[(size_t)tok * out_ld + h * HD + d] = __float2bfloat16_rn(acc * inv);
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * out_ld + h * HD + d) =
+            __floats2bfloat162_rn(a0 * inv, a1 * inv);
     }
 }
 
@@ -423,7 +446,8 @@ int fsie_attn_mma(int row_class, const void* q, int q_ld, const void* k_pages, c
     const int count = combine_tokens ? num_combine : tokens;
     if (count <= 0) return 0;
     dim3 cgrid(count, heads);
-    attn_mma_combine_kernel<<<cgrid, HD >= 128 ? 128 : 64, 0, stream>>>(
+    if (nsplit > 32) return ERR_BAD_ARGUMENT;
+    attn_mma_combine_kernel<<<cgrid, HD >= 128 ? 64 : 32, 0, stream>>>(
         part_o, part_ml, (bf16*)out, out_ld, tokens, heads, nsplit, combine_tokens);
     return (int)cudaGetLastError();
 }

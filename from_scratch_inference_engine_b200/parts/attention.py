@@ -90,17 +90,29 @@ class GqaAttention(Mixer):
         group_size = self.num_heads // self.num_kv_heads
         sms = ctx.runtime.sm_count
 
-        def splits(blocks: int, longest: int) -> int:
-            if blocks >= sms:
+        def splits(blocks: int, longest: int, even_work: bool = False) -> int:
+            """Into how many key ranges to split each tile: the count (each range at least
+            128 keys, at most 32 ranges) that fills the GPU's block slots most evenly.  Tiles
+            of decoded tokens all have about the same work, so evening out the last wave
+            pays up to a few waves; tiles of a prompt do not, and are split only when there
+            are fewer of them than slots."""
+            slots = 2 * sms                       # two attention blocks fit on an SM
+            if blocks >= (4 * slots if even_work else slots):
                 return 1
-            return max(1, min(-(-2 * sms // blocks), longest // 128, 32))
+            best, best_fill = 1, 0.0
+            for n in range(1, max(1, min(32, longest // 128)) + 1):
+                total = blocks * n
+                fill = total / (-(-total // slots) * slots)
+                if fill > best_fill + 0.02:
+                    best, best_fill = n, fill
+            return best
 
         common = (cache.k_pages, cache.v_pages, cache.page_stride, group.page_size,
                   group.block_tables)
         if qkv.dtype is torch.bfloat16 and self.head_dim % 16 == 0:
             for row_class, tiles, class_tokens, count, longest in \
                     ctx.attention_row_classes(group_size, ops.ATTENTION_ROW_CLASSES):
-                nsplit = splits(tiles.count * self.num_kv_heads, longest)
+                nsplit = splits(tiles.count * self.num_kv_heads, longest, row_class == 0)
                 part_o = part_ml = None
                 if nsplit > 1:
                     part_o = ctx.scratch("attention.part_o", nsplit * tokens * self.q_width)
