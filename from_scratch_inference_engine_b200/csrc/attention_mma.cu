@@ -220,18 +220,31 @@ attn_mma_kernel(const AttnParams p) {
                 mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
             }
         }
-        // ---- mask, running maximum
+        // ---- mask (only where some key of this warp's range is hidden from some row), maximum
         float mx_lo = -INFINITY, mx_hi = -INFINITY;
+        const int k_last = k0 + KPW - 1;
+        // rows beyond the tile's count are never written: they do not force the masked path
+        const int see_lo = r_lo < nrows ? pos_lo : 0x7fffffff, see_hi = r_hi < nrows ? pos_hi : 0x7fffffff;
+        const bool clear = k_last < kend && k_last <= min(see_lo, see_hi) &&
+                           k0 > max(lowest_lo, lowest_hi);
+        if (__all_sync(0xffffffffu, clear)) {
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
+            for (int n = 0; n < NT; ++n) {
+                mx_lo = fmaxf(mx_lo, fmaxf(s[n][0], s[n][1]));
+                mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
+            }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = k0 + n * 8 + 2 * t + e;
-                const bool in = key < kend;
-                if (!(in && key <= pos_lo && key > lowest_lo)) s[n][e] = -INFINITY;
-                if (!(in && key <= pos_hi && key > lowest_hi)) s[n][2 + e] = -INFINITY;
-                mx_lo = fmaxf(mx_lo, s[n][e]);
-                mx_hi = fmaxf(mx_hi, s[n][2 + e]);
+            for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = k0 + n * 8 + 2 * t + e;
+                    const bool in = key < kend;
+                    if (!(in && key <= pos_lo && key > lowest_lo)) s[n][e] = -INFINITY;
+                    if (!(in && key <= pos_hi && key > lowest_hi)) s[n][2 + e] = -INFINITY;
+                    mx_lo = fmaxf(mx_lo, s[n][e]);
+                    mx_hi = fmaxf(mx_hi, s[n][2 + e]);
+                }
             }
         }
         mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
@@ -253,9 +266,11 @@ attn_mma_kernel(const AttnParams p) {
         }
         l_lo = l_lo * corr_lo + sum_lo;          // per-thread partial; the quad is summed at the end
         l_hi = l_hi * corr_hi + sum_hi;
+        if (__any_sync(0xffffffffu, corr_lo != 1.f || corr_hi != 1.f)) {
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) {
-            o[n][0] *= corr_lo; o[n][1] *= corr_lo; o[n][2] *= corr_hi; o[n][3] *= corr_hi;
+            for (int n = 0; n < HD / 8; ++n) {
+                o[n][0] *= corr_lo; o[n][1] *= corr_lo; o[n][2] *= corr_hi; o[n][3] *= corr_hi;
+            }
         }
         // ---- O += P V
 #pragma unroll
