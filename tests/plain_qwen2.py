@@ -73,7 +73,7 @@ def read_safetensors(path, dtype=torch.float64):
 # ------------------------------------------------------------------------------- parts
 def embedding(weight, ids):
     """Row copy, src/model/nn.cpp:90-108."""
-    return weight[torch.as_tensor(ids, dtype=torch.long)]
+    return weight[torch.as_tensor(ids, dtype=torch.long, device=weight.device)]
 
 
 def rms_norm(x, weight, eps):
@@ -96,7 +96,8 @@ def rope(x, n_heads, head_dim, theta, positions):
     inv_freq = torch.tensor([theta ** (-2.0 * i / head_dim) for i in range(half)],
                             dtype=torch.float64)
     ang = torch.as_tensor(positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
-    c, sn = torch.cos(ang).to(x.dtype)[:, None, :], torch.sin(ang).to(x.dtype)[:, None, :]
+    c = torch.cos(ang).to(dtype=x.dtype, device=x.device)[:, None, :]
+    sn = torch.sin(ang).to(dtype=x.dtype, device=x.device)[:, None, :]
     xh = x.reshape(s, n_heads, head_dim)
     x1, x2 = xh[..., :half], xh[..., half:]
     return torch.cat([x1 * c - x2 * sn, x2 * c + x1 * sn], dim=-1).reshape(s, n_heads * head_dim)
