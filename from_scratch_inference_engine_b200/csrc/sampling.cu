@@ -14,6 +14,7 @@
 // u in [0,1) comes from the host, one per row, so a request's draws do not depend on
 // what else is in the batch.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <math.h>
 
 namespace fsie {
@@ -264,6 +265,238 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     if (threadIdx.x == 0) out[rix] = choice < 0 ? 0 : choice;
 }
 
+// ------------------------------------------------------------------ cluster version
+// The same choice with a cluster of CLUSTER blocks per row (thread-block clusters,
+// distributed shared memory).  Each block keeps its slice of the row in shared memory as
+// (order key, weight) pairs, computed once, so the 32 rounds of a search read shared
+// memory only; the blocks' partial sums meet through distributed shared memory, summed in
+// rank order (the same bits on every run).  Rows then take microseconds per round instead
+// of a pass over global memory by a single block.
+namespace cg = cooperative_groups;
+constexpr int CLUSTER = 8;
+
+struct ClusterRow {
+    const unsigned* keys; const float* w; int count;    // this block's slice
+    int first;                                           // index of its first element in the row
+    unsigned kept_key, kept_ties;
+    float* slots;                                        // [2][4] exchange area of this block
+    int parity;
+};
+
+// sum over the cluster in rank order; every block gets the same bits
+__device__ float cluster_sum(cg::cluster_group& cluster, ClusterRow& r, float v, float* scratch) {
+    v = block_sum(v, scratch);
+    float* mine = r.slots + r.parity * 4;
+    if (threadIdx.x == 0) mine[0] = v;
+    cluster.sync();
+    float total = 0.f;
+    for (int rank = 0; rank < CLUSTER; ++rank)
+        total += (cluster.map_shared_rank(r.slots, rank) + r.parity * 4)[0];
+    r.parity ^= 1;
+    return total;
+}
+
+// three sums at once (one block reduction, one exchange); `wide` holds 96 floats
+__device__ void cluster_sum3(cg::cluster_group& cluster, ClusterRow& r, float (&v)[3], float* wide) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) v[j] = warp_sum(v[j]);
+    __syncthreads();
+    if (lane == 0) { wide[warp * 3] = v[0]; wide[warp * 3 + 1] = v[1]; wide[warp * 3 + 2] = v[2]; }
+    __syncthreads();
+    float* mine = r.slots + r.parity * 4;
+    if (threadIdx.x < 3) {
+        float total = 0.f;
+        for (int w = 0; w < warps; ++w) total += wide[w * 3 + threadIdx.x];
+        mine[threadIdx.x] = total;
+    }
+    cluster.sync();
+    v[0] = v[1] = v[2] = 0.f;
+    for (int rank = 0; rank < CLUSTER; ++rank) {
+        const float* theirs = cluster.map_shared_rank(r.slots, rank) + r.parity * 4;
+        v[0] += theirs[0]; v[1] += theirs[1]; v[2] += theirs[2];
+    }
+    r.parity ^= 1;
+}
+
+struct Found { unsigned key; float above; float w; float count; };
+
+// as locate() above, over the cluster's shared-memory copy of the row
+__device__ Found cluster_locate(cg::cluster_group& cluster, ClusterRow& r, float target, float* scratch,
+                               float* wide) {
+    // two key bits per round: the weights at or above the three candidates prefix + {1,2,3} * 2^lo
+    unsigned prefix = 0;
+    for (int lo = 30; lo >= 0; lo -= 2) {
+        const unsigned c1 = prefix | (1u << lo), c2 = prefix | (2u << lo), c3 = prefix | (3u << lo);
+        float m[3] = {0.f, 0.f, 0.f};
+        if (c3 > r.kept_key && target != INFINITY) {
+            for (int i = threadIdx.x; i < r.count; i += blockDim.x) {
+                const unsigned key = r.keys[i];
+                const float wi = r.w[i];
+                if (key >= c1) m[0] += wi;
+                if (key >= c2) m[1] += wi;
+                if (key >= c3) m[2] += wi;
+            }
+            cluster_sum3(cluster, r, m, wide);
+        }
+        const bool inf = target == INFINITY;
+        const bool r1 = c1 <= r.kept_key || (!inf && m[0] >= target && m[0] > 0.f);
+        const bool r2 = c2 <= r.kept_key || (!inf && m[1] >= target && m[1] > 0.f);
+        const bool r3 = c3 <= r.kept_key || (!inf && m[2] >= target && m[2] > 0.f);
+        if (r3) prefix = c3; else if (r2) prefix = c2; else if (r1) prefix = c1;
+    }
+    float v[3] = {0.f, 0.f, 0.f};      // weight above, tokens at the key, weight of one of them
+    float w_at = 0.f;
+    for (int i = threadIdx.x; i < r.count; i += blockDim.x) {
+        const unsigned key = r.keys[i];
+        if (key > prefix) v[0] += r.w[i];
+        else if (key == prefix) { v[1] += 1.f; w_at = r.w[i]; }
+    }
+    v[2] = block_max(w_at, scratch);   // equal keys have equal weights: max picks it
+    // max over the cluster through the same exchange: send it as a sum of one-hot parts
+    float* mine = r.slots + r.parity * 4;
+    v[0] = block_sum(v[0], scratch);
+    v[1] = block_sum(v[1], scratch);
+    if (threadIdx.x == 0) { mine[0] = v[0]; mine[1] = v[1]; mine[2] = v[2]; }
+    cluster.sync();
+    Found out;
+    out.key = prefix; out.above = 0.f; out.count = 0.f; out.w = 0.f;
+    for (int rank = 0; rank < CLUSTER; ++rank) {
+        const float* theirs = cluster.map_shared_rank(r.slots, rank) + r.parity * 4;
+        out.above += theirs[0]; out.count += theirs[1]; out.w = fmaxf(out.w, theirs[2]);
+    }
+    r.parity ^= 1;
+    if (prefix == r.kept_key && (float)r.kept_ties < out.count) out.count = (float)r.kept_ties;
+    return out;
+}
+
+__device__ __forceinline__ unsigned cluster_ties_needed(const Found& at, float target) {
+    if (at.count <= 1.f || !(at.w > 0.f)) return 1;
+    const float n = ceilf((target - at.above) / at.w);
+    if (!(n >= 1.f)) return 1;
+    return n >= at.count ? (unsigned)at.count : (unsigned)n;
+}
+
+__global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(SAMPLE_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int vocab, int slice,
+                      const float* __restrict__ temperature, const int* __restrict__ top_k,
+                      const float* __restrict__ top_p, const float* __restrict__ uniform,
+                      int* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char sample_smem[];
+    __shared__ float scratch[32];
+    __shared__ float wide[96];
+    __shared__ float slots[2 * 4];
+    __shared__ unsigned counts[SAMPLE_THREADS];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int rix = blockIdx.y;
+    const float temp = temperature[rix];
+    if (!(temp > 0.f)) {                         // uniform over the cluster: no sync is skipped
+        if (rank == 0 && threadIdx.x == 0) out[rix] = -1;
+        return;
+    }
+    unsigned* keys = reinterpret_cast<unsigned*>(sample_smem);
+    float* w = reinterpret_cast<float*>(sample_smem) + slice;
+    ClusterRow r;
+    r.first = rank * slice;
+    r.count = max(0, min(slice, vocab - r.first));
+    r.keys = keys; r.w = w; r.slots = slots; r.parity = 0;
+    const float* row = logits + (size_t)rix * vocab + r.first;
+    const float inv_temp = 1.0f / temp;
+
+    // ---- the row's maximum, then this block's (key, weight) pairs
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < r.count; i += blockDim.x) mx = fmaxf(mx, row[i]);
+    mx = block_max(mx, scratch);
+    if (threadIdx.x == 0) slots[0] = mx;
+    cluster.sync();
+    float maxl = -INFINITY;
+    for (int q = 0; q < CLUSTER; ++q) maxl = fmaxf(maxl, cluster.map_shared_rank(slots, q)[0]);
+    cluster.sync();                              // everyone has read slot 0 before it is reused
+    for (int i = threadIdx.x; i < r.count; i += blockDim.x) {
+        const float v = row[i];
+        keys[i] = order_key(v);
+        w[i] = expf((v - maxl) * inv_temp);
+    }
+    __syncthreads();
+
+    // ---- top-k: key of the k-th largest logit, and how many of its ties are kept
+    r.kept_key = 0; r.kept_ties = 0xffffffffu;
+    const int k = top_k[rix];
+    if (k > 0 && k < vocab) {
+        unsigned prefix = 0;                             // largest key with count(key >= it) >= k
+        for (int lo = 30; lo >= 0; lo -= 2) {
+            const unsigned c1 = prefix | (1u << lo), c2 = prefix | (2u << lo), c3 = prefix | (3u << lo);
+            float c[3] = {0.f, 0.f, 0.f};                // counts up to 2^24 are exact in float
+            for (int i = threadIdx.x; i < r.count; i += blockDim.x) {
+                const unsigned key = keys[i];
+                c[0] += key >= c1 ? 1.f : 0.f; c[1] += key >= c2 ? 1.f : 0.f; c[2] += key >= c3 ? 1.f : 0.f;
+            }
+            cluster_sum3(cluster, r, c, wide);
+            if (c[2] >= (float)k) prefix = c3; else if (c[1] >= (float)k) prefix = c2;
+            else if (c[0] >= (float)k) prefix = c1;
+        }
+        float above = 0.f;
+        for (int i = threadIdx.x; i < r.count; i += blockDim.x) above += keys[i] > prefix ? 1.f : 0.f;
+        above = cluster_sum(cluster, r, above, scratch);
+        r.kept_key = prefix;
+        r.kept_ties = (unsigned)k - (unsigned)above;
+    }
+    const Found whole = cluster_locate(cluster, r, INFINITY, scratch, wide);
+    const float total = whole.above + whole.count * whole.w;
+    float nucleus = total;
+    const float pp = top_p[rix];
+    if (pp < 1.0f) {
+        const float target = pp * total;
+        const Found at = cluster_locate(cluster, r, target, scratch, wide);
+        nucleus = at.above + (float)cluster_ties_needed(at, target) * at.w;
+    }
+    const float target = uniform[rix] * nucleus;
+    const Found at = cluster_locate(cluster, r, target, scratch, wide);
+    unsigned n = cluster_ties_needed(at, target);
+
+    // ---- the n-th token (by ascending index) whose key equals at.key: which block holds it?
+    float mine[3] = {0.f, 0.f, 0.f};
+    for (int i = threadIdx.x; i < r.count; i += blockDim.x) mine[0] += keys[i] == at.key ? 1.f : 0.f;
+    mine[0] = block_sum(mine[0], scratch);
+    float* slot = r.slots + r.parity * 4;
+    if (threadIdx.x == 0) slot[0] = mine[0];
+    cluster.sync();
+    unsigned before = 0, here = 0, all = 0;
+    for (int q = 0; q < CLUSTER; ++q) {
+        const unsigned c = (unsigned)(cluster.map_shared_rank(r.slots, q) + r.parity * 4)[0];
+        if (q < rank) before += c;
+        if (q == rank) here = c;
+        all += c;
+    }
+    if (n > all) n = all;
+    if (all == 0 && rank == 0 && threadIdx.x == 0) out[rix] = 0;
+    if (n > before && n <= before + here) {       // this block owns the answer
+        const unsigned local = n - before;
+        const int per = (r.count + blockDim.x - 1) / blockDim.x;
+        const int begin = threadIdx.x * per, end = min(r.count, begin + per);
+        unsigned cnt = 0;
+        for (int i = begin; i < end; ++i) cnt += keys[i] == at.key;
+        counts[threadIdx.x] = cnt;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned run = 0;
+            int found = -1;
+            for (int t = 0; t < (int)blockDim.x && found < 0; ++t) {
+                if (run + counts[t] >= local) {
+                    const int b = t * per, e = min(r.count, b + per);
+                    for (int i = b; i < e; ++i)
+                        if (keys[i] == at.key && ++run == local) { found = i; break; }
+                } else {
+                    run += counts[t];
+                }
+            }
+            out[rix] = found < 0 ? 0 : r.first + found;
+        }
+    }
+    cluster.sync();                               // no block leaves while its slots may be read
+}
+
 }  // namespace fsie
 
 extern "C" {
@@ -293,6 +526,21 @@ int fsie_sample(const float* logits, int rows, int vocab, const float* temperatu
                 cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return fsie::ERR_BAD_ARGUMENT;
+    // a cluster of 8 blocks per row while a slice of the row fits in shared memory
+    const int slice = ((vocab + fsie::CLUSTER - 1) / fsie::CLUSTER + 3) / 4 * 4;
+    const size_t smem = (size_t)slice * 8;
+    if (vocab >= 4096 && smem <= 200 * 1024 && rows <= 65535) {
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(fsie::sample_cluster_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        fsie::sample_cluster_kernel<<<dim3(fsie::CLUSTER, rows), fsie::SAMPLE_THREADS, smem, stream>>>(
+            logits, vocab, slice, temperature, top_k, top_p, uniform, out);
+        return FSIE_LAUNCH_CHECK();
+    }
     fsie::sample_kernel<<<rows, fsie::SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, top_k,
                                                                   top_p, uniform, out);
     return FSIE_LAUNCH_CHECK();
