@@ -303,6 +303,77 @@ def attention_mma(row_class: int, q: torch.Tensor, q_ld: int, k_pages: torch.Ten
     return out
 
 
+# ------------------------------------------------- tcgen05 product for few tokens
+_gemm_decode = None
+
+
+def gemm_decode_lib():
+    global _gemm_decode
+    if _gemm_decode is None:
+        lib = build.load_library("gemm_decode")
+        i, ll, p = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_tensor_map_bytes.argtypes = []
+        lib.fsie_gemm_decode_weight_map.argtypes = [p, p, ll, ll, i]
+        lib.fsie_gemm_decode.argtypes = [p, p, i, p, i, p, i, i, i, i, i, i, p, p]
+        for name in ("fsie_tensor_map_bytes", "fsie_gemm_decode_weight_map", "fsie_gemm_decode"):
+            getattr(lib, name).restype = i
+        _gemm_decode = lib
+    return _gemm_decode
+
+
+GEMM_DECODE_MAX_TOKENS = 64
+
+
+class DecodeWeight:
+    """A bfloat16 weight [rows, K] prepared for `gemm_decode`: its TMA descriptor.
+    For SwiGLU the weight holds the gate rows and then as many up rows."""
+
+    def __init__(self, weight: torch.Tensor, swiglu: bool = False):
+        _need(weight, torch.bfloat16, "weight")
+        rows, k = weight.shape
+        if k % 8:
+            raise KernelError("gemm_decode: K must be a multiple of 8")
+        if swiglu and rows % 2:
+            raise KernelError("gemm_decode: a SwiGLU weight holds gate rows and as many up rows")
+        lib = gemm_decode_lib()
+        self.weight, self.swiglu, self.k = weight, swiglu, k
+        self.n = rows // 2 if swiglu else rows
+        self.map = ctypes.create_string_buffer(lib.fsie_tensor_map_bytes() + 64)
+        offset = (-ctypes.addressof(self.map)) % 64
+        self.map_ptr = ctypes.c_void_p(ctypes.addressof(self.map) + offset)
+        _check(lib.fsie_gemm_decode_weight_map(self.map_ptr, _ptr(weight), rows, k,
+                                               64 if swiglu else 128), "gemm_decode weight map")
+
+
+def gemm_decode_splits(tiles: int, k: int, sm_count: int) -> int:
+    """Blocks of a cluster that share the k range of one tile: enough to occupy the GPU."""
+    splits = 1
+    while splits < 8 and tiles * splits < sm_count and (k // 64) // (splits * 2) >= 4:
+        splits *= 2
+    return splits
+
+
+def gemm_decode(weight: DecodeWeight, x: torch.Tensor, out: torch.Tensor,
+                bias: Optional[torch.Tensor], error: torch.Tensor, splits: int = 1) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ w.T (+ bias), or silu(x @ gate.T) * (x @ up.T); T <= 64; out is
+    bfloat16 or float32."""
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(out, None, "out")
+    tokens, k = x.shape
+    if k != weight.k or x.stride(1) != 1 or tokens > GEMM_DECODE_MAX_TOKENS:
+        raise KernelError("gemm_decode: x does not fit the weight (or more than 64 tokens)")
+    if out.shape[0] < tokens or out.shape[1] != weight.n or out.dtype not in (torch.bfloat16,
+                                                                            torch.float32):
+        raise KernelError("gemm_decode: out does not fit")
+    if bias is not None:
+        _need(bias, torch.bfloat16, "bias")
+    _check(gemm_decode_lib().fsie_gemm_decode(
+        weight.map_ptr, _ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(bias), tokens,
+        weight.n, k, int(weight.swiglu), int(out.dtype is torch.float32), splits, _ptr(error),
+        _stream()), "gemm_decode")
+    return out
+
+
 # --------------------------------------------------------------------------- sampling
 ARGMAX_PARTS = 32      # blocks per row of the two-stage argmax
 

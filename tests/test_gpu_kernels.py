@@ -403,3 +403,40 @@ def test_sample_frequencies(ops):
                dev(torch.ones(2000)), dev(u), out)
     counts = torch.bincount(out.cpu().long(), minlength=3).tolist()
     assert abs(counts[1] - 1400) < 90 and abs(counts[0] - 400) < 70 and abs(counts[2] - 200) < 55
+
+
+# -------------------------------------------------------- tcgen05 product for few tokens
+@pytest.mark.parametrize("tokens", [1, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("n,k,splits", [(384, 512, 1), (200, 136, 1), (256, 1024, 2), (128, 2048, 8),
+                                        (3584, 3584, 4)])
+def test_gemm_decode_tcgen05(ops, tokens, n, k, splits):
+    torch.manual_seed(tokens + n)
+    x = dev(torch.randn(tokens, k), torch.bfloat16)
+    w = dev(torch.randn(n, k) / math.sqrt(k), torch.bfloat16)
+    bias = dev(torch.randn(n), torch.bfloat16)
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want = x.double() @ w.double().T
+    weight = ops.DecodeWeight(w)
+    out = torch.full((tokens, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_decode(weight, x, out, None, error, splits)
+    assert error.item() == 0
+    assert (out.double() - want).abs().max().item() < 1.6e-2 * want.abs().max().item()
+    out32 = torch.full((tokens, n), float("nan"), dtype=torch.float32, device="cuda")
+    ops.gemm_decode(weight, x, out32, bias, error, splits)
+    assert error.item() == 0
+    assert (out32.double() - want - bias.double()).abs().max().item() < 2e-3 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("tokens,inter,k,splits", [(8, 320, 512, 1), (3, 100, 264, 1), (64, 192, 1024, 4),
+                                                   (8, 18944, 3584, 1)])
+def test_gemm_decode_swiglu_epilogue(ops, tokens, inter, k, splits):
+    torch.manual_seed(inter)
+    x = dev(torch.randn(tokens, k), torch.bfloat16)
+    w = dev(torch.randn(2 * inter, k) / math.sqrt(k), torch.bfloat16)
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gate_up = (x.double() @ w.double().T).to(torch.bfloat16).double()      # rounded as the library path
+    want = plain.silu_mul(gate_up[:, :inter], gate_up[:, inter:])
+    out = torch.full((tokens, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_decode(ops.DecodeWeight(w, swiglu=True), x, out, None, error, splits)
+    assert error.item() == 0
+    assert (out.double() - want).abs().max().item() < 2.5e-2 * want.abs().max().item()
