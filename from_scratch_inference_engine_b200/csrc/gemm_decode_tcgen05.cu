@@ -96,7 +96,8 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 
 template <int TN> struct Layout {
-    static constexpr int STAGES = TN == 64 ? 6 : 8;
+    static constexpr int STAGES = 4;                             // ~72-97 KB: two or three blocks per SM overlap
+                                                                 // one block's epilogue with the others' streaming
     static constexpr uint32_t A_BYTES = BM * BK * 2;             // 16 KB
     static constexpr uint32_t B_BYTES = TN * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -126,11 +127,26 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
     const int n0 = EPI == EPI_SWIGLU ? tile * (BM / 2) : tile * BM;
 
+    auto load_stage = [&](int kb, int s) {
+        unsigned char* a = smem + s * L::STAGE_BYTES;
+        unsigned char* b = a + L::A_BYTES;
+        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+        if (EPI == EPI_SWIGLU) {                      // 64 gate rows, then the 64 up rows of the same outputs
+            tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
+            tma_load_2d(a + L::A_BYTES / 2, &map_w, kb * BK, p.up_row0 + n0, &full_bar[s]);
+        } else {
+            tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
+        }
+        tma_load_2d(b, &map_x, kb * BK, 0, &full_bar[s]);
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the producer fills the ring at once; tensor memory is allocated meanwhile
+        for (int it = 0; it < L::STAGES && kb0 + it < kb1; ++it) load_stage(kb0 + it, it);
     }
     if (warp == 1) {        // one warp allocates the accumulator's columns of tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)), "r"(L::TMEM_COLS) : "memory");
@@ -143,24 +159,16 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------ TMA producer
-        int issued = 0;
-        for (int kb = kb0; kb < kb1; ++kb) {
+        // (its first STAGES loads were issued before the block-wide barrier above)
+        int issued = min(kb1 - kb0, L::STAGES);
+        for (int kb = kb0 + L::STAGES; kb < kb1; ++kb) {
             const int it = kb - kb0, s = it % L::STAGES;
-            if (it >= L::STAGES && !mbar_wait(&empty_bar[s], ((it / L::STAGES) - 1) & 1)) {
+            if (!mbar_wait(&empty_bar[s], ((it / L::STAGES) - 1) & 1)) {
                 atomicExch(p.error, ERR_TMA_WAIT); atomicExch(&abort_flag, 1); break;
             }
             if (*(volatile int*)&abort_flag) break;
             issued = it + 1;
-            unsigned char* a = smem + s * L::STAGE_BYTES;
-            unsigned char* b = a + L::A_BYTES;
-            mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-            if (EPI == EPI_SWIGLU) {                      // 64 gate rows, then the 64 up rows of the same outputs
-                tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
-                tma_load_2d(a + L::A_BYTES / 2, &map_w, kb * BK, p.up_row0 + n0, &full_bar[s]);
-            } else {
-                tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
-            }
-            tma_load_2d(b, &map_x, kb * BK, 0, &full_bar[s]);
+            load_stage(kb, s);
         }
         if (*(volatile int*)&abort_flag) {
             // giving up: let the copies already issued land before the block's memory is released

@@ -32,20 +32,21 @@ class LoadedModel:
 
     @classmethod
     def from_pretrained(cls, model_dir, dtype="bfloat16", device="cuda:0",
-                        max_positions: int = 0) -> "LoadedModel":
+                        max_positions: int = 0, **runtime_options) -> "LoadedModel":
         """Read config.json (which names the architecture) and model.safetensors."""
         config = load_config(model_dir)
-        return cls.from_tensors(config, load_checkpoint(model_dir), dtype, device, max_positions)
+        return cls.from_tensors(config, load_checkpoint(model_dir), dtype, device, max_positions,
+                                **runtime_options)
 
     @classmethod
     def from_tensors(cls, config, tensors, dtype="bfloat16", device="cuda:0",
-                     max_positions: int = 0) -> "LoadedModel":
+                     max_positions: int = 0, **runtime_options) -> "LoadedModel":
         spec = config.build_spec()
         # positions the engine can encode: what the configuration names (the reference parses
         # max_position_embeddings and never enforces it, src/model/model_config.cpp:25) and
         # at least what the caller's cache will hold
         limit = max(spec.max_position, max_positions) or 32768
-        runtime = Runtime(device, parse_dtype(dtype), max_positions=limit)
+        runtime = Runtime(device, parse_dtype(dtype), max_positions=limit, **runtime_options)
         model = DecoderModel(spec)
         model.bind(tensors, runtime)
         return cls(config, model, runtime)

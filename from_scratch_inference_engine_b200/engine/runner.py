@@ -118,7 +118,7 @@ class ModelRunner:
                 cache.v_pages = pages[:, position, 1]
                 cache.page_stride = pages.stride(0)
             self.layer_caches.append(cache)
-        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        self.error = runtime.error
         self._ring = PinnedRing()
         self._scratch: Dict[str, torch.Tensor] = {}
         # steps of single tokens replay a captured graph (not for mixers with state of their
@@ -232,5 +232,8 @@ class ModelRunner:
         code = int(self.error.item())
         if code:
             self.error.zero_()
-            what = {1: "token id outside the vocabulary", 2: "position outside the table"}
+            what = {1: "token id outside the vocabulary", 2: "position outside the table",
+                    11: "matrix product: the copy engine's stage never became free",
+                    12: "matrix product: a tile never arrived", 13: "matrix product: the "
+                    "accumulator never completed"}
             raise DeviceFault(what.get(code, f"device error flag {code}"))

@@ -34,7 +34,8 @@ class Runtime:
     this package in both modes.
     """
 
-    def __init__(self, device="cuda:0", dtype=torch.bfloat16, max_positions: int = 0):
+    def __init__(self, device="cuda:0", dtype=torch.bfloat16, max_positions: int = 0,
+                 few_token_min_elements: int = 32 * 1024 * 1024):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this engine has no CPU path")
         self.device = torch.device(device)
@@ -43,6 +44,12 @@ class Runtime:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._tables: Dict[object, torch.Tensor] = {}
         self._f32_out: Optional[bool] = None
+        # device-side error flag that kernels set when they refuse an input or give up a wait
+        self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # weights prepared for the tcgen05 product of steps with few tokens, by storage address
+        self._few_token_weights: Dict[int, ops.DecodeWeight] = {}
+        self.few_token_limit = 16          # steps of up to this many tokens take that product
+        self.few_token_min_elements = few_token_min_elements   # ... for matrices at least this large
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -52,17 +59,55 @@ class Runtime:
             self._tables[key] = make().to(self.device).contiguous()
         return self._tables[key]
 
+    def prepare_weight(self, weight: torch.Tensor, swiglu: bool = False) -> None:
+        """Called by a part at bind for a matrix it will multiply activations with.  Large
+        bfloat16 matrices get a TMA descriptor for the tcgen05 product that steps of few
+        tokens use (the library product is kept where it measured faster: small matrices)."""
+        if self.dtype is not torch.bfloat16 or weight.dtype is not torch.bfloat16:
+            return
+        rows, k = weight.shape
+        if k % 8 or rows * k < self.few_token_min_elements or (swiglu and rows % 2):
+            return
+        self._few_token_weights[weight.data_ptr()] = ops.DecodeWeight(weight, swiglu)
+
+    def _few_tokens(self, x: torch.Tensor, weight: torch.Tensor) -> Optional["ops.DecodeWeight"]:
+        if x.shape[0] > self.few_token_limit or x.stride(0) % 8:
+            return None
+        return self._few_token_weights.get(weight.data_ptr())
+
+    def _few_token_product(self, prepared, x, bias, out_dtype) -> torch.Tensor:
+        out = torch.empty((x.shape[0], prepared.n), dtype=out_dtype, device=x.device)
+        tiles = -(-prepared.n // (64 if prepared.swiglu else 128))
+        splits = ops.gemm_decode_splits(tiles, prepared.k, self.sm_count)
+        return ops.gemm_decode(prepared, x, out, bias, self.error, splits)
+
     def linear(self, x: torch.Tensor, weight: torch.Tensor,
                bias: Optional[torch.Tensor]) -> torch.Tensor:
         """x @ weight.T (+ bias) in the compute dtype."""
         if self.dtype is torch.float32:
             return ops.gemm_f32(x, weight, bias)
+        prepared = self._few_tokens(x, weight)
+        if prepared is not None and not prepared.swiglu:
+            return self._few_token_product(prepared, x, bias, torch.bfloat16)
         return F.linear(x, weight, bias)
+
+    def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+        """silu(x @ gate.T) * (x @ up.T) for the stacked weight [gate rows; up rows]: one fused
+        kernel for steps of few tokens, else the library product and the SwiGLU kernel."""
+        prepared = self._few_tokens(x, gate_up) if self.dtype is torch.bfloat16 else None
+        if prepared is not None and prepared.swiglu:
+            return self._few_token_product(prepared, x, None, torch.bfloat16)
+        both = self.linear(x, gate_up, None) if prepared is None else F.linear(x, gate_up)
+        act = torch.empty((x.shape[0], gate_up.shape[0] // 2), dtype=both.dtype, device=x.device)
+        return ops.swiglu(both, act)
 
     def linear_f32_out(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         """x @ weight.T with a float32 result (the logits)."""
         if self.dtype is torch.float32:
             return ops.gemm_f32(x, weight, None)
+        prepared = self._few_tokens(x, weight)
+        if prepared is not None and not prepared.swiglu:
+            return self._few_token_product(prepared, x, None, torch.float32)
         if self._f32_out is None:
             try:
                 torch.mm(x[:1], weight[:8].t(), out_dtype=torch.float32)

@@ -185,6 +185,19 @@ def run(args):
             u = torch.rand(args.tokens, generator=g, device="cuda")
             ms = timer(lambda: ops.sample(logits, ones * 0.8, k, ones * args.top_p, u, out))
         nbytes, flops = args.tokens * args.vocab * 4, float(args.tokens * args.vocab)
+    elif args.kernel in ("gemm_decode", "gemm_decode_swiglu"):
+        m, n, k = args.tokens, args.n, args.k
+        swiglu = args.kernel == "gemm_decode_swiglu"
+        x, w = rand(m, k).to(dtype), rand(2 * n if swiglu else n, k).to(dtype)
+        weight = ops.DecodeWeight(w, swiglu=swiglu)
+        out = torch.empty((m, n), dtype=dtype, device="cuda")
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        tiles = -(-n // (64 if swiglu else 128))
+        splits = args.nsplit if args.nsplit > 0 else ops.gemm_decode_splits(tiles, k, sms)
+        ms = timer(lambda: ops.gemm_decode(weight, x, out, None, error, splits))
+        extra = {"splits": splits, "error": int(error.item())}
+        nbytes, flops = (m * k + w.shape[0] * k + m * n) * elem, 2.0 * m * w.shape[0] * k
     elif args.kernel in ("linear", "gemm_f32"):
         m, n, k = args.tokens, args.n, args.k
         if args.kernel == "linear":

@@ -63,6 +63,8 @@ class GqaAttention(Mixer):
         self.b_qkv = (torch.cat([tensors[p + f"{n}_proj.bias"] for n in "qkv"]).contiguous()
                       if self.qkv_bias else None)
         self.w_o = tensors[p + "o_proj.weight"].contiguous()
+        runtime.prepare_weight(self.w_qkv)
+        runtime.prepare_weight(self.w_o)
         self.position.bind(tensors, runtime)
 
     def forward(self, ctx, y: torch.Tensor, cache: LayerCache) -> torch.Tensor:

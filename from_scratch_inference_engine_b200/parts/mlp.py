@@ -34,11 +34,9 @@ class SwiGluMlp(Part):
         self.w_gate_up = torch.cat([tensors[p + "gate_proj.weight"],
                                     tensors[p + "up_proj.weight"]]).contiguous()
         self.w_down = tensors[p + "down_proj.weight"].contiguous()
+        runtime.prepare_weight(self.w_gate_up, swiglu=True)
+        runtime.prepare_weight(self.w_down)
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
         rt = self.runtime
-        gate_up = rt.linear(y, self.w_gate_up, None)
-        act = torch.empty((y.shape[0], self.intermediate_size), dtype=gate_up.dtype,
-                          device=y.device)
-        ops.swiglu(gate_up, act)
-        return rt.linear(act, self.w_down, None)
+        return rt.linear(rt.linear_swiglu(y, self.w_gate_up), self.w_down, None)

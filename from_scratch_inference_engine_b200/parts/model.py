@@ -66,6 +66,7 @@ class DecoderModel:
         self.embedding = placed[self.spec.embedding_name].contiguous()
         self.head = (placed[self.spec.head_name].contiguous()
                      if self.spec.head_name is not None else self.embedding)
+        runtime.prepare_weight(self.head)
         self.final_norm.bind(placed, runtime)
         for block in self.blocks:
             block.bind(placed, runtime)

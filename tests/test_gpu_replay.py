@@ -33,10 +33,11 @@ def requests_for(name):
             for key, n in REQUESTS[name].items()}
 
 
-def build_runner(folder, dtype, max_tokens, page_size):
+def build_runner(folder, dtype, max_tokens, page_size, **runtime_options):
     from from_scratch_inference_engine_b200.engine import LoadedModel, ModelRunner
     pages = -(-max_tokens // page_size)
-    model = LoadedModel.from_pretrained(folder, dtype=dtype, max_positions=pages * page_size)
+    model = LoadedModel.from_pretrained(folder, dtype=dtype, max_positions=pages * page_size,
+                                        **runtime_options)
     return ModelRunner(model.model, model.runtime, page_size=page_size, num_pages=pages,
                        max_requests=8)
 
@@ -99,3 +100,18 @@ def test_cutting_does_not_change_float32_beyond_rounding(folders):
     for other in results[1:]:
         for key, row in results[0].items():
             assert np.abs(row - other[key]).max() < 2e-5
+
+
+@pytest.mark.parametrize("family", ["tail", "mixed"])
+@pytest.mark.parametrize("name,page_size", [("B", 8), ("C", 16), ("D", 16)])
+def test_replay_with_the_few_token_product_on_every_matrix(folders, name, page_size, family):
+    """The tcgen05 product that steps of up to 16 tokens use is reserved for large matrices;
+    here it is forced onto the tiny models' matrices so that replay covers it too."""
+    requests = requests_for(name)
+    steps = FAMILIES[family](requests, 11)
+    need = helpers.live_tokens_needed(steps, round_to=page_size)
+    runner = build_runner(folders[name], "bfloat16", need, page_size, few_token_min_elements=0)
+    assert runner.runtime._few_token_weights
+    rows = helpers.run_trace_in_process(runner, steps)
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], TOLERANCE["bfloat16"])
+    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
