@@ -147,6 +147,14 @@ class CacheManager:
         want = self.blocks_for(handle.length + n_new)
         return [max(0, want - len(table)) for table in handle.tables]
 
+    def fits_in_held_pages(self, handle: RequestCache, n_new: int) -> bool:
+        """Whether `n_new` more tokens need no new page (the common case of a decode step)."""
+        want = (handle.length + n_new + self.page_size - 1) // self.page_size
+        for table in handle.tables:
+            if len(table) < want:
+                return False
+        return True
+
     def free_pages(self) -> List[int]:
         """Free pages per group, counting cached prefix pages nobody else holds."""
         free = [pool.num_free for pool in self.pools]
@@ -172,6 +180,8 @@ class CacheManager:
 
     # ------------------------------------------------------------ step protocol
     def reserve(self, handle: RequestCache, n_new: int) -> None:
+        if self.fits_in_held_pages(handle, n_new):
+            return
         needed = self.pages_needed(handle, n_new)
         if not all(n <= b for n, b in zip(needed, self.free_pages())):
             raise OutOfPages(f"request {handle.request_id!r} needs {needed} pages, "

@@ -86,9 +86,12 @@ class StepContext:
         self.h_slots = np.asarray(slots, dtype=np.int32)
         self.max_context = max_context or (int((self.h_pos0 + self.h_qlen).max()) if I else 0)
         self.fixed_context = max_context
-        positions = np.concatenate([np.arange(p, p + n, dtype=np.int32)
-                                    for p, n in zip(pos0, q_len)]) if I else np.zeros(0, np.int32)
-        token_item = np.repeat(np.arange(I, dtype=np.int32), self.h_qlen)
+        if T == I:                   # one token per request: a decode step
+            positions, token_item = self.h_pos0, np.arange(I, dtype=np.int32)
+        else:
+            positions = np.concatenate([np.arange(p, p + n, dtype=np.int32)
+                                        for p, n in zip(pos0, q_len)]) if I else np.zeros(0, np.int32)
+            token_item = np.repeat(np.arange(I, dtype=np.int32), self.h_qlen)
         parts = [np.asarray(token_ids, dtype=np.int32), positions, self.h_qstart, self.h_qlen,
                  self.h_pos0, self.h_slots]
         shapes = []

@@ -143,7 +143,8 @@ class ModelRunner:
             n = len(entry.tokens)
             if n == 0:
                 raise ValueError(f"step: request {entry.handle.request_id!r} brings no tokens")
-            low, high = min(entry.tokens), max(entry.tokens)
+            low, high = (entry.tokens[0], entry.tokens[0]) if n == 1 else \
+                (min(entry.tokens), max(entry.tokens))
             if low < 0 or high >= self.vocab_size:
                 raise IndexError(f"step: token id out of range [0, {self.vocab_size}) in request "
                                  f"{entry.handle.request_id!r}")

@@ -129,6 +129,8 @@ class Scheduler:
             pages_left = cache.free_pages()
 
             def take(handle, n) -> bool:
+                if cache.fits_in_held_pages(handle, n):
+                    return True
                 need = cache.pages_needed(handle, n)
                 if any(k > left for k, left in zip(need, pages_left)):
                     return False
