@@ -34,11 +34,13 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     "core": ("elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "sampling.cu"),
     # tensor-core attention, one build per head size: defines=("-DHEAD_DIM=128",)
     "attn_mma": ("attention_mma.cu",),
+    # the same attention fed by TMA (head sizes in steps of 64), one build per head size
+    "attn_tma": ("attention_tma.cu",),
     # tcgen05 / TMA matrix product for steps of few tokens
     "gemm_decode": ("gemm_decode_tcgen05.cu",),
 }
 # specialisations compiled by build_all() beside the default form of every library
-DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)]}
+DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)], "attn_tma": [("-DHEAD_DIM=128",)]}
 
 _loaded: Dict[Tuple[str, Tuple[str, ...]], ctypes.CDLL] = {}
 _lock = threading.Lock()

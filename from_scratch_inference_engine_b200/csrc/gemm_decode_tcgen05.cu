@@ -19,8 +19,8 @@
 // Every wait on an mbarrier is bounded: when it runs out the kernel records where in
 // *error, drains what it started, frees its tensor memory and returns.
 #include "common.cuh"
+#include "tma.cuh"
 #include <cooperative_groups.h>
-#include <cuda.h>
 #include <math.h>
 #include <string.h>
 
@@ -30,7 +30,6 @@ namespace cg = cooperative_groups;
 constexpr int BM = 128;            // weight rows per block (UMMA M)
 constexpr int BK = 64;             // k elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
-constexpr uint32_t SPIN_LIMIT = 4u * 1000u * 1000u;    // polls of a barrier before giving up
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
 enum { ERR_TMA_WAIT = 11, ERR_MMA_WAIT = 12, ERR_EPILOGUE_WAIT = 13 };
@@ -44,33 +43,6 @@ struct GemmParams {
     int out_f32;
     int* error;
 };
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-// Polls until the phase with `parity` completes; false when the limit runs out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_addr(bar);
-    for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
-        uint32_t done;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_addr(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar)) : "memory");
-}
 
 // Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128
 // bytes, groups of 8 rows 1,024 bytes apart (stride byte offset), version 1, layout type 2.
@@ -274,22 +246,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         else reinterpret_cast<bf16*>(p.y)[(size_t)t * p.ldy + n] = __float2bfloat16_rn(out);
     }
     if (splits > 1) cg::this_cluster().sync();        // nobody leaves while its sums may be read
-}
-
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiled encode_tiled() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult status;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
-            status == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)ptr;
-    }
-    return fn;
 }
 
 // bf16 matrix [rows, cols] with `ld` elements between rows; boxes of box_rows x 64 columns, 128-byte swizzle

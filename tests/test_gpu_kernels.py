@@ -228,8 +228,8 @@ class PagedCase:
         return out.cpu().double()
 
 
-    def run_mma(self, ops, nsplit=1):
-        """The tensor-core kernel: requests sorted into row classes as the engine does."""
+    def run_mma(self, ops, nsplit=1, tma=False):
+        """The tensor-core kernels: requests sorted into row classes as the engine does."""
         group = self.heads // self.kv_heads
         i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
         qstart, at = [], 0
@@ -257,6 +257,16 @@ class PagedCase:
                     tile_row0.append(r0)
             if not tile_item:
                 continue
+            if tma:
+                error = torch.zeros(1, dtype=torch.int32, device="cuda")
+                ops.attention_tma(c, ops.PagesMap(pages), 0, q, q.stride(0), dev(self.tables),
+                                  i32(tile_item), i32(tile_row0), len(tile_item), i32(qstart),
+                                  i32([n for _, n in self.items]), i32([p for p, _ in self.items]),
+                                  out, tokens, self.heads, self.kv_heads, self.window,
+                                  1.0 / math.sqrt(self.hd), error, nsplit, part_o, part_ml,
+                                  i32(toks), len(toks))
+                assert error.item() == 0
+                continue
             ops.attention_mma(c, q, q.stride(0), pages[:, 0, 0], pages[:, 0, 1], pages.stride(0),
                               self.page_size, dev(self.tables), i32(tile_item), i32(tile_row0),
                               len(tile_item), i32(qstart), i32([n for _, n in self.items]),
@@ -267,16 +277,21 @@ class PagedCase:
 
 
 def run_kernel(case, ops, kernel, nsplit=1):
+    if kernel == "tma":
+        if case.hd % 64 or case.page_size not in ops.ATTENTION_TMA_PAGES:
+            pytest.skip("the TMA-fed kernel takes head sizes in steps of 64 and pages of 8..64")
+        return case.run_mma(ops, nsplit, tma=True)
     return case.run_mma(ops, nsplit) if kernel == "mma" else case.run(ops, nsplit)
 
 
-KERNELS = [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16)]
+KERNELS = [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16),
+           ("tma", torch.bfloat16)]
 
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("heads,kv_heads,hd,page_size", [
     (4, 4, 16, 4), (6, 2, 48, 8), (7, 1, 80, 16), (28, 4, 128, 16), (3, 1, 256, 32),
-    (40, 1, 32, 5)])
+    (40, 1, 32, 5), (8, 2, 64, 8), (5, 1, 192, 64), (28, 4, 128, 32)])
 def test_attention_sizes(ops, kernel, dtype, heads, kv_heads, hd, page_size):
     case = PagedCase(dtype, heads, kv_heads, hd, page_size,
                      items=[(0, 37), (45, 1), (19, 6), (0, 1), (63, 2), (130, 70)], seed=heads)
