@@ -503,7 +503,7 @@ int fsie_attn_tma(int row_class, const void* pages_map, int entries, int entry, 
     TmaExtra x;
     x.entries = entries; x.entry = entry; x.error_slot = 0; x.error = error;
     int rc;
-    if (row_class == 0) rc = launch<1, 4, 3>(map, p, x, tiles, stream);
+    if (row_class == 0) rc = launch<1, 4, 2>(map, p, x, tiles, stream);
     else if (row_class == 1) rc = launch<2, 2, 3>(map, p, x, tiles, stream);
     else rc = launch<4, 1, 2>(map, p, x, tiles, stream);
     if (rc != 0 || nsplit == 1) return rc;

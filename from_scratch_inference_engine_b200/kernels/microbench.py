@@ -107,19 +107,23 @@ def run_attention(args, timer, decode: bool):
     tile_item, tile_row0 = i32(tile_item), i32(tile_row0)
     nsplit = args.nsplit
     if nsplit <= 0:
-        blocks, slots = tile_item.numel() * kv_heads, 2 * sms
-        nsplit, best = 1, 0.0
-        if blocks < (4 * slots if decode else slots):
-            for n in range(1, max(1, min(32, args.context // 128)) + 1):
-                fill = blocks * n / (-(-blocks * n // slots) * slots)
-                if fill > best + 0.02:
-                    nsplit, best = n, fill
+        from ..parts.attention import attention_splits
+        nsplit = attention_splits(tile_item.numel() * kv_heads, args.context, sms, decode)
     part_o = torch.empty(max(1, nsplit * tokens * heads * hd), device="cuda")
     part_ml = torch.empty(max(1, nsplit * tokens * heads * 2), device="cuda")
     scale = 1.0 / math.sqrt(hd)
 
+    use_tma = args.variant == "tma" and row_class >= 0
+    if use_tma:
+        pages_map = ops.PagesMap(pages)
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+
     def launch():
-        if row_class >= 0:
+        if use_tma:
+            ops.attention_tma(row_class, pages_map, 0, q, q.stride(0), tables, tile_item, tile_row0,
+                              tile_item.numel(), qstart, qlen, pos0, out, tokens, heads, kv_heads,
+                              0, scale, error, nsplit, part_o, part_ml, None, 0)
+        elif row_class >= 0:
             ops.attention_mma(row_class, q, q.stride(0), pages[:, 0, 0], pages[:, 0, 1],
                               pages.stride(0), page, tables, tile_item, tile_row0,
                               tile_item.numel(), qstart, qlen, pos0, out, tokens, heads, kv_heads,
@@ -137,7 +141,7 @@ def run_attention(args, timer, decode: bool):
     pairs = args.batch * (new * past + new * (new + 1) / 2)
     flops = 4.0 * heads * hd * pairs
     return ms, io_bytes, flops, {"nsplit": nsplit, "tiles": tile_item.numel(),
-                                 "variant": "mma" if row_class >= 0 else "generic"}
+                                 "variant": ("tma" if use_tma else "mma") if row_class >= 0 else "generic"}
 
 
 def run(args):
@@ -240,6 +244,8 @@ def main(argv=None) -> int:
     parser.add_argument("--n", type=int, default=37888)
     parser.add_argument("--k", type=int, default=3584)
     parser.add_argument("--nsplit", type=int, default=0, help="0 = the engine's choice")
+    parser.add_argument("--variant", default="mma", choices=["mma", "tma"],
+                        help="bfloat16 attention: cp.async loads or TMA loads")
     parser.add_argument("--top-k", type=int, default=0)
     parser.add_argument("--top-p", type=float, default=1.0)
     parser.add_argument("--warmup", type=int, default=3)
