@@ -72,6 +72,9 @@ class Qwen2Config:
         eos = data.get("eos_token_id")
         if isinstance(eos, list):
             eos = eos[0] if eos else None
+        if data.get("rope_scaling") is not None:
+            raise ConfigError("config.json: rope_scaling is not supported (the reference applies "
+                              "plain rotary encoding only)")
         use_window = bool(data.get("use_sliding_window", False))
         config = cls(
             hidden_size=hidden,

@@ -8,6 +8,7 @@ lookup failure (src/model/safetensors.cpp:127-133).
 
 from __future__ import annotations
 
+import json
 from pathlib import Path
 from typing import Dict, Iterable, Mapping
 
@@ -68,5 +69,24 @@ def to_runtime_dtype(tensor: torch.Tensor, spec: TensorSpec, dtype: torch.dtype)
 
 
 def load_checkpoint(model_dir) -> Dict[str, torch.Tensor]:
-    """All tensors of `model_dir/model.safetensors`, in their stored dtypes, on the host."""
-    return load_file(Path(model_dir) / "model.safetensors")
+    """All tensors of the checkpoint in `model_dir`, in their stored dtypes, on the host:
+    `model.safetensors`, or the shards that `model.safetensors.index.json` names (the
+    reference reads the single file only, src/model/model.cpp:43-47)."""
+    model_dir = Path(model_dir)
+    single, index = model_dir / "model.safetensors", model_dir / "model.safetensors.index.json"
+    if single.exists() or not index.exists():
+        return load_file(single)
+    try:
+        weight_map = json.loads(index.read_text(encoding="utf-8"))["weight_map"]
+    except (OSError, ValueError, KeyError) as error:
+        raise WeightError(f"{index} is not a shard index: {error}") from error
+    tensors: Dict[str, torch.Tensor] = {}
+    for shard in sorted(set(weight_map.values())):
+        for name, tensor in load_file(model_dir / shard).items():
+            if name in tensors:
+                raise WeightError(f"tensor '{name}' is stored in more than one shard")
+            tensors[name] = tensor
+    absent = sorted(name for name in weight_map if name not in tensors)
+    if absent:
+        raise WeightError(f"{index} names tensors its shards do not hold: {', '.join(absent)}")
+    return tensors

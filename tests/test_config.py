@@ -41,6 +41,7 @@ def test_explicit_head_dim_and_bias_of_other_model_types():
     dict(hidden_act="gelu"), dict(vocab_size=0), dict(rope_theta=-1.0),
     dict(use_sliding_window=True, sliding_window=0),
     dict(use_sliding_window=True, sliding_window=8, max_window_layers=5),
+    dict(rope_scaling={"type": "yarn", "factor": 4.0}),
 ])
 def test_invalid_values_are_refused(bad):
     with pytest.raises(ConfigError):

@@ -163,3 +163,23 @@ def test_standard_normal_is_keyed_by_seed_and_name():
     assert np.array_equal(a[:100], standard_normal(3, "x", 100))
     assert not np.array_equal(a[:100], standard_normal(3, "y", 100))
     assert abs(a.mean()) < 0.05 and abs(a.std() - 1.0) < 0.05
+
+
+def test_sharded_checkpoint_is_read_through_its_index(tmp_path):
+    c = config_from_dict(TINY["A"]["config"])
+    folder = write_random_model(tmp_path / "m", c, seed=0, std=0.02)
+    whole = load_checkpoint(folder)
+    names = sorted(whole)
+    first, second = names[:len(names) // 2], names[len(names) // 2:]
+    save_file({n: whole[n] for n in first}, folder / "model-00001-of-00002.safetensors")
+    save_file({n: whole[n] for n in second}, folder / "model-00002-of-00002.safetensors")
+    index = {"weight_map": {**{n: "model-00001-of-00002.safetensors" for n in first},
+                            **{n: "model-00002-of-00002.safetensors" for n in second}}}
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    (folder / "model.safetensors").unlink()
+    shards = load_checkpoint(folder)
+    assert set(shards) == set(whole) and all(torch.equal(shards[n], whole[n]) for n in whole)
+    index["weight_map"]["ghost.weight"] = "model-00002-of-00002.safetensors"
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(WeightError, match="ghost.weight"):
+        load_checkpoint(folder)
