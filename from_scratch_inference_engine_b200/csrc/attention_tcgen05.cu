@@ -1,0 +1,487 @@
+// Causal grouped-query attention for prompt portions on the 5th-generation tensor cores:
+// scores and outputs are accumulated in tensor memory by tcgen05.mma, keys and values arrive
+// by TMA, bfloat16 storage, 32-bit scores / softmax statistics / accumulation.
+// Compiled per head size (-DHEAD_DIM=64 or 128).
+//
+// A block owns 128 query rows of one request and one kv head - a row is a (new token, head of
+// the group) pair as in attention_mma.cu - and walks the keys in tiles of 128:
+//
+//   producer warp   TMA: one cp.async.bulk.tensor per page and 128-byte column half, for K and V,
+//                   into a 2-stage ring (full/empty mbarriers), 128-byte swizzle
+//   MMA warp        S[i] = Q K_i^T  (128 x 128 x head_dim, A and B K-major) into one of two score
+//                   buffers in tensor memory, issued one tile ahead of the softmax;
+//                   O += P_i V_i    (128 x head_dim x 128, A = P from shared memory, B = V
+//                   MN-major straight from its [key][dim] tile)
+//   4 softmax warps one thread per row (= tensor-memory lane): read S, mask, running maximum and
+//                   sum, write P as bfloat16 into shared memory in the swizzled K-major layout,
+//                   rescale O in tensor memory when a row's maximum moved, finally normalise O
+//                   and store it (or a partial result when the key range is split)
+//
+// Formula: src/model/nn.cpp:151-226 of the reference, as a running softmax.
+// Every wait on an mbarrier is bounded; when one runs out *error is set, all roles leave their
+// loops, tensor memory is freed and the kernel returns.
+#include "common.cuh"
+#include "attention_params.cuh"
+#include "tma.cuh"
+#include <math.h>
+#include <string.h>
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<head size>"
+#endif
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size 64 or 128");
+
+namespace fsie {
+
+constexpr int HD = HEAD_DIM;
+constexpr int BM = 128;                 // query rows per block = tensor-memory lanes
+constexpr int BN = 128;                 // keys per tile
+constexpr int STAGES = 2;
+constexpr int HALVES = HD / 64;         // 128-byte column halves of a row of head_dim elements
+constexpr int ATOM_BYTES = 128 * 128;   // 128 rows x 128 bytes: one swizzled block
+constexpr int Q_BYTES = HALVES * ATOM_BYTES;
+constexpr int KV_BYTES = HALVES * ATOM_BYTES;          // one K or V tile
+constexpr int P_BYTES = (BN / 64) * ATOM_BYTES;        // P[128 rows, 128 keys] bf16
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + P_BYTES + STAGES * 2 * KV_BYTES;
+constexpr uint32_t TMEM_COLS = 512;     // S0 | S1 | O  (128 + 128 + head_dim columns), power of two
+constexpr uint32_t COL_S0 = 0, COL_S1 = BN, COL_O = 2 * BN;
+enum { ERR_TC_PRODUCER = 31, ERR_TC_MMA = 32, ERR_TC_SOFTMAX = 33 };
+
+struct TcExtra { int entries, entry; int* error; };
+
+// 64-bit shared-memory matrix descriptors (version 1, 128-byte swizzle).
+// K-major: rows of 128 bytes, 8-row groups 1,024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(const void* p) {
+    return (uint64_t)((smem_addr(p) & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major (the tile is stored [k][mn] with 64 mn-elements = 128 bytes per k): 8 k-rows are a
+// 1,024-byte block (stride byte offset), the next 64 mn-elements are a whole block column
+// further (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mn_major(const void* p, uint32_t mn_block_bytes) {
+    return (uint64_t)((smem_addr(p) & 0x3FFFF) >> 4) | ((uint64_t)(mn_block_bytes >> 4) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// instruction descriptor: D float, A and B bfloat16, M x N; b_mn_major selects an MN-major B
+__device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr),
+                   "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                   "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                   "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                   "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                   "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                   "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                   "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                   "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a 128-byte-swizzled block
+__device__ __forceinline__ int swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+__global__ void __launch_bounds__(192)
+attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p, const TcExtra x) {
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+    unsigned char* q_s = smem;                               // [HALVES][128 rows][128 B]
+    unsigned char* p_s = q_s + Q_BYTES;                      // [2][128 rows][128 B]: keys 0-63 | 64-127
+    unsigned char* kv_s = p_s + P_BYTES;                     // [STAGES][K | V][HALVES][128 keys][128 B]
+    __shared__ uint64_t kv_full[STAGES], kv_empty[STAGES], s_full[2], p_ready, o_done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int group = p.heads / p.kv_heads;
+    const int item = p.tile_item[tile];
+    const int row0 = p.tile_row0[tile];
+    const int qstart = p.item_qstart[item], qlen = p.item_qlen[item], pos0 = p.item_pos0[item];
+    const int nrows = min(BM, qlen * group - row0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bf16* q = (const bf16*)p.q;
+    const int* bt = p.block_tables + (size_t)item * p.bt_stride;
+
+    const int pos_first = pos0 + row0 / group;
+    const int pos_last = pos0 + (row0 + nrows - 1) / group;
+    int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int kend = pos_last + 1;
+    if (p.nsplit > 1) {
+        const int span = kend - kbegin;
+        int chunk = (span + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + BN - 1) / BN) * BN;
+        const int b = kbegin + split * chunk;
+        kend = min(kend, b + chunk);
+        kbegin = b;
+    }
+    kbegin = kbegin / BN * BN;          // tiles hold whole pages; keys before the window are masked
+    const int ntiles = kend > kbegin ? (kend - kbegin + BN - 1) / BN : 0;
+
+    // ---- set-up: barriers, tensor memory, zeroed stages (pages never fetched must read as finite
+    // numbers), the query tile in the swizzled K-major layout
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
+        mbar_init(&p_ready, 128); mbar_init(&o_done, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    for (int e = tid; e < (P_BYTES + STAGES * 2 * KV_BYTES) / 16; e += blockDim.x)
+        reinterpret_cast<uint4*>(p_s)[e] = make_uint4(0, 0, 0, 0);
+    for (int e = tid; e < BM * (HD / 8); e += blockDim.x) {
+        const int r = e / (HD / 8), c = e - r * (HD / 8);     // 16-byte chunk c of row r
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nrows) {
+            const int row = row0 + r;
+            const int tok = qstart + row / group, h = kvh * group + row % group;
+            v = *reinterpret_cast<const uint4*>(q + (size_t)tok * p.q_ld + h * HD + c * 8);
+        }
+        *reinterpret_cast<uint4*>(q_s + (c >> 3) * ATOM_BYTES + swizzled(r, c & 7)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes before async-proxy reads
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const int ps = p.page_size, pages_per_tile = BN / ps;
+            const long long rows_per_page = (long long)x.entries * 2 * p.kv_heads * ps;
+            const long long k_row0 = ((long long)x.entry * 2) * p.kv_heads * ps + (long long)kvh * ps;
+            const long long v_row0 = k_row0 + (long long)p.kv_heads * ps;
+            for (int i = 0; i < ntiles; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1)) {
+                    atomicExch(x.error, ERR_TC_PRODUCER); atomicExch(&abort_flag, 1); break;
+                }
+                if (*(volatile int*)&abort_flag) break;
+                const int k0 = kbegin + i * BN;
+                unsigned char* kd = kv_s + (size_t)s * 2 * KV_BYTES;
+                unsigned char* vd = kd + KV_BYTES;
+                int wanted = 0;
+                for (int j = 0; j < pages_per_tile; ++j) {
+                    const int key = k0 + j * ps;
+                    wanted += key < kend && bt[key / ps] >= 0;
+                }
+                mbar_expect_tx(&kv_full[s], (uint32_t)wanted * ps * HD * 2 * 2);
+                for (int j = 0; j < pages_per_tile; ++j) {
+                    const int key = k0 + j * ps;
+                    const int page = key < kend ? bt[key / ps] : -1;
+                    if (page < 0) continue;
+                    const long long base = (long long)page * rows_per_page;
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) {
+                        tma_load_2d(kd + h * ATOM_BYTES + j * ps * 128, &pages_map, h * 64, (int)(base + k_row0), &kv_full[s]);
+                        tma_load_2d(vd + h * ATOM_BYTES + j * ps * 128, &pages_map, h * 64, (int)(base + v_row0), &kv_full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && ntiles > 0) {
+            const uint32_t idesc_s = idesc_bf16(BM, BN, 0), idesc_o = idesc_bf16(BM, HD, 1);
+            bool ok = true;
+            auto scores = [&](int i) {       // S[i % 2] = Q K_i^T
+                const int s = i % STAGES;
+                if (!mbar_wait(&kv_full[s], (i / STAGES) & 1)) {
+                    atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false; return;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned char* kd = kv_s + (size_t)s * 2 * KV_BYTES;
+                const uint32_t d = tmem + ((i & 1) ? COL_S1 : COL_S0);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint64_t a = desc_k_major(q_s + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
+                    const uint64_t b = desc_k_major(kd + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
+                    mma_ss(d, a, b, idesc_s, k > 0);
+                }
+                mma_commit(&s_full[i & 1]);
+            };
+            scores(0);
+            for (int i = 0; i < ntiles && ok; ++i) {
+                if (i + 1 < ntiles) scores(i + 1);          // one tile ahead of the softmax
+                if (!ok) break;
+                if (!mbar_wait(&p_ready, i & 1)) {
+                    atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int s = i % STAGES;
+                const unsigned char* vd = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k) {         // 16 keys per instruction
+                    const uint64_t a = desc_k_major(p_s + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
+                    const uint64_t b = desc_mn_major(vd + k * 16 * 128, ATOM_BYTES);
+                    mma_ss(tmem + COL_O, a, b, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(&kv_empty[s]);                   // K_i and V_i may be overwritten
+                mma_commit(&o_done);                        // O holds tiles 0..i; P may be overwritten
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax, one thread per row
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                  // row of the tile = tensor-memory lane
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool valid = r < nrows;
+        const int pos = valid ? pos0 + (row0 + r) / group : -1;
+        const int lowest = p.window > 0 ? pos - p.window : -1;       // keys <= this are unseen
+        const float sc = p.scale * 1.4426950408889634f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int i = 0; i < ntiles && ok; ++i) {
+            // (decisions to give up are taken by whole warps: the tensor-memory accesses below are
+            // warp-collective)
+            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1))) {
+                if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
+                atomicExch(&abort_flag, 1); ok = false; break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t s_addr = lane_base + ((i & 1) ? COL_S1 : COL_S0);
+            const int k0 = kbegin + i * BN;
+            // pass 1: the row's maximum over the tile
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float v[32];
+                tmem_ld32(s_addr + c, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int key = k0 + c + j;
+                    if (key < kend && key <= pos && key > lowest) mx = fmaxf(mx, v[j]);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float base = m_new == -INFINITY ? 0.f : m_new * sc;
+            const float corr = exp2f(m_run * sc - base);               // m_run = -inf gives 0
+            // the previous tile's P V must be complete before P is overwritten and O rescaled
+            if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(&o_done, (i - 1) & 1))) {
+                if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
+                atomicExch(&abort_flag, 1); ok = false; break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 32) {
+                    float v[32];
+                    tmem_ld32(lane_base + COL_O + c, v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] *= corr;
+                    tmem_st32(lane_base + COL_O + c, v);
+                }
+            }
+            // pass 2: p = exp2(s * sc - base), row sum, P as bfloat16 in the swizzled layout
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float v[32];
+                tmem_ld32(s_addr + c, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int key = k0 + c + j;
+                    const bool seen = key < kend && key <= pos && key > lowest;
+                    v[j] = seen ? exp2f(v[j] * sc - base) : 0.f;
+                    sum += v[j];
+                }
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {                       // 8 keys = one 16-byte chunk
+                    uint4 packed;
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(v[g8 * 8 + 2 * j], v[g8 * 8 + 2 * j + 1]);
+                    const int chunk = (c >> 3) + g8;                   // chunk of the 128-key row, 0..15
+                    *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
+                }
+            }
+            l_run = l_run * corr + sum;
+            m_run = m_new;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P before the tensor core reads it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");  // O rescale before the next MMA
+            mbar_arrive(&p_ready);
+        }
+        // ---- the last P V, then normalise and store (or hand a partial result to the merge)
+        bool have = ok && ntiles > 0;
+        if (have && !__all_sync(0xffffffffu, mbar_wait(&o_done, (ntiles - 1) & 1))) {
+            if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
+            atomicExch(&abort_flag, 1); have = false;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = row0 + (valid ? r : 0);
+        const int tok = qstart + row / group, h = kvh * group + row % group;
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+            float v[32];
+            if (have) tmem_ld32(lane_base + COL_O + c, v);       // warp-collective: every lane takes part
+            else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            }
+            if (!valid) continue;
+            if (p.nsplit == 1) {
+                bf16* dst = (bf16*)p.out + (size_t)tok * p.out_ld + h * HD + c;
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    uint4 packed;
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        h2[j] = __floats2bfloat162_rn(v[g8 * 8 + 2 * j] * inv, v[g8 * 8 + 2 * j + 1] * inv);
+                    *reinterpret_cast<uint4*>(dst + g8 * 8) = packed;
+                }
+            } else {
+                const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
+                float* dst = p.part_o + idx * HD + c;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+        }
+        if (valid && p.nsplit > 1) {
+            const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
+            p.part_ml[idx * 2] = m_run == -INFINITY ? -INFINITY : m_run * p.scale;
+            p.part_ml[idx * 2 + 1] = l_run;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Merge the key splits of one (token, head); same arithmetic as attention_generic.cu.
+__global__ void attn_tc_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       bf16* __restrict__ out, int out_ld, int tokens, int heads,
+                                       int nsplit, const int* __restrict__ token_list) {
+    const int tok = token_list ? token_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    const size_t stride = (size_t)tokens * heads, slot = (size_t)tok * heads + h;
+    float mz = -INFINITY, lz = 0.f;
+    if (lane < nsplit) {
+        mz = part_ml[(lane * stride + slot) * 2];
+        lz = part_ml[(lane * stride + slot) * 2 + 1];
+    }
+    const float mmax = warp_max(mz);
+    const float wz = mz == -INFINITY ? 0.f : __expf(mz - mmax);
+    const float denom = warp_sum(lz * wz);
+    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+    for (int d = threadIdx.x * 2; d < HD; d += blockDim.x * 2) {
+        float a0 = 0.f, a1 = 0.f;
+        for (int z = 0; z < nsplit; ++z) {
+            const float w = __shfl_sync(0xffffffffu, wz, z);
+            if (w != 0.f) {
+                const float2 v = *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d);
+                a0 += v.x * w; a1 += v.y * w;
+            }
+        }
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * out_ld + h * HD + d) = __floats2bfloat162_rn(a0 * inv, a1 * inv);
+    }
+}
+
+}  // namespace fsie
+
+using namespace fsie;
+
+extern "C" {
+
+int fsie_attn_tc_head_dim() { return HD; }
+int fsie_attn_tc_rows() { return BM; }
+int fsie_attn_tc_map_bytes() { return (int)sizeof(CUtensorMap); }
+
+// Tensor map of a cache group's pages [num_pages, entries, 2, kv_heads, page_size, head_dim] seen
+// as a matrix of head_dim columns; boxes of page_size rows x 64 columns, 128-byte swizzle.
+int fsie_attn_tc_pages_map(void* map_out, const void* pages, long long total_rows, int head_dim, int page_size) {
+    if (head_dim != HD) return ERR_UNSUPPORTED;
+    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return ERR_UNSUPPORTED;
+    if (total_rows <= 0 || total_rows >= (1ll << 31)) return ERR_UNSUPPORTED;
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return ERR_UNSUPPORTED;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)total_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box,
+                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return ERR_BAD_ARGUMENT;
+    memcpy(map_out, &map, sizeof(map));
+    return 0;
+}
+
+// Tiles of 128 query rows.  Arguments as fsie_attn_tma (attention_tma.cu).
+int fsie_attn_tc(const void* pages_map, int entries, int entry, const void* q, int q_ld, int page_size,
+                 const int* block_tables, int bt_stride, const int* tile_item, const int* tile_row0, int tiles,
+                 const int* item_qstart, const int* item_qlen, const int* item_pos0, void* out, int out_ld,
+                 float* part_o, float* part_ml, int tokens, int heads, int kv_heads, int head_dim, int window,
+                 int nsplit, float scale, const int* combine_tokens, int num_combine, int* error,
+                 cudaStream_t stream) {
+    if (tiles <= 0 || tokens <= 0) return 0;
+    if (head_dim != HD) return ERR_UNSUPPORTED;
+    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return ERR_UNSUPPORTED;
+    if (kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 || nsplit > 32 || (q_ld % 8) != 0 ||
+        (out_ld % 8) != 0 || entries <= 0 || entry < 0 || entry >= entries || !error)
+        return ERR_BAD_ARGUMENT;
+    if (nsplit > 1 && (!part_o || !part_ml)) return ERR_BAD_ARGUMENT;
+    CUtensorMap map;
+    memcpy(&map, pages_map, sizeof(map));
+    AttnParams p;
+    p.q = q; p.q_ld = q_ld; p.k_pages = nullptr; p.v_pages = nullptr;
+    p.page_stride = 0; p.page_size = page_size;
+    p.block_tables = block_tables; p.bt_stride = bt_stride;
+    p.tile_item = tile_item; p.tile_row0 = tile_row0;
+    p.item_qstart = item_qstart; p.item_qlen = item_qlen; p.item_pos0 = item_pos0;
+    p.out = out; p.out_ld = out_ld; p.part_o = part_o; p.part_ml = part_ml;
+    p.tokens = tokens; p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
+    p.window = window; p.nsplit = nsplit; p.scale = scale;
+    TcExtra x;
+    x.entries = entries; x.entry = entry; x.error = error;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attn_tc_kernel<<<dim3(tiles, kv_heads, nsplit), 192, SMEM_BYTES, stream>>>(map, p, x);
+    int rc = (int)cudaGetLastError();
+    if (rc != 0 || nsplit == 1) return rc;
+    const int count = combine_tokens ? num_combine : tokens;
+    if (count <= 0) return 0;
+    attn_tc_combine_kernel<<<dim3(count, heads), HD >= 128 ? 64 : 32, 0, stream>>>(
+        part_o, part_ml, (bf16*)out, out_ld, tokens, heads, nsplit, combine_tokens);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

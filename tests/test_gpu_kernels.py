@@ -228,7 +228,7 @@ class PagedCase:
         return out.cpu().double()
 
 
-    def run_mma(self, ops, nsplit=1, tma=False):
+    def run_mma(self, ops, nsplit=1, tma=False, tc=False):
         """The tensor-core kernels: requests sorted into row classes as the engine does."""
         group = self.heads // self.kv_heads
         i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
@@ -244,6 +244,8 @@ class PagedCase:
             part_o = torch.full((nsplit * tokens * self.heads * self.hd,), float("nan"), device="cuda")
             part_ml = torch.full((nsplit * tokens * self.heads * 2,), float("nan"), device="cuda")
         classes = ops.ATTENTION_ROW_CLASSES
+        if tc:      # prompt portions in tiles of 128 rows through the tcgen05 kernel
+            classes = classes[:2] + (ops.ATTENTION_TC_ROWS,)
         for c, per_tile in enumerate(classes):
             tile_item, tile_row0, toks = [], [], []
             for i, (_, new) in enumerate(self.items):
@@ -256,6 +258,16 @@ class PagedCase:
                     tile_item.append(i)
                     tile_row0.append(r0)
             if not tile_item:
+                continue
+            if tc and c == 2:
+                error = torch.zeros(1, dtype=torch.int32, device="cuda")
+                ops.attention_tc(ops.PagesMap(pages, "tc"), 0, q, q.stride(0), dev(self.tables),
+                                 i32(tile_item), i32(tile_row0), len(tile_item), i32(qstart),
+                                 i32([n for _, n in self.items]), i32([p for p, _ in self.items]),
+                                 out, tokens, self.heads, self.kv_heads, self.window,
+                                 1.0 / math.sqrt(self.hd), error, nsplit, part_o, part_ml,
+                                 i32(toks), len(toks))
+                assert error.item() == 0
                 continue
             if tma:
                 error = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -277,6 +289,10 @@ class PagedCase:
 
 
 def run_kernel(case, ops, kernel, nsplit=1):
+    if kernel == "tc":
+        if case.hd not in ops.ATTENTION_TC_HEAD_DIMS or case.page_size not in ops.ATTENTION_TC_PAGES:
+            pytest.skip("the tcgen05 kernel takes head sizes 64 and 128 and pages of 8..128")
+        return case.run_mma(ops, nsplit, tc=True)
     if kernel == "tma":
         if case.hd % 64 or case.page_size not in ops.ATTENTION_TMA_PAGES:
             pytest.skip("the TMA-fed kernel takes head sizes in steps of 64 and pages of 8..64")
@@ -285,7 +301,7 @@ def run_kernel(case, ops, kernel, nsplit=1):
 
 
 KERNELS = [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16),
-           ("tma", torch.bfloat16)]
+           ("tma", torch.bfloat16), ("tc", torch.bfloat16)]
 
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
