@@ -74,6 +74,27 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// issue a read of 32 columns; the registers are valid only after tmem_wait_ld()
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32_issue(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -116,7 +137,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
-    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // later tiles of a prompt see more keys: start them first so that the last wave is short
+    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     const int item = p.tile_item[tile];
     const int row0 = p.tile_row0[tile];
@@ -174,36 +196,34 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            const int ps = p.page_size, pages_per_tile = BN / ps;
-            const long long rows_per_page = (long long)x.entries * 2 * p.kv_heads * ps;
-            const long long k_row0 = ((long long)x.entry * 2) * p.kv_heads * ps + (long long)kvh * ps;
-            const long long v_row0 = k_row0 + (long long)p.kv_heads * ps;
-            for (int i = 0; i < ntiles; ++i) {
-                const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1)) {
-                    atomicExch(x.error, ERR_TC_PRODUCER); atomicExch(&abort_flag, 1); break;
-                }
-                if (*(volatile int*)&abort_flag) break;
-                const int k0 = kbegin + i * BN;
-                unsigned char* kd = kv_s + (size_t)s * 2 * KV_BYTES;
+        // lane j looks up and fetches page j of the tile: the table reads and the copy
+        // instructions of a tile go out side by side instead of one after the other
+        const int ps = p.page_size, pages_per_tile = BN / ps;
+        const long long rows_per_page = (long long)x.entries * 2 * p.kv_heads * ps;
+        const long long k_row0 = ((long long)x.entry * 2) * p.kv_heads * ps + (long long)kvh * ps;
+        const long long v_row0 = k_row0 + (long long)p.kv_heads * ps;
+        for (int i = 0; i < ntiles; ++i) {
+            const int s = i % STAGES;
+            const int key = kbegin + i * BN + lane * ps;
+            const int page = (lane < pages_per_tile && key < kend) ? bt[key / ps] : -1;   // before the wait: overlaps it
+            bool ok = true;
+            if (lane == 0 && i >= STAGES) ok = mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1);
+            ok = __shfl_sync(0xffffffffu, ok, 0) && !*(volatile int*)&abort_flag;
+            if (!ok) {
+                if (lane == 0) { atomicExch(x.error, ERR_TC_PRODUCER); atomicExch(&abort_flag, 1); }
+                break;
+            }
+            const int wanted = __popc(__ballot_sync(0xffffffffu, page >= 0));
+            if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)wanted * ps * HD * 2 * 2);
+            __syncwarp();
+            if (page >= 0) {
+                unsigned char* kd = kv_s + (size_t)s * 2 * KV_BYTES + lane * ps * 128;
                 unsigned char* vd = kd + KV_BYTES;
-                int wanted = 0;
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    const int key = k0 + j * ps;
-                    wanted += key < kend && bt[key / ps] >= 0;
-                }
-                mbar_expect_tx(&kv_full[s], (uint32_t)wanted * ps * HD * 2 * 2);
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    const int key = k0 + j * ps;
-                    const int page = key < kend ? bt[key / ps] : -1;
-                    if (page < 0) continue;
-                    const long long base = (long long)page * rows_per_page;
+                const long long base = (long long)page * rows_per_page;
 #pragma unroll
-                    for (int h = 0; h < HALVES; ++h) {
-                        tma_load_2d(kd + h * ATOM_BYTES + j * ps * 128, &pages_map, h * 64, (int)(base + k_row0), &kv_full[s]);
-                        tma_load_2d(vd + h * ATOM_BYTES + j * ps * 128, &pages_map, h * 64, (int)(base + v_row0), &kv_full[s]);
-                    }
+                for (int h = 0; h < HALVES; ++h) {
+                    tma_load_2d(kd + h * ATOM_BYTES, &pages_map, h * 64, (int)(base + k_row0), &kv_full[s]);
+                    tma_load_2d(vd + h * ATOM_BYTES, &pages_map, h * 64, (int)(base + v_row0), &kv_full[s]);
                 }
             }
         }
@@ -269,16 +289,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t s_addr = lane_base + ((i & 1) ? COL_S1 : COL_S0);
             const int k0 = kbegin + i * BN;
-            // pass 1: the row's maximum over the tile
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                float v[32];
-                tmem_ld32(s_addr + c, v);
+            // the row's 128 scores in registers: four reads in flight, one wait
+            uint32_t sr[BN];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int key = k0 + c + j;
-                    if (key < kend && key <= pos && key > lowest) mx = fmaxf(mx, v[j]);
+            for (int c = 0; c < BN; c += 32) tmem_ld32_issue(s_addr + c, sr + c);
+            tmem_wait_ld();
+            float mx = -INFINITY;
+            const bool clear = k0 + BN - 1 < kend && k0 + BN - 1 <= pos && k0 > lowest;   // nothing to mask
+            if (__all_sync(0xffffffffu, clear || !valid)) {
+#pragma unroll
+                for (int j = 0; j < BN; ++j) mx = fmaxf(mx, __uint_as_float(sr[j]));
+                if (!valid) mx = -INFINITY;
+            } else {
+#pragma unroll
+                for (int j = 0; j < BN; ++j) {
+                    const int key = k0 + j;
+                    const bool seen = key < kend && key <= pos && key > lowest;
+                    if (!seen) sr[j] = 0xff800000u;                    // -inf
+                    mx = fmaxf(mx, __uint_as_float(sr[j]));
                 }
             }
             const float m_new = fmaxf(m_run, mx);
@@ -290,38 +318,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 atomicExch(&abort_flag, 1); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll 1
-                for (int c = 0; c < HD; c += 32) {
-                    float v[32];
-                    tmem_ld32(lane_base + COL_O + c, v);
+            if (i > 0 && __any_sync(0xffffffffu, valid && corr != 1.f)) {
+                uint32_t orr[HD];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] *= corr;
-                    tmem_st32(lane_base + COL_O + c, v);
-                }
+                for (int c = 0; c < HD; c += 32) tmem_ld32_issue(lane_base + COL_O + c, orr + c);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < HD; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * corr);
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) tmem_st32_issue(lane_base + COL_O + c, orr + c);
+                tmem_wait_st();
             }
-            // pass 2: p = exp2(s * sc - base), row sum, P as bfloat16 in the swizzled layout
+            // p = exp2(s * sc - base), row sum, P as bfloat16 in the swizzled layout
             float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                float v[32];
-                tmem_ld32(s_addr + c, v);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int key = k0 + c + j;
-                    const bool seen = key < kend && key <= pos && key > lowest;
-                    v[j] = seen ? exp2f(v[j] * sc - base) : 0.f;
-                    sum += v[j];
+            for (int chunk = 0; chunk < BN / 8; ++chunk) {                 // 8 keys = one 16-byte chunk
+                float pv[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    pv[j] = valid ? exp2f(__uint_as_float(sr[chunk * 8 + j]) * sc - base) : 0.f;
+                    sum += pv[j];
                 }
+                uint4 packed;
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-                for (int g8 = 0; g8 < 4; ++g8) {                       // 8 keys = one 16-byte chunk
-                    uint4 packed;
-                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(v[g8 * 8 + 2 * j], v[g8 * 8 + 2 * j + 1]);
-                    const int chunk = (c >> 3) + g8;                   // chunk of the 128-key row, 0..15
-                    *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
-                }
+                for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(pv[2 * j], pv[2 * j + 1]);
+                *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
             }
             l_run = l_run * corr + sum;
             m_run = m_new;

@@ -152,37 +152,35 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams 
 
     if (warp == WARPS_M * WARPS_K) {
         // ------------------------------------------------------------------ producer warp
-        if (lane == 0) {
-            const int ps = p.page_size, pages_per_tile = BN / ps;
-            // rows of the [all pages x entries x K|V x kv heads x slots, head_dim] tensor
-            const long long rows_per_page = (long long)x.entries * 2 * p.kv_heads * ps;
-            const long long k_row0 = ((long long)x.entry * 2) * p.kv_heads * ps + (long long)kvh * ps;
-            const long long v_row0 = k_row0 + (long long)p.kv_heads * ps;
-            for (int i = 0; i < ntiles; ++i) {
-                const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
-                    atomicExch(x.error, ERR_ATTN_PRODUCER);
-                    break;
-                }
-                const int k0 = kbegin + i * BN;
-                int pages[BN / 8];                       // page ids of the tile (at most 8)
-                int wanted = 0;
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    const int key = k0 + j * ps;
-                    pages[j] = key < kend ? bt[key / ps] : -1;
-                    wanted += pages[j] >= 0;
-                }
-                mbar_expect_tx(&full_bar[s], (uint32_t)wanted * ps * HD * 2 * 2);
-                unsigned char* kd = Ks + (size_t)s * TILE_BYTES;
-                unsigned char* vd = Vs + (size_t)s * TILE_BYTES;
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    if (pages[j] < 0) continue;
-                    const long long base = (long long)pages[j] * rows_per_page;
+        // lane j looks up and fetches page j of the tile: the table reads and the copy
+        // instructions of a tile go out side by side instead of one after the other
+        const int ps = p.page_size, pages_per_tile = BN / ps;
+        // rows of the [all pages x entries x K|V x kv heads x slots, head_dim] tensor
+        const long long rows_per_page = (long long)x.entries * 2 * p.kv_heads * ps;
+        const long long k_row0 = ((long long)x.entry * 2) * p.kv_heads * ps + (long long)kvh * ps;
+        const long long v_row0 = k_row0 + (long long)p.kv_heads * ps;
+        for (int i = 0; i < ntiles; ++i) {
+            const int s = i % STAGES;
+            const int key = kbegin + i * BN + lane * ps;
+            const int page = (lane < pages_per_tile && key < kend) ? bt[key / ps] : -1;
+            bool ok = true;
+            if (lane == 0 && i >= STAGES) ok = mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) atomicExch(x.error, ERR_ATTN_PRODUCER);
+                break;
+            }
+            const int wanted = __popc(__ballot_sync(0xffffffffu, page >= 0));
+            if (lane == 0) mbar_expect_tx(&full_bar[s], (uint32_t)wanted * ps * HD * 2 * 2);
+            __syncwarp();
+            if (page >= 0) {
+                unsigned char* kd = Ks + (size_t)s * TILE_BYTES + lane * ps * 128;
+                unsigned char* vd = Vs + (size_t)s * TILE_BYTES + lane * ps * 128;
+                const long long base = (long long)page * rows_per_page;
 #pragma unroll
-                    for (int h = 0; h < HALVES; ++h) {
-                        tma_load_2d(kd + h * HALF_BYTES + j * ps * 128, &pages_map, h * 64, (int)(base + k_row0), &full_bar[s]);
-                        tma_load_2d(vd + h * HALF_BYTES + j * ps * 128, &pages_map, h * 64, (int)(base + v_row0), &full_bar[s]);
-                    }
+                for (int h = 0; h < HALVES; ++h) {
+                    tma_load_2d(kd + h * HALF_BYTES, &pages_map, h * 64, (int)(base + k_row0), &full_bar[s]);
+                    tma_load_2d(vd + h * HALF_BYTES, &pages_map, h * 64, (int)(base + v_row0), &full_bar[s]);
                 }
             }
         }

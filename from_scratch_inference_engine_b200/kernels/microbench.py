@@ -96,6 +96,8 @@ def run_attention(args, timer, decode: bool):
     if dtype is torch.bfloat16:
         row_class = next((c for c, r in enumerate(ops.ATTENTION_ROW_CLASSES) if rows <= r), 2)
         per_tile = ops.ATTENTION_ROW_CLASSES[row_class]
+        if args.variant == "tc" and row_class == 2:
+            per_tile = ops.ATTENTION_TC_ROWS
     else:
         row_class, per_tile = -1, ops.attention_rows_per_tile()
     tile_item, tile_row0 = [], []
@@ -114,12 +116,17 @@ def run_attention(args, timer, decode: bool):
     scale = 1.0 / math.sqrt(hd)
 
     use_tma = args.variant == "tma" and row_class >= 0
-    if use_tma:
-        pages_map = ops.PagesMap(pages)
+    use_tc = args.variant == "tc" and row_class == 2
+    if use_tma or use_tc:
+        pages_map = ops.PagesMap(pages, "tc" if use_tc else "tma")
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def launch():
-        if use_tma:
+        if use_tc:
+            ops.attention_tc(pages_map, 0, q, q.stride(0), tables, tile_item, tile_row0,
+                             tile_item.numel(), qstart, qlen, pos0, out, tokens, heads, kv_heads,
+                             0, scale, error, nsplit, part_o, part_ml, None, 0)
+        elif use_tma:
             ops.attention_tma(row_class, pages_map, 0, q, q.stride(0), tables, tile_item, tile_row0,
                               tile_item.numel(), qstart, qlen, pos0, out, tokens, heads, kv_heads,
                               0, scale, error, nsplit, part_o, part_ml, None, 0)
@@ -141,7 +148,8 @@ def run_attention(args, timer, decode: bool):
     pairs = args.batch * (new * past + new * (new + 1) / 2)
     flops = 4.0 * heads * hd * pairs
     return ms, io_bytes, flops, {"nsplit": nsplit, "tiles": tile_item.numel(),
-                                 "variant": ("tma" if use_tma else "mma") if row_class >= 0 else "generic"}
+                                 "variant": ("tc" if use_tc else "tma" if use_tma else "mma") if row_class >= 0
+                                 else "generic"}
 
 
 def run(args):
@@ -244,8 +252,9 @@ def main(argv=None) -> int:
     parser.add_argument("--n", type=int, default=37888)
     parser.add_argument("--k", type=int, default=3584)
     parser.add_argument("--nsplit", type=int, default=0, help="0 = the engine's choice")
-    parser.add_argument("--variant", default="mma", choices=["mma", "tma"],
-                        help="bfloat16 attention: cp.async loads or TMA loads")
+    parser.add_argument("--variant", default="mma", choices=["mma", "tma", "tc"],
+                        help="bfloat16 attention: mma.sync with cp.async loads, with TMA loads, "
+                             "or tcgen05 (prompt portions)")
     parser.add_argument("--top-k", type=int, default=0)
     parser.add_argument("--top-p", type=float, default=1.0)
     parser.add_argument("--warmup", type=int, default=3)
