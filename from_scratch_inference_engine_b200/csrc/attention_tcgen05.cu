@@ -123,6 +123,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
                  : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ float fast_exp2(float v) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a 128-byte-swizzled block
 __device__ __forceinline__ int swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
@@ -294,24 +299,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
 #pragma unroll
             for (int c = 0; c < BN; c += 32) tmem_ld32_issue(s_addr + c, sr + c);
             tmem_wait_ld();
-            float mx = -INFINITY;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains, not one
             const bool clear = k0 + BN - 1 < kend && k0 + BN - 1 <= pos && k0 > lowest;   // nothing to mask
             if (__all_sync(0xffffffffu, clear || !valid)) {
 #pragma unroll
-                for (int j = 0; j < BN; ++j) mx = fmaxf(mx, __uint_as_float(sr[j]));
-                if (!valid) mx = -INFINITY;
+                for (int j = 0; j < BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
             } else {
 #pragma unroll
                 for (int j = 0; j < BN; ++j) {
                     const int key = k0 + j;
                     const bool seen = key < kend && key <= pos && key > lowest;
                     if (!seen) sr[j] = 0xff800000u;                    // -inf
-                    mx = fmaxf(mx, __uint_as_float(sr[j]));
+                    mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
                 }
             }
-            const float m_new = fmaxf(m_run, mx);
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            if (!valid) mx = -INFINITY;
+            // The reference point of the exponentials moves only when the row's maximum has grown
+            // by more than 2^8 since it was set: until then p may exceed 1 (by at most 256x, exact
+            // enough in float and bfloat16), and O and the row sum need no rescaling.
+            float m_new = m_run;
+            if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * sc > 8.f)) m_new = mx;
             const float base = m_new == -INFINITY ? 0.f : m_new * sc;
-            const float corr = exp2f(m_run * sc - base);               // m_run = -inf gives 0
+            const float corr = m_new == m_run ? 1.f : fast_exp2(m_run * sc - base);    // m_run = -inf gives 0
             // the previous tile's P V must be complete before P is overwritten and O rescaled
             if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(&o_done, (i - 1) & 1))) {
                 if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
@@ -330,14 +340,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 tmem_wait_st();
             }
             // p = exp2(s * sc - base), row sum, P as bfloat16 in the swizzled layout
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int chunk = 0; chunk < BN / 8; ++chunk) {                 // 8 keys = one 16-byte chunk
                 float pv[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    pv[j] = valid ? exp2f(__uint_as_float(sr[chunk * 8 + j]) * sc - base) : 0.f;
-                    sum += pv[j];
+                    pv[j] = fast_exp2(fmaf(__uint_as_float(sr[chunk * 8 + j]), sc, -base));
+                    sum4[j & 3] += pv[j];
                 }
                 uint4 packed;
                 __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
@@ -345,6 +355,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(pv[2 * j], pv[2 * j + 1]);
                 *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
             }
+            const float sum = valid ? (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]) : 0.f;
             l_run = l_run * corr + sum;
             m_run = m_new;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P before the tensor core reads it
