@@ -41,8 +41,8 @@ constexpr int HALVES = HD / 64;         // 128-byte column halves of a row of he
 constexpr int ATOM_BYTES = 128 * 128;   // 128 rows x 128 bytes: one swizzled block
 constexpr int Q_BYTES = HALVES * ATOM_BYTES;
 constexpr int KV_BYTES = HALVES * ATOM_BYTES;          // one K or V tile
-constexpr int P_BYTES = (BN / 64) * ATOM_BYTES;        // P[128 rows, 128 keys] bf16
-constexpr int SMEM_BYTES = 1024 + Q_BYTES + P_BYTES + STAGES * 2 * KV_BYTES;
+constexpr int P_BYTES = (BN / 64) * ATOM_BYTES;        // P[128 rows, 128 keys] bf16; two of them
+constexpr int SMEM_BYTES = 1024 + Q_BYTES + 2 * P_BYTES + STAGES * 2 * KV_BYTES;
 constexpr uint32_t TMEM_COLS = 512;     // S0 | S1 | O  (128 + 128 + head_dim columns), power of two
 constexpr uint32_t COL_S0 = 0, COL_S1 = BN, COL_O = 2 * BN;
 enum { ERR_TC_PRODUCER = 31, ERR_TC_MMA = 32, ERR_TC_SOFTMAX = 33 };
@@ -136,9 +136,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
     unsigned char* q_s = smem;                               // [HALVES][128 rows][128 B]
-    unsigned char* p_s = q_s + Q_BYTES;                      // [2][128 rows][128 B]: keys 0-63 | 64-127
-    unsigned char* kv_s = p_s + P_BYTES;                     // [STAGES][K | V][HALVES][128 keys][128 B]
-    __shared__ uint64_t kv_full[STAGES], kv_empty[STAGES], s_full[2], p_ready, o_done;
+    unsigned char* p_s = q_s + Q_BYTES;                      // [2 buffers][2][128 rows][128 B]: keys 0-63 | 64-127
+    unsigned char* kv_s = p_s + 2 * P_BYTES;                     // [STAGES][K | V][HALVES][128 keys][128 B]
+    __shared__ uint64_t kv_full[STAGES], kv_empty[STAGES], s_full[2], p_ready, o_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -173,7 +173,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
         mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
-        mbar_init(&p_ready, 128); mbar_init(&o_done, 1);
+        mbar_init(&p_ready, 128); mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -181,7 +181,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int e = tid; e < (P_BYTES + STAGES * 2 * KV_BYTES) / 16; e += blockDim.x)
+    for (int e = tid; e < (2 * P_BYTES + STAGES * 2 * KV_BYTES) / 16; e += blockDim.x)
         reinterpret_cast<uint4*>(p_s)[e] = make_uint4(0, 0, 0, 0);
     for (int e = tid; e < BM * (HD / 8); e += blockDim.x) {
         const int r = e / (HD / 8), c = e - r * (HD / 8);     // 16-byte chunk c of row r
@@ -265,12 +265,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 const unsigned char* vd = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {         // 16 keys per instruction
-                    const uint64_t a = desc_k_major(p_s + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
+                    const uint64_t a = desc_k_major(p_s + (i & 1) * P_BYTES + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
                     const uint64_t b = desc_mn_major(vd + k * 16 * 128, ATOM_BYTES);
                     mma_ss(tmem + COL_O, a, b, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 mma_commit(&kv_empty[s]);                   // K_i and V_i may be overwritten
-                mma_commit(&o_done);                        // O holds tiles 0..i; P may be overwritten
+                mma_commit(&o_done[i & 1]);                 // O holds tiles 0..i; this P buffer may be overwritten
             }
         }
     } else {
@@ -322,13 +322,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * sc > 8.f)) m_new = mx;
             const float base = m_new == -INFINITY ? 0.f : m_new * sc;
             const float corr = m_new == m_run ? 1.f : fast_exp2(m_run * sc - base);    // m_run = -inf gives 0
-            // the previous tile's P V must be complete before P is overwritten and O rescaled
-            if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(&o_done, (i - 1) & 1))) {
+            // this tile's P buffer was last read by the P V of tile i - 2; O may be rescaled only
+            // after the P V of tile i - 1 (tile t reports to o_done[t % 2], phase t / 2)
+            const bool rescale = i > 0 && __any_sync(0xffffffffu, valid && corr != 1.f);
+            bool waited = true;
+            if (i >= 2) waited = mbar_wait(&o_done[i & 1], ((i - 2) >> 1) & 1);
+            if (rescale && waited) waited = mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1);
+            if (!__all_sync(0xffffffffu, waited)) {
                 if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
                 atomicExch(&abort_flag, 1); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (i > 0 && __any_sync(0xffffffffu, valid && corr != 1.f)) {
+            if (rescale) {
                 uint32_t orr[HD];
 #pragma unroll
                 for (int c = 0; c < HD; c += 32) tmem_ld32_issue(lane_base + COL_O + c, orr + c);
@@ -353,7 +358,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(pv[2 * j], pv[2 * j + 1]);
-                *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
+                *reinterpret_cast<uint4*>(p_s + (i & 1) * P_BYTES + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
             }
             const float sum = valid ? (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]) : 0.f;
             l_run = l_run * corr + sum;
@@ -364,7 +369,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         }
         // ---- the last P V, then normalise and store (or hand a partial result to the merge)
         bool have = ok && ntiles > 0;
-        if (have && !__all_sync(0xffffffffu, mbar_wait(&o_done, (ntiles - 1) & 1))) {
+        if (have && !__all_sync(0xffffffffu, mbar_wait(&o_done[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1))) {
             if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
             atomicExch(&abort_flag, 1); have = false;
         }

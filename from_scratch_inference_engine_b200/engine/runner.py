@@ -117,6 +117,7 @@ class ModelRunner:
                 cache.k_pages = pages[:, position, 0]
                 cache.v_pages = pages[:, position, 1]
                 cache.page_stride = pages.stride(0)
+                cache.pages, cache.entry_index = pages, position
             self.layer_caches.append(cache)
         self.error = runtime.error
         self._ring = PinnedRing()

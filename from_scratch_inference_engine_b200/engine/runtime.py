@@ -53,6 +53,17 @@ class Runtime:
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
+    def pages_map(self, pages: torch.Tensor):
+        """TMA descriptor of a cache group's page tensor (made once per tensor), or None when
+        the TMA-fed attention kernels do not take its head size or page size."""
+        key = ("pages_map", pages.data_ptr())
+        if key not in self._tables:
+            head_dim, page_size = pages.shape[-1], pages.shape[-2]
+            ok = (pages.dtype is torch.bfloat16 and head_dim in ops.ATTENTION_TC_HEAD_DIMS
+                  and page_size in ops.ATTENTION_TC_PAGES)
+            self._tables[key] = ops.PagesMap(pages, "tc") if ok else None
+        return self._tables[key]
+
     def shared_table(self, key, make: Callable[[], torch.Tensor]) -> torch.Tensor:
         """A constant table on the device, built once per distinct key."""
         if key not in self._tables:

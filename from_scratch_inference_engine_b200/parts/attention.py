@@ -119,13 +119,26 @@ class GqaAttention(Mixer):
         common = (cache.k_pages, cache.v_pages, cache.page_stride, group.page_size,
                   group.block_tables)
         if qkv.dtype is torch.bfloat16 and self.head_dim % 16 == 0:
+            # prompt portions (the last row class) run on tcgen05 in tiles of 128 rows where the
+            # head size and the page size allow it
+            pages_map = ctx.runtime.pages_map(cache.pages) if cache.pages is not None else None
+            class_rows = ops.ATTENTION_ROW_CLASSES
+            if pages_map is not None:
+                class_rows = class_rows[:-1] + (ops.ATTENTION_TC_ROWS,)
             for row_class, tiles, class_tokens, count, longest in \
-                    ctx.attention_row_classes(group_size, ops.ATTENTION_ROW_CLASSES):
+                    ctx.attention_row_classes(group_size, class_rows):
                 nsplit = splits(tiles.count * self.num_kv_heads, longest, row_class == 0)
                 part_o = part_ml = None
                 if nsplit > 1:
                     part_o = ctx.scratch("attention.part_o", nsplit * tokens * self.q_width)
                     part_ml = ctx.scratch("attention.part_ml", nsplit * tokens * self.num_heads * 2)
+                if pages_map is not None and row_class == len(class_rows) - 1:
+                    ops.attention_tc(pages_map, cache.entry_index, qkv, qkv.stride(0),
+                                     group.block_tables, tiles.item, tiles.row0, tiles.count,
+                                     ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out, tokens,
+                                     self.num_heads, self.num_kv_heads, self.window, self.scale,
+                                     ctx.error, nsplit, part_o, part_ml, class_tokens, count)
+                    continue
                 ops.attention_mma(row_class, qkv, qkv.stride(0), *common, tiles.item, tiles.row0,
                                   tiles.count, ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out,
                                   tokens, self.num_heads, self.num_kv_heads, self.head_dim,

@@ -79,6 +79,9 @@ class LayerCache:
     v_pages      the same for values
     writes       whether this call stores the new tokens' keys and values
     state        [num_slots, *StateNeed.shape] or None
+    pages        the group's page tensor [pages, entries, K|V, kv_heads, slots, head_dim] that
+                 k_pages and v_pages are views of (TMA-fed kernels address it as a whole)
+    entry_index  which of a page's entries this cache entry is
     """
 
     group: int = -1
@@ -87,6 +90,8 @@ class LayerCache:
     page_stride: int = 0
     writes: bool = True
     state: Optional[torch.Tensor] = None
+    pages: Optional[torch.Tensor] = None     # the group's whole page tensor
+    entry_index: int = 0                     # index of this entry inside a page of the group
 
 
 class Part:

@@ -46,6 +46,13 @@ TINY = {
                           vocab_size=200, rope_theta=10000.0, rms_norm_eps=1e-6,
                           tie_word_embeddings=True, max_position_embeddings=256),
               seed=3, std=0.1),
+    # head size 64 and pages of 16: prompt portions take the tcgen05 attention kernel
+    "E": dict(config=dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2",
+                          num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+                          num_key_value_heads=2, head_dim=64, intermediate_size=320,
+                          vocab_size=300, rope_theta=10000.0, rms_norm_eps=1e-6,
+                          tie_word_embeddings=False, max_position_embeddings=1024),
+              seed=5, std=0.05),
 }
 
 

@@ -18,6 +18,7 @@ REQUESTS = {
     "B": {"a": 130, "b": 33, "c": 100, "d": 64, "e": 7, "f": 1 + 32},
     "C": {"a": 150, "b": 40, "c": 97, "d": 64, "e": 23},
     "D": {"a": 70, "b": 35, "c": 48},
+    "E": {"a": 300, "b": 150, "c": 90, "d": 64},
 }
 
 
@@ -52,7 +53,7 @@ FAMILIES = {
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("family", list(FAMILIES))
-@pytest.mark.parametrize("name,page_size", [("A", 4), ("B", 8), ("C", 16), ("D", 16)])
+@pytest.mark.parametrize("name,page_size", [("A", 4), ("B", 8), ("C", 16), ("D", 16), ("E", 16)])
 def test_replay_matches_plain(folders, name, page_size, family, dtype):
     requests = requests_for(name)
     steps = FAMILIES[family](requests, 11)
