@@ -85,6 +85,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restric
                                        const int* __restrict__ rows, int hidden, float eps,
                                        int write_x) {
     __shared__ float scratch[32];
+    // a kernel launched as a programmatic dependent of this one may begin its set-up now; it
+    // waits for this grid to finish before it reads y (no effect on ordinary launches)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
     float* xr = x + s * hidden;

@@ -99,26 +99,33 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
     const int n0 = EPI == EPI_SWIGLU ? tile * (BM / 2) : tile * BM;
 
-    auto load_stage = [&](int kb, int s) {
+    auto load_weights = [&](int kb, int s) {
         unsigned char* a = smem + s * L::STAGE_BYTES;
-        unsigned char* b = a + L::A_BYTES;
-        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);     // the activation tile's bytes are counted here too
         if (EPI == EPI_SWIGLU) {                      // 64 gate rows, then the 64 up rows of the same outputs
             tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
             tma_load_2d(a + L::A_BYTES / 2, &map_w, kb * BK, p.up_row0 + n0, &full_bar[s]);
         } else {
             tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
         }
-        tma_load_2d(b, &map_x, kb * BK, 0, &full_bar[s]);
     };
+    auto load_activations = [&](int kb, int s) {
+        tma_load_2d(smem + s * L::STAGE_BYTES + L::A_BYTES, &map_x, kb * BK, 0, &full_bar[s]);
+    };
+    auto load_stage = [&](int kb, int s) { load_weights(kb, s); load_activations(kb, s); };
     if (threadIdx.x == 0) {
         for (int s = 0; s < L::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // the producer fills the ring at once; tensor memory is allocated meanwhile
-        for (int it = 0; it < L::STAGES && kb0 + it < kb1; ++it) load_stage(kb0 + it, it);
+        // The producer fills the ring at once; tensor memory is allocated meanwhile.  Weights do
+        // not depend on the kernel before this one: under programmatic dependent launch they are
+        // fetched while that kernel still runs; its output (the activations) is read only after
+        // griddepcontrol.wait.
+        for (int it = 0; it < L::STAGES && kb0 + it < kb1; ++it) load_weights(kb0 + it, it);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        for (int it = 0; it < L::STAGES && kb0 + it < kb1; ++it) load_activations(kb0 + it, it);
     }
     if (warp == 1) {        // one warp allocates the accumulator's columns of tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)), "r"(L::TMEM_COLS) : "memory");
@@ -128,6 +135,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_acc = tmem_base_slot;
+    // every thread: nothing of the previous kernel is touched before it has completed (thread 0
+    // waited above already); and the kernel after this one may start its own set-up now
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -280,13 +291,17 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Gemm
     config.blockDim = dim3(192, 1, 1);
     config.dynamicSmemBytes = L::SMEM;
     config.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = splits;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: this kernel's set-up and first weight tiles may overlap the
+    // tail of the kernel before it in the stream (it waits before touching that kernel's output)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    config.numAttrs = 1;
+    config.numAttrs = 2;
     return (int)cudaLaunchKernelEx(&config, kernel, map_w, map_x, p);
 }
 
