@@ -90,6 +90,8 @@ attn_mma_kernel(const AttnParams p) {
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw + S::Q_BYTES);
     bf16* Vs = Ks + (size_t)STAGES * BN * LDS;
 
+    grid_dependency_wait();
+    grid_dependents_go();
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     const int item = p.tile_item[tile];
@@ -374,6 +376,8 @@ attn_mma_kernel(const AttnParams p) {
 __global__ void attn_mma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                         bf16* __restrict__ out, int out_ld, int tokens, int heads,
                                         int nsplit, const int* __restrict__ token_list) {
+    grid_dependency_wait();
+    grid_dependents_go();
     const int tok = token_list ? token_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const size_t stride = (size_t)tokens * heads;              // (token, head) slots per split
@@ -412,8 +416,7 @@ static int launch(const AttnParams& p, int tiles, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(tiles, p.kv_heads, p.nsplit);
-    kernel<<<grid, S::THREADS, S::SMEM, stream>>>(p);
-    return (int)cudaGetLastError();
+    return launch_dependent(kernel, grid, dim3(S::THREADS), S::SMEM, stream, p);
 }
 
 }  // namespace fsie
@@ -465,9 +468,9 @@ int fsie_attn_mma(int row_class, const void* q, int q_ld, const void* k_pages, c
     if (count <= 0) return 0;
     dim3 cgrid(count, heads);
     if (nsplit > 32) return ERR_BAD_ARGUMENT;
-    attn_mma_combine_kernel<<<cgrid, HD >= 128 ? 64 : 32, 0, stream>>>(
-        part_o, part_ml, (bf16*)out, out_ld, tokens, heads, nsplit, combine_tokens);
-    return (int)cudaGetLastError();
+    return launch_dependent(attn_mma_combine_kernel, cgrid, dim3(HD >= 128 ? 64 : 32), 0, stream,
+                            (const float*)part_o, (const float*)part_ml, (bf16*)out, out_ld, tokens, heads, nsplit,
+                            combine_tokens);
 }
 
 }  // extern "C"

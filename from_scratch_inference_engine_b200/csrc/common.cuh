@@ -86,6 +86,31 @@ enum { DTYPE_F32 = 0, DTYPE_BF16 = 1 };
 // Return codes of the C entry points beyond cudaError_t values.
 enum { ERR_BAD_ARGUMENT = -1, ERR_UNSUPPORTED = -2 };
 
+// ---- programmatic dependent launch
+// A kernel launched with launch_dependent() may be scheduled while the kernel before it in the
+// stream is still running; it must call grid_dependency_wait() before it touches anything that
+// kernel wrote (and before it writes anything that kernel may read).  A kernel that calls
+// grid_dependents_go() lets the kernel after it be scheduled from that point on.  Both are
+// no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_go() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... Params, typename... Args>
+inline int launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 }  // namespace fsie
 
 #define FSIE_LAUNCH_CHECK() ((int)cudaGetLastError())

@@ -26,6 +26,8 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __rest
 template <typename T>
 __global__ void embed_gather_vec_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab, int* error) {
+    grid_dependency_wait();
+    grid_dependents_go();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -85,9 +87,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restric
                                        const int* __restrict__ rows, int hidden, float eps,
                                        int write_x) {
     __shared__ float scratch[32];
-    // a kernel launched as a programmatic dependent of this one may begin its set-up now; it
-    // waits for this grid to finish before it reads y (no effect on ordinary launches)
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    grid_dependency_wait();
+    grid_dependents_go();
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
     float* xr = x + s * hidden;
@@ -207,6 +208,8 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int ld, const int*
                                          long long page_stride, int page_size,
                                          int heads, int kv_heads, int head_dim, int rotary_dim,
                                          int write_cache, int* error) {
+    grid_dependency_wait();
+    grid_dependents_go();
     const int t = blockIdx.x;
     int pos = positions[t];
     if (rotary_dim > 0 && (pos < 0 || pos >= table_len)) {
@@ -284,6 +287,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter,
                                   long long chunks) {
+    grid_dependency_wait();
+    grid_dependents_go();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= chunks) return;
     const int per_row = inter / 8;
@@ -309,10 +314,8 @@ int fsie_embed_gather(const int* ids, const void* table, float* out, int tokens,
     if (hidden % 8 == 0) {
         const int threads = hidden / 8 >= 256 ? 256 : (hidden / 8 >= 128 ? 128 : 64);
         if (dtype == DTYPE_F32)
-            embed_gather_vec_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, error);
-        else
-            embed_gather_vec_kernel<bf16><<<tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, error);
-        return FSIE_LAUNCH_CHECK();
+            return launch_dependent(embed_gather_vec_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab, error);
+        return launch_dependent(embed_gather_vec_kernel<bf16>, tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab, error);
     }
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == DTYPE_F32)
@@ -332,19 +335,16 @@ int fsie_add_rmsnorm(float* x, const void* delta, const void* gain, int gain_is_
         const int nch = chunks <= 1024 ? 1 : (chunks <= 2048 ? 2 : 4);
         const int threads = ((chunks + nch - 1) / nch + 31) / 32 * 32;
 #define FSIE_NORM_VEC(T, G)                                                                      \
-        do {                                                                                     \
-            if (nch == 1) add_rmsnorm_vec_kernel<T, G, 1><<<num_rows, threads, 0, stream>>>(     \
-                x, (const T*)delta, (const G*)gain, (T*)y, rows, hidden, eps, write_x);          \
-            else if (nch == 2) add_rmsnorm_vec_kernel<T, G, 2><<<num_rows, threads, 0, stream>>>( \
-                x, (const T*)delta, (const G*)gain, (T*)y, rows, hidden, eps, write_x);          \
-            else add_rmsnorm_vec_kernel<T, G, 4><<<num_rows, threads, 0, stream>>>(              \
-                x, (const T*)delta, (const G*)gain, (T*)y, rows, hidden, eps, write_x);          \
-        } while (0)
-        if (dtype == DTYPE_F32) FSIE_NORM_VEC(float, float);
-        else if (gain_is_f32) FSIE_NORM_VEC(bf16, float);
-        else FSIE_NORM_VEC(bf16, bf16);
+        (nch == 1 ? launch_dependent(add_rmsnorm_vec_kernel<T, G, 1>, num_rows, threads, 0, stream, \
+                                     x, (const T*)delta, (const G*)gain, (T*)y, rows, hidden, eps, write_x) \
+         : nch == 2 ? launch_dependent(add_rmsnorm_vec_kernel<T, G, 2>, num_rows, threads, 0, stream, \
+                                       x, (const T*)delta, (const G*)gain, (T*)y, rows, hidden, eps, write_x) \
+                    : launch_dependent(add_rmsnorm_vec_kernel<T, G, 4>, num_rows, threads, 0, stream, \
+                                       x, (const T*)delta, (const G*)gain, (T*)y, rows, hidden, eps, write_x))
+        if (dtype == DTYPE_F32) return FSIE_NORM_VEC(float, float);
+        if (gain_is_f32) return FSIE_NORM_VEC(bf16, float);
+        return FSIE_NORM_VEC(bf16, bf16);
 #undef FSIE_NORM_VEC
-        return FSIE_LAUNCH_CHECK();
     }
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return ERR_UNSUPPORTED;
@@ -379,14 +379,12 @@ int fsie_rope_kv_write(void* qkv, int ld, const int* positions, const float* cos
                           kv_heads * (head_dim / 8);
         const int vthreads = items >= 512 ? 512 : (items + 31) / 32 * 32;
         if (dtype == DTYPE_F32)
-            rope_kv_write_vec_kernel<float><<<tokens, vthreads, 0, stream>>>(
+            return launch_dependent(rope_kv_write_vec_kernel<float>, tokens, vthreads, 0, stream,
                 (float*)qkv, ld, positions, cos_sin, table_len, slot_of, (float*)k_pages, (float*)v_pages,
                 page_stride, page_size, heads, kv_heads, head_dim, rotary_dim, write_cache, error);
-        else
-            rope_kv_write_vec_kernel<bf16><<<tokens, vthreads, 0, stream>>>(
-                (bf16*)qkv, ld, positions, cos_sin, table_len, slot_of, (bf16*)k_pages, (bf16*)v_pages,
-                page_stride, page_size, heads, kv_heads, head_dim, rotary_dim, write_cache, error);
-        return FSIE_LAUNCH_CHECK();
+        return launch_dependent(rope_kv_write_vec_kernel<bf16>, tokens, vthreads, 0, stream,
+            (bf16*)qkv, ld, positions, cos_sin, table_len, slot_of, (bf16*)k_pages, (bf16*)v_pages,
+            page_stride, page_size, heads, kv_heads, head_dim, rotary_dim, write_cache, error);
     }
     const int threads = 256;
     if (dtype == DTYPE_F32)
@@ -409,10 +407,8 @@ int fsie_swiglu(const void* gu, void* act, long long tokens, int inter, int dtyp
         const long long chunks = total / 8;
         const unsigned vblocks = (unsigned)((chunks + threads - 1) / threads);
         if (dtype == DTYPE_F32)
-            swiglu_vec_kernel<float><<<vblocks, threads, 0, stream>>>((const float*)gu, (float*)act, inter, chunks);
-        else
-            swiglu_vec_kernel<bf16><<<vblocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)act, inter, chunks);
-        return FSIE_LAUNCH_CHECK();
+            return launch_dependent(swiglu_vec_kernel<float>, vblocks, threads, 0, stream, (const float*)gu, (float*)act, inter, chunks);
+        return launch_dependent(swiglu_vec_kernel<bf16>, vblocks, threads, 0, stream, (const bf16*)gu, (bf16*)act, inter, chunks);
     }
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == DTYPE_F32)
