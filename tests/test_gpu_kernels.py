@@ -315,6 +315,16 @@ def test_attention_sizes(ops, kernel, dtype, heads, kv_heads, hd, page_size):
     assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
 
 
+@pytest.mark.parametrize("kernel,dtype", [k for k in KERNELS if k[0] != "generic" or k[1] is torch.float32])
+def test_attention_long_context(ops, kernel, dtype):
+    """Thousands of keys over hundreds of shuffled pages: a long prompt portion on top of a long
+    history, a decoded token, and a whole prompt, with and without split key ranges."""
+    case = PagedCase(dtype, 4, 2, 64, 16, items=[(3000, 300), (4100, 1), (0, 700)], seed=12)
+    for nsplit in (1, 7):
+        got = run_kernel(case, ops, kernel, nsplit)
+        assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+
+
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("nsplit", [2, 5, 32])
 def test_attention_split_keys(ops, kernel, dtype, nsplit):
