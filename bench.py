@@ -130,6 +130,74 @@ def prefill_flops(config, layers, tokens):
     return linear + attention
 
 
+SHAPE_1P5B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=28,
+                  hidden_size=1536, num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+                  intermediate_size=8960, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                  tie_word_embeddings=True, max_position_embeddings=32768, use_sliding_window=False)
+SHAPE_14B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=48,
+                 hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+                 intermediate_size=13824, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6,
+                 tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False)
+
+
+def serving_workload(args) -> int:
+    """Continuous batching at the Qwen2.5-1.5B shape: 256 requests, prompts of 64-2,048 uniform
+    token ids, 32-512 output tokens, half of them behind one common 512-token prefix, all
+    submitted up front.  Prints one JSON line: total tokens/s, time to first token and per
+    output token, preemptions, prefix hits."""
+    import numpy as np
+    import torch
+    from from_scratch_inference_engine_b200 import Engine, LoadedModel, SamplingParams, SeqStatus
+    from from_scratch_inference_engine_b200.config import config_from_dict
+
+    config = config_from_dict(dict(SHAPE_1P5B))
+    rng = np.random.default_rng(1)
+    requests = args.requests
+    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16", max_positions=4096)
+    engine = Engine(model, block_size=16, num_blocks=args.num_blocks, max_batch=256,
+                    enable_prefix_cache=True, max_step_tokens=2048)
+    prefix = rng.integers(0, config.vocab_size, size=512).tolist()
+    prompts, outputs = [], []
+    for r in range(requests):
+        length = int(rng.integers(64, 2049))
+        body = rng.integers(0, config.vocab_size, size=length).tolist()
+        prompts.append((prefix + body)[:max(length, 513)] if r % 2 == 0 else body)
+        outputs.append(int(rng.integers(32, 513)))
+    torch.cuda.synchronize()
+    start = time.perf_counter()
+    ids = [engine.add_request(p, SamplingParams(temperature=0.0), max_tokens=n)
+           for p, n in zip(prompts, outputs)]
+    first, done = {}, {}
+    while engine.has_work():
+        if engine.step() == 0:
+            raise RuntimeError("no request can make progress")
+        now = time.perf_counter()
+        for rid in ids:
+            if rid not in first and engine.output(rid):
+                first[rid] = now
+            if rid not in done and engine.status(rid) is SeqStatus.Finished:
+                done[rid] = now
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - start
+    produced = sum(len(engine.output(r)) for r in ids)
+    ttft = sorted((first[r] - start) * 1000.0 for r in ids)
+    tpot = [(done[r] - first[r]) * 1000.0 / (len(engine.output(r)) - 1) for r in ids
+            if len(engine.output(r)) > 1]
+    stats = engine.stats()
+    print(json.dumps({
+        "metric": "continuous batching tokens/s (Qwen2.5-1.5B shape, 256 requests)", "impl": "engine",
+        "value": (sum(map(len, prompts)) + produced) / wall, "unit": "tokens/s", "n_gpus": 1,
+        "output_tokens_per_s": produced / wall, "wall_s": wall, "requests": requests,
+        "prompt_tokens": sum(map(len, prompts)), "output_tokens": produced,
+        "ttft_ms": {"mean": statistics.fmean(ttft), "p50": ttft[len(ttft) // 2],
+                    "p90": ttft[int(len(ttft) * 0.9)]},
+        "tpot_ms_mean": statistics.fmean(tpot), "steps": stats["steps"],
+        "preemptions": stats["preemptions"], "prefix_hits": stats["prefix_hits"],
+        "num_blocks": args.num_blocks, "dtype": "bf16",
+        "data": "synthetic: random bf16 weights, uniform random token ids"}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -142,6 +210,11 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has")
     parser.add_argument("--prefill-tokens", type=int, default=2048)
     parser.add_argument("--points", default="1,64", help="extra decode batch sizes ('' = none)")
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                        help="decode: the default measurement; serving: continuous batching of 256 "
+                             "requests at the 1.5B shape")
+    parser.add_argument("--requests", type=int, default=256)
+    parser.add_argument("--num-blocks", type=int, default=16384)
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -154,6 +227,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
         return 2
+    if args.workload == "serving":
+        return serving_workload(args)
 
     import numpy as np
     import torch

@@ -19,6 +19,7 @@ prefixes cannot block admission.
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -54,6 +55,29 @@ class RequestCache:
     length: int = 0
     shared_tokens: int = 0        # leading tokens that came from shared prefix pages
     closed: bool = False
+    _arrays: Optional[list] = None    # per group (table length, int32 array) for the step's staging
+
+    def table_array(self, g: int):
+        """The block table of group g as an int32 numpy array, rebuilt only when it changed
+        (tables only grow at the end; a windowed group also turns entries into -1 in place,
+        which `note_release` reports)."""
+        import numpy as np
+        if self._arrays is None:
+            self._arrays = [None] * len(self.tables)
+        table = self.tables[g]
+        cached = self._arrays[g]
+        if cached is None or cached[0] > len(table):
+            array = np.asarray(table, dtype=np.int32)
+        elif cached[0] < len(table):
+            array = np.concatenate([cached[1], np.asarray(table[cached[0]:], dtype=np.int32)])
+        else:
+            return cached[1]
+        self._arrays[g] = (len(table), array)
+        return array
+
+    def note_release(self, g: int, block: int) -> None:
+        if self._arrays is not None and self._arrays[g] is not None and block < self._arrays[g][0]:
+            self._arrays[g][1][block] = -1
 
 
 @dataclass
@@ -65,15 +89,10 @@ class _PrefixEntry:
 
 
 def _hash_block(parent: int, tokens: Sequence[int]) -> int:
-    """FNV-1a over the parent hash and the page's tokens; matches are confirmed by
-    comparing tokens, so a collision costs a probe, not correctness."""
-    h = (parent ^ 0xCBF29CE484222325) & 0xFFFFFFFFFFFFFFFF
-    for token in tokens:
-        value = token & 0xFFFFFFFFFFFFFFFF
-        for shift in range(0, 64, 8):
-            h ^= (value >> shift) & 0xFF
-            h = (h * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
-    return h
+    """Hash of (parent page's hash, this page's tokens), chained like the reference's FNV-1a
+    (src/kvcache/block_manager.cpp:120-130) but with the interpreter's tuple hash; matches are
+    confirmed by comparing tokens, so a collision costs a probe, not correctness."""
+    return hash((parent, tuple(tokens)))
 
 
 def group_needs(needs: Sequence[Optional[CacheNeed]]) -> List[Tuple[CacheNeed, List[int]]]:
@@ -110,6 +129,13 @@ class CacheManager:
         # sharing a prefix needs every position's keys to be kept: no windowed group
         self.prefix_enabled = enable_prefix_cache and all(g.need.window == 0 for g in self.groups)
         self._prefix: Dict[int, List[_PrefixEntry]] = {}
+        # cached entries from least to most recently used, and by their page in group 0 (the
+        # pages of an entry are always shared together, so group 0 speaks for all of them);
+        # _evictable counts the entries nobody but the cache holds, kept up to date on every
+        # reference change so that free_pages() costs nothing per step
+        self._lru: "OrderedDict[int, _PrefixEntry]" = OrderedDict()
+        self._cached_page: Dict[int, _PrefixEntry] = {}
+        self._evictable = 0
         self._tick = 0
         self.prefix_hits = 0
 
@@ -124,11 +150,12 @@ class CacheManager:
     def close(self, handle: RequestCache) -> None:
         if handle.closed:
             raise RuntimeError(f"request {handle.request_id!r} was closed twice")
-        for pool, table in zip(self.pools, handle.tables):
+        for g, table in enumerate(handle.tables):
             for page in table:
                 if page >= 0:
-                    pool.free(page)
+                    self._free(g, page)
             table.clear()
+        handle._arrays = None
         self.slots.release(handle.slot)
         handle.length = 0
         handle.shared_tokens = 0
@@ -157,14 +184,17 @@ class CacheManager:
 
     def free_pages(self) -> List[int]:
         """Free pages per group, counting cached prefix pages nobody else holds."""
-        free = [pool.num_free for pool in self.pools]
-        if self._prefix:
-            for entries in self._prefix.values():
-                for entry in entries:
-                    if all(self.pools[g].ref_count(p) == 1 for g, p in enumerate(entry.pages)):
-                        for g in range(len(free)):
-                            free[g] += 1
-        return free
+        return [pool.num_free + self._evictable for pool in self.pools]
+
+    def _incref(self, g: int, page: int) -> None:
+        if g == 0 and page in self._cached_page and self.pools[0].ref_count(page) == 1:
+            self._evictable -= 1              # a request shares it again
+        self.pools[g].incref(page)
+
+    def _free(self, g: int, page: int) -> None:
+        self.pools[g].free(page)
+        if g == 0 and page in self._cached_page and self.pools[0].ref_count(page) == 1:
+            self._evictable += 1              # only the cache holds it now
 
     def can_reserve(self, handle: RequestCache, n_new: int,
                     budget: Optional[List[int]] = None) -> bool:
@@ -201,8 +231,9 @@ class CacheManager:
             table = handle.tables[g]
             for block in range(min(len(table), max(0, first_needed) // self.page_size)):
                 if table[block] >= 0:
-                    self.pools[g].free(table[block])
+                    self._free(g, table[block])
                     table[block] = -1
+                    handle.note_release(g, block)
 
     def _allocate(self, g: int) -> int:
         if self.pools[g].num_free == 0:
@@ -230,8 +261,9 @@ class CacheManager:
                 break
             self._tick += 1
             found.last_used = self._tick
+            self._lru.move_to_end(id(found))
             for g, page in enumerate(found.pages):
-                self.pools[g].incref(page)
+                self._incref(g, page)
                 handle.tables[g].append(page)
             parent = h
             matched += ps
@@ -256,35 +288,42 @@ class CacheManager:
             entries = self._prefix.setdefault(h, [])
             if not any(e.parent == parent and e.tokens == span for e in entries):
                 pages = tuple(table[b] for table in handle.tables)
+                if pages[0] in self._cached_page:
+                    parent = h            # the page already backs another entry: share no further
+                    continue
                 for g, page in enumerate(pages):
                     self.pools[g].incref(page)
                 self._tick += 1
-                entries.append(_PrefixEntry(parent, span, pages, self._tick))
+                entry = _PrefixEntry(parent, span, pages, self._tick)
+                entries.append(entry)
+                self._lru[id(entry)] = entry
+                self._cached_page[pages[0]] = entry
             parent = h
 
-    def _evict_one(self) -> bool:
-        victim = None
-        for h, entries in self._prefix.items():
-            for index, entry in enumerate(entries):
-                if all(self.pools[g].ref_count(p) == 1 for g, p in enumerate(entry.pages)):
-                    if victim is None or entry.last_used < victim[2].last_used:
-                        victim = (h, index, entry)
-        if victim is None:
-            return False
-        h, index, entry = victim
+    def _drop_entry(self, entry: _PrefixEntry) -> None:
+        h = _hash_block(entry.parent, entry.tokens)
+        bucket = self._prefix[h]
+        bucket.remove(entry)
+        if not bucket:
+            del self._prefix[h]
+        del self._lru[id(entry)]
+        del self._cached_page[entry.pages[0]]
+        if self.pools[0].ref_count(entry.pages[0]) == 1:
+            self._evictable -= 1
         for g, page in enumerate(entry.pages):
             self.pools[g].free(page)
-        del self._prefix[h][index]
-        if not self._prefix[h]:
-            del self._prefix[h]
-        return True
+
+    def _evict_one(self) -> bool:
+        """Drop the least recently used entry that only the cache holds."""
+        for entry in self._lru.values():
+            if self.pools[0].ref_count(entry.pages[0]) == 1:
+                self._drop_entry(entry)
+                return True
+        return False
 
     def clear_prefix_cache(self) -> None:
-        for entries in self._prefix.values():
-            for entry in entries:
-                for g, page in enumerate(entry.pages):
-                    self.pools[g].free(page)
-        self._prefix.clear()
+        for entry in list(self._lru.values()):
+            self._drop_entry(entry)
 
     # ----------------------------------------------------------------- checking
     def check(self) -> None:
@@ -303,3 +342,7 @@ class CacheManager:
                 if count != pool.ref_count(page):
                     raise AssertionError(f"group {g} page {page}: {count} holders but "
                                          f"reference count {pool.ref_count(page)}")
+        evictable = sum(1 for e in self._lru.values() if self.pools[0].ref_count(e.pages[0]) == 1)
+        if evictable != self._evictable or len(self._lru) != sum(map(len, self._prefix.values())):
+            raise AssertionError(f"prefix cache accounting: {self._evictable} evictable counted, "
+                                 f"{evictable} found")

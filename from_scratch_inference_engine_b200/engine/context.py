@@ -98,7 +98,7 @@ class StepContext:
         for page_size, tables in group_tables:
             width = table_width or max(1, max((len(t) for t in tables), default=1))
             table = np.full((I, width), -1, dtype=np.int32)
-            for i, row in enumerate(tables):
+            for i, row in enumerate(tables):          # rows are lists or ready int32 arrays
                 table[i, :len(row)] = row
             block = positions // page_size
             page = table[token_item, block] if T else np.zeros(0, np.int32)

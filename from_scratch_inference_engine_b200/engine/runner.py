@@ -176,7 +176,7 @@ class ModelRunner:
             graph = self._graphs[key] = _DecodeGraph(self, batch, width)
         graph.fill([e.tokens[0] for e in entries], [e.handle.length for e in entries],
                    [e.handle.slot for e in entries],
-                   [[e.handle.tables[g] for e in entries] for g in range(len(cache.groups))])
+                   [[e.handle.table_array(g) for e in entries] for g in range(len(cache.groups))])
         logits = graph.replay()
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if not wanted:
@@ -213,7 +213,7 @@ class ModelRunner:
                 fresh_slots.append(entry.handle.slot)
             want_rows += [len(token_ids) + w for w in entry.want]
             token_ids += list(entry.tokens)
-        tables = [(cache.page_size, [e.handle.tables[g] for e in entries])
+        tables = [(cache.page_size, [e.handle.table_array(g) for e in entries])
                   for g in range(len(cache.groups))]
         ctx = StepContext(self.runtime, self._ring, self._scratch, self.error, token_ids, q_start,
                           q_len, pos0, slots, tables)

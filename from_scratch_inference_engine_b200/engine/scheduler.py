@@ -55,6 +55,18 @@ class Sequence_:
     def context(self) -> List[int]:
         return self.prompt + self.output
 
+    def context_length(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    def context_slice(self, start: int, stop: int) -> List[int]:
+        """context()[start:stop] without building the whole list."""
+        n = len(self.prompt)
+        if stop <= n:
+            return self.prompt[start:stop]
+        if start >= n:
+            return self.output[start - n:stop - n]
+        return self.prompt[start:] + self.output[:stop - n]
+
 
 @dataclass
 class PlanItem:
@@ -108,7 +120,7 @@ class Scheduler:
         cache = self.cache
         while self.waiting and len(self.running) < self.max_batch and cache.can_open():
             seq = self.sequences[self.waiting[0]]
-            first = min(len(seq.context()), self.max_step_tokens)
+            first = min(seq.context_length(), self.max_step_tokens)
             # pages the first portion needs, seen against what is free before this step
             if any(cache.blocks_for(first) > free for free in cache.free_pages()):
                 break
@@ -147,14 +159,14 @@ class Scheduler:
                 seq = self.sequences[sid]
                 if seq.prefilled or tokens_left <= 0:
                     continue
-                context = seq.context()
+                total = seq.context_length()
                 handle = seq.handle
-                if handle.length == 0 and not any(handle.tables):
-                    cap = ((len(context) - 1) // cache.page_size) * cache.page_size
+                if cache.prefix_enabled and handle.length == 0 and not any(handle.tables):
+                    cap = ((total - 1) // cache.page_size) * cache.page_size
                     if cap > 0:
-                        cache.acquire_prefix(handle, context[:cap])
+                        cache.acquire_prefix(handle, seq.context_slice(0, cap))
                         pages_left = [min(a, b) for a, b in zip(pages_left, cache.free_pages())]
-                remaining = len(context) - handle.length
+                remaining = total - handle.length
                 chunk = min(remaining, tokens_left)
                 # shrink the portion to the pages that are left
                 room = min((len(t) + left) * cache.page_size - handle.length
@@ -163,7 +175,7 @@ class Scheduler:
                 chunk = min(chunk, room)
                 if chunk <= 0 or not take(handle, chunk):
                     continue
-                portion = context[handle.length:handle.length + chunk]
+                portion = seq.context_slice(handle.length, handle.length + chunk)
                 items.append(PlanItem(seq, portion, chunk == remaining, True))
                 tokens_left -= chunk
             if items or len(self.running) <= 1 or not self._preempt_youngest():
@@ -201,5 +213,5 @@ class Scheduler:
                 self.cache.close(seq.handle)
                 seq.handle = None
                 self.running.remove(seq.id)
-            elif item.was_prefill:
-                self.cache.register_prefix(seq.handle, seq.context()[:seq.handle.length])
+            elif item.was_prefill and self.cache.prefix_enabled:
+                self.cache.register_prefix(seq.handle, seq.context_slice(0, seq.handle.length))
