@@ -49,6 +49,10 @@ enum { ERR_TC_PRODUCER = 31, ERR_TC_MMA = 32, ERR_TC_SOFTMAX = 33 };
 
 struct TcExtra { int entries, entry; int* error; };
 
+}  // namespace fsie
+#include "attention_combine.cuh"
+namespace fsie {
+
 // 64-bit shared-memory matrix descriptors (version 1, 128-byte swizzle).
 // K-major: rows of 128 bytes, 8-row groups 1,024 bytes apart.
 __device__ __forceinline__ uint64_t desc_k_major(const void* p) {
@@ -419,35 +423,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     }
 }
 
-// Merge the key splits of one (token, head); same arithmetic as attention_generic.cu.
-__global__ void attn_tc_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       bf16* __restrict__ out, int out_ld, int tokens, int heads,
-                                       int nsplit, const int* __restrict__ token_list) {
-    const int tok = token_list ? token_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
-    const int lane = threadIdx.x & 31;
-    const size_t stride = (size_t)tokens * heads, slot = (size_t)tok * heads + h;
-    float mz = -INFINITY, lz = 0.f;
-    if (lane < nsplit) {
-        mz = part_ml[(lane * stride + slot) * 2];
-        lz = part_ml[(lane * stride + slot) * 2 + 1];
-    }
-    const float mmax = warp_max(mz);
-    const float wz = mz == -INFINITY ? 0.f : __expf(mz - mmax);
-    const float denom = warp_sum(lz * wz);
-    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-    for (int d = threadIdx.x * 2; d < HD; d += blockDim.x * 2) {
-        float a0 = 0.f, a1 = 0.f;
-        for (int z = 0; z < nsplit; ++z) {
-            const float w = __shfl_sync(0xffffffffu, wz, z);
-            if (w != 0.f) {
-                const float2 v = *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d);
-                a0 += v.x * w; a1 += v.y * w;
-            }
-        }
-        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * out_ld + h * HD + d) = __floats2bfloat162_rn(a0 * inv, a1 * inv);
-    }
-}
-
 }  // namespace fsie
 
 using namespace fsie;
@@ -517,7 +492,7 @@ int fsie_attn_tc(const void* pages_map, int entries, int entry, const void* q, i
     if (rc != 0 || nsplit == 1) return rc;
     const int count = combine_tokens ? num_combine : tokens;
     if (count <= 0) return 0;
-    attn_tc_combine_kernel<<<dim3(count, heads), HD >= 128 ? 64 : 32, 0, stream>>>(
+    attn_combine_kernel<<<dim3(count, heads), HD >= 128 ? 64 : 32, 0, stream>>>(
         part_o, part_ml, (bf16*)out, out_ld, tokens, heads, nsplit, combine_tokens);
     return (int)cudaGetLastError();
 }

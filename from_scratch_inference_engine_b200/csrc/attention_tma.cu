@@ -77,6 +77,10 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+}  // namespace fsie
+#include "attention_combine.cuh"
+namespace fsie {
+
 template <int WARPS_M, int WARPS_K, int STAGES>
 struct Shape {
     static constexpr int BM = 16 * WARPS_M;
@@ -394,38 +398,6 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams 
     }
 }
 
-// Merge the key splits of one (token, head); same arithmetic as attention_generic.cu.  The
-// weight e^(m_z - M) of split z is computed once by lane z (nsplit <= 32) and broadcast.
-__global__ void attn_tma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                        bf16* __restrict__ out, int out_ld, int tokens, int heads,
-                                        int nsplit, const int* __restrict__ token_list) {
-    const int tok = token_list ? token_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
-    const int lane = threadIdx.x & 31;
-    const size_t stride = (size_t)tokens * heads;              // (token, head) slots per split
-    const size_t slot = (size_t)tok * heads + h;
-    float mz = -INFINITY, lz = 0.f;
-    if (lane < nsplit) {
-        mz = part_ml[(lane * stride + slot) * 2];
-        lz = part_ml[(lane * stride + slot) * 2 + 1];
-    }
-    const float mmax = warp_max(mz);
-    const float wz = mz == -INFINITY ? 0.f : __expf(mz - mmax);
-    const float denom = warp_sum(lz * wz);
-    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-    for (int d = threadIdx.x * 2; d < HD; d += blockDim.x * 2) {
-        float a0 = 0.f, a1 = 0.f;
-        for (int z = 0; z < nsplit; ++z) {
-            const float w = __shfl_sync(0xffffffffu, wz, z);
-            if (w != 0.f) {
-                const float2 v = *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d);
-                a0 += v.x * w; a1 += v.y * w;
-            }
-        }
-        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * out_ld + h * HD + d) =
-            __floats2bfloat162_rn(a0 * inv, a1 * inv);
-    }
-}
-
 template <int WARPS_M, int WARPS_K, int STAGES>
 static int launch(const CUtensorMap& map, const AttnParams& p, const TmaExtra& x, int tiles, cudaStream_t stream) {
     using S = Shape<WARPS_M, WARPS_K, STAGES>;
@@ -508,7 +480,7 @@ int fsie_attn_tma(int row_class, const void* pages_map, int entries, int entry, 
     const int count = combine_tokens ? num_combine : tokens;
     if (count <= 0) return 0;
     dim3 cgrid(count, heads);
-    attn_tma_combine_kernel<<<cgrid, HD >= 128 ? 64 : 32, 0, stream>>>(
+    attn_combine_kernel<<<cgrid, HD >= 128 ? 64 : 32, 0, stream>>>(
         part_o, part_ml, (bf16*)out, out_ld, tokens, heads, nsplit, combine_tokens);
     return (int)cudaGetLastError();
 }
