@@ -151,6 +151,10 @@ def library_path(name: str, defines: Sequence[str] = ()) -> Path:
             _say(f"built {target.name} in {time.time() - started:.0f} s")
         finally:
             fcntl.flock(lock_file, fcntl.LOCK_UN)
+            try:
+                lock_path.unlink()
+            except OSError:
+                pass
     return target
 
 
