@@ -124,7 +124,8 @@ class ModelRunner:
         self._scratch: Dict[str, torch.Tensor] = {}
         # steps of single tokens replay a captured graph (not for mixers with state of their
         # own, whose Python-side loops a graph would freeze)
-        self.cuda_graphs = cuda_graphs and all(s is None for s in self.states)
+        self.cuda_graphs = (cuda_graphs and all(s is None for s in self.states)
+                            and getattr(model, "capturable", False))
         self._graphs: Dict[tuple, _DecodeGraph] = {}
         self._graph_pool = None
         self.vocab_size = model.spec.vocab_size

@@ -46,6 +46,8 @@ class GqaAttention(Mixer):
     [q_width + 2 kv_width, hidden], made at bind.
     """
 
+    capturable = True
+
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, qkv_bias: bool, position: PartSpec, window: int = 0):
         if num_heads % num_kv_heads:

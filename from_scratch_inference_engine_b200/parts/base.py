@@ -98,6 +98,11 @@ class Part:
     """Base of all parts: tensor declarations and binding."""
 
     prefix: str = ""
+    # True when forward launches the same kernels on the same addresses whatever the data
+    # holds (no host read of a device value, no loop over its values).  Only a model all of
+    # whose parts say so has its decode steps captured in CUDA graphs; a part says nothing
+    # and is safe.
+    capturable: bool = False
 
     def tensor_specs(self) -> List[TensorSpec]:
         return []

@@ -32,6 +32,10 @@ class PreNormBlock(Part):
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
+    @property
+    def capturable(self) -> bool:
+        return all(part.capturable for part in self.parts())
+
     def tensor_specs(self) -> List[TensorSpec]:
         return [spec for part in self.parts() for spec in part.tensor_specs()]
 

@@ -17,6 +17,8 @@ class SwiGluMlp(Part):
     src/model/nn.cpp:74-88).  gate and up are one product over the stacked weight
     [2 * intermediate, hidden]: gate rows first, then up rows."""
 
+    capturable = True
+
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int):
         self.prefix, self.hidden_size = prefix, int(hidden_size)
         self.intermediate_size = int(intermediate_size)

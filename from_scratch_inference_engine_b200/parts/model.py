@@ -72,6 +72,11 @@ class DecoderModel:
             block.bind(placed, runtime)
 
     # -------------------------------------------------------------------- needs
+    @property
+    def capturable(self) -> bool:
+        """Whether a step launches the same kernels whatever the data (every part says so)."""
+        return self.final_norm.capturable and all(block.capturable for block in self.blocks)
+
     def cache_needs(self) -> List[Optional[CacheNeed]]:
         """Need of each cache entry (index = position in the run order); None where the
         entry is not written by its own call or the mixer keeps no keys."""

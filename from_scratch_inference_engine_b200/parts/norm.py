@@ -19,6 +19,8 @@ class RMSNorm(Part):
     forward adds `delta` into the float32 residual `x` first (one kernel, one pass over x).
     """
 
+    capturable = True
+
     def __init__(self, prefix: str, width: int, eps: float):
         self.prefix, self.width, self.eps = prefix, int(width), float(eps)
         self.gain: Optional[torch.Tensor] = None

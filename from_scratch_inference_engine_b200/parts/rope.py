@@ -26,6 +26,8 @@ class RotaryEncoding(Part):
     """Half-rotation pairs (i, i + rotary_dim/2) over the first `rotary_dim` of each head.
     The rotation itself runs inside the mixer's kernel; this part owns the table."""
 
+    capturable = True
+
     def __init__(self, prefix: str, theta: float, rotary_dim: int, max_position: int = 0):
         if rotary_dim % 2:
             raise ValueError("rotary_dim must be even")
@@ -45,6 +47,8 @@ class RotaryEncoding(Part):
 @register_part("position", "none")
 class NoPositionEncoding(Part):
     """No position encoding: queries and keys are used as projected."""
+
+    capturable = True
 
     rotary_dim = 0
 

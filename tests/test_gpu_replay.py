@@ -90,6 +90,30 @@ def test_long_decoding(folders, dtype):
     assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_decode_steps_equal_uncaptured_ones(folders, dtype):
+    """Steps of single tokens replay CUDA graphs; the same kernels launched one by one give
+    the same logits beyond rounding (a graph is captured for a rounded-up table width and
+    may split the keys otherwise), across batch sizes that change and tables that grow."""
+    requests = requests_for("B")
+    steps = helpers.trace_mixed(requests, seed=7, decode_tail=20)
+    need = helpers.live_tokens_needed(steps, round_to=8)
+    runner = build_runner(folders["B"], dtype, need, 8)
+    assert runner.cuda_graphs
+    captured = helpers.run_trace_in_process(runner, steps)
+    assert runner._graphs, "no decode step went through a graph"
+    plain_runner = build_runner(folders["B"], dtype, need, 8)
+    plain_runner.cuda_graphs = False
+    direct = helpers.run_trace_in_process(plain_runner, steps)
+    assert captured.keys() == direct.keys()
+    if dtype == "float32":
+        for key, row in captured.items():
+            assert np.abs(row - direct[key]).max() < 2e-5, key
+    for rows in (captured, direct):
+        worst, scale, bad = helpers.compare_rows(rows, requests, folders["B"], TOLERANCE[dtype])
+        assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
+
+
 def test_cutting_does_not_change_float32_beyond_rounding(folders):
     """The same request whole and in portions: rows agree far inside the tolerance."""
     requests = {"x": helpers.random_ids(384, 90, 3)}
