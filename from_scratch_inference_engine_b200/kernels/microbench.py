@@ -3,7 +3,8 @@
     python -m from_scratch_inference_engine_b200.kernels.microbench KERNEL [options]
 
 KERNEL: attention_decode, attention_prefill, add_rmsnorm, rope_kv_write, swiglu, argmax,
-sample, linear (the library product as the engine calls it), gemm_f32.
+sample, linear (the library product as the engine calls it), gemm_f32, gemm_decode,
+gemm_decode_swiglu, gemm_tiles, gemm_tiles_swiglu (the engine's own tcgen05 products).
 
 Each kernel is timed with CUDA events over --iters launches after --warmup launches; between
 launches a buffer larger than L2 is read so that inputs come from HBM (read, not written:
@@ -209,6 +210,17 @@ def run(args):
         splits = args.nsplit if args.nsplit > 0 else ops.gemm_decode_splits(tiles, k, sms)
         ms = timer(lambda: ops.gemm_decode(weight, x, out, None, error, splits))
         extra = {"splits": splits, "error": int(error.item())}
+        nbytes, flops = (m * k + w.shape[0] * k + m * n) * elem, 2.0 * m * w.shape[0] * k
+    elif args.kernel in ("gemm_tiles", "gemm_tiles_swiglu"):
+        m, n, k = args.tokens, args.n, args.k
+        swiglu = args.kernel == "gemm_tiles_swiglu"
+        x, w = rand(m, k).to(dtype), rand(2 * n if swiglu else n, k).to(dtype)
+        weight = ops.TiledWeight(w, swiglu=swiglu)
+        out = torch.empty((m, n), dtype=dtype, device="cuda")
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        ms = timer(lambda: ops.gemm_tiles(weight, x, out, None, error, sms))
+        extra = {"error": int(error.item())}
         nbytes, flops = (m * k + w.shape[0] * k + m * n) * elem, 2.0 * m * w.shape[0] * k
     elif args.kernel in ("linear", "gemm_f32"):
         m, n, k = args.tokens, args.n, args.k

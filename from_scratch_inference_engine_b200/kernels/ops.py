@@ -504,6 +504,68 @@ def gemm_decode(weight: DecodeWeight, x: torch.Tensor, out: torch.Tensor,
     return out
 
 
+_gemm_tiles = None
+
+
+def gemm_tiles_lib():
+    global _gemm_tiles
+    if _gemm_tiles is None:
+        lib = build.load_library("gemm_tiles")
+        i, ll, p = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_gemm_tiles_map_bytes.argtypes = []
+        lib.fsie_gemm_tiles_weight_map.argtypes = [p, p, ll, ll]
+        lib.fsie_gemm_tiles.argtypes = [p, p, ll, p, ll, p, i, i, i, i, i, i, p, p]
+        for name in ("fsie_gemm_tiles_map_bytes", "fsie_gemm_tiles_weight_map", "fsie_gemm_tiles"):
+            getattr(lib, name).restype = i
+        _gemm_tiles = lib
+    return _gemm_tiles
+
+
+class TiledWeight:
+    """A bfloat16 weight [rows, K] prepared for `gemm_tiles`: its TMA descriptor (boxes of 128
+    rows).  For SwiGLU the weight holds the gate rows and then as many up rows."""
+
+    def __init__(self, weight: torch.Tensor, swiglu: bool = False):
+        _need(weight, torch.bfloat16, "weight")
+        rows, k = weight.shape
+        if k % 8:
+            raise KernelError("gemm_tiles: K must be a multiple of 8")
+        if swiglu and rows % 2:
+            raise KernelError("gemm_tiles: a SwiGLU weight holds gate rows and as many up rows")
+        lib = gemm_tiles_lib()
+        self.weight, self.swiglu, self.k = weight, swiglu, k
+        self.n = rows // 2 if swiglu else rows
+        self.map = ctypes.create_string_buffer(lib.fsie_gemm_tiles_map_bytes() + 64)
+        offset = (-ctypes.addressof(self.map)) % 64
+        self.map_ptr = ctypes.c_void_p(ctypes.addressof(self.map) + offset)
+        _check(lib.fsie_gemm_tiles_weight_map(self.map_ptr, _ptr(weight), rows, k),
+               "gemm_tiles weight map")
+
+
+def gemm_tiles(weight: TiledWeight, x: torch.Tensor, out: torch.Tensor,
+               bias: Optional[torch.Tensor], error: torch.Tensor, blocks: int) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w.T (+ bias), or silu(x @ gate.T) * (x @ up.T), any M; out is
+    bfloat16 (or float32 for the plain product).  `blocks`: size of the persistent grid."""
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(out, None, "out", contiguous=False)
+    rows, k = x.shape
+    if k != weight.k or x.stride(1) != 1 or x.stride(0) % 8:
+        raise KernelError("gemm_tiles: x does not fit the weight (rows must start on 16 bytes)")
+    if (out.shape[0] != rows or out.shape[1] != weight.n or out.stride(1) != 1
+            or out.dtype not in (torch.bfloat16, torch.float32)
+            or (weight.swiglu and out.dtype is torch.float32)):
+        raise KernelError("gemm_tiles: out does not fit")
+    if bias is not None:
+        _need(bias, torch.bfloat16, "bias")
+        if weight.swiglu or bias.numel() != weight.n:
+            raise KernelError("gemm_tiles: bias does not fit")
+    _check(gemm_tiles_lib().fsie_gemm_tiles(
+        weight.map_ptr, _ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(bias), rows,
+        weight.n, k, int(weight.swiglu), int(out.dtype is torch.float32), blocks, _ptr(error),
+        _stream()), "gemm_tiles")
+    return out
+
+
 # --------------------------------------------------------------------------- sampling
 ARGMAX_PARTS = 32      # blocks per row of the two-stage argmax
 

@@ -481,3 +481,61 @@ def test_gemm_decode_swiglu_epilogue(ops, tokens, inter, k, splits):
     ops.gemm_decode(ops.DecodeWeight(w, swiglu=True), x, out, None, error, splits)
     assert error.item() == 0
     assert (out.double() - want).abs().max().item() < 2.5e-2 * want.abs().max().item()
+
+
+# -------------------------------------------------------- tcgen05 product for many tokens
+@pytest.mark.parametrize("rows", [1, 100, 129, 256, 300, 700])
+@pytest.mark.parametrize("n,k,blocks", [(384, 512, 148), (200, 136, 148), (520, 72, 2), (1288, 1024, 3)])
+def test_gemm_tiles_tcgen05(ops, rows, n, k, blocks):
+    """Tiles of 256 x 256 with ragged edges in every direction; with fewer blocks than tiles a
+    block walks over several tiles and reuses its stages and its tensor memory."""
+    torch.manual_seed(rows + n)
+    x_full = dev(torch.randn(rows, k + 8), torch.bfloat16)
+    x = x_full[:, :k]                                          # rows 16 bytes further apart than k
+    w = dev(torch.randn(n, k) / math.sqrt(k), torch.bfloat16)
+    bias = dev(torch.randn(n), torch.bfloat16)
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want = x.double() @ w.double().T
+    weight = ops.TiledWeight(w)
+    out_full = torch.full((rows, n + 8), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tiles(weight, x, out_full[:, :n], None, error, blocks)
+    assert error.item() == 0
+    assert torch.isnan(out_full[:, n:]).all()                  # nothing beyond the last column
+    assert (out_full[:, :n].double() - want).abs().max().item() < 1.6e-2 * want.abs().max().item()
+    out32 = torch.full((rows, n), float("nan"), dtype=torch.float32, device="cuda")
+    ops.gemm_tiles(weight, x, out32, bias, error, blocks)
+    assert error.item() == 0
+    assert (out32.double() - want - bias.double()).abs().max().item() < 2e-3 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("rows,inter,k,blocks", [(300, 320, 512, 148), (77, 100, 264, 148), (513, 712, 128, 4),
+                                                 (256, 18944, 3584, 148)])
+def test_gemm_tiles_swiglu_epilogue(ops, rows, inter, k, blocks):
+    torch.manual_seed(inter)
+    x = dev(torch.randn(rows, k), torch.bfloat16)
+    w = dev(torch.randn(2 * inter, k) / math.sqrt(k), torch.bfloat16)
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gate_up = (x.double() @ w.double().T).to(torch.bfloat16).double()      # rounded as the unfused path
+    want = plain.silu_mul(gate_up[:, :inter], gate_up[:, inter:])
+    out = torch.full((rows, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tiles(ops.TiledWeight(w, swiglu=True), x, out, None, error, blocks)
+    assert error.item() == 0
+    assert (out.double() - want).abs().max().item() < 2.5e-2 * want.abs().max().item()
+
+
+def test_gemm_tiles_one_key_block_stands_out(ops):
+    """One k-block of one row tile carries the whole result: a stage that is read too early,
+    too late or for the wrong tile shows as a gross error, not as noise."""
+    rows, n, k = 600, 512, 1024
+    x = torch.zeros(rows, k)
+    w = torch.zeros(n, k)
+    x[:, 640:704] = torch.randn(rows, 64)
+    w[:, 640:704] = torch.randn(n, 64)
+    x[300:, :64] = 1.0                                         # rows of the second tile also see k-block 0
+    w[:, :64] = 0.5
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.empty((rows, n), dtype=torch.float32, device="cuda")
+    ops.gemm_tiles(ops.TiledWeight(dev(w, torch.bfloat16)), dev(x, torch.bfloat16), out, None, error, 2)
+    want = dev(x, torch.bfloat16).double() @ dev(w, torch.bfloat16).double().T
+    assert error.item() == 0
+    assert (out.double() - want).abs().max().item() < 1e-3 * want.abs().max().item()
