@@ -3,23 +3,31 @@
 // tensor cores, with the bias add or the SwiGLU activation applied to the accumulator before
 // anything is written.
 //
-// A persistent grid of one block per SM walks over 256 x 256 output tiles.  Per k-block of 64
-// one thread issues four TMA boxes (two of x, two of w; 128 rows x 128 bytes each, 128-byte
-// swizzle) into a ring of three 64 KB stages; one thread issues eight tcgen05.mma of
-// 128 x 256 x 16 - the two row halves of the tile share the w boxes in shared memory - into
-// two accumulators that fill all 512 columns of tensor memory; eight warps read a finished
-// tile back (tcgen05.ld), apply the epilogue and store rows while the copy engine already
-// fetches the next tile's first stages.
+// Two blocks on neighbouring SMs (a cluster of two) share every 256 x 256 output tile: each
+// loads 128 rows of x and 128 rows of w per k-block of 64 (two TMA boxes of 16 KB into a ring
+// of six 32 KB stages), one thread of the first block issues tcgen05.mma with cta_group::2 -
+// 256 x 256 x 16 over both blocks' shared memory - and each block keeps its 128 rows of the
+// result in its own tensor memory.  Halving the bytes each SM has to fetch per MMA is what
+// lets the ring run far enough ahead of the tensor cores to hide the latency of L2.
+// Tensor memory holds two accumulators per block (2 x 256 columns), so the eight epilogue
+// warps of a block read a finished tile back (tcgen05.ld), apply the epilogue and store rows
+// while the next tile's MMAs already run into the other accumulator.
 //
-// Tiles are numbered row-tile fastest, so blocks that run at the same time share a few w
-// tiles and all of x in L2, and w is read from HBM once.
+// A persistent grid of one pair per two SMs walks over the tiles, row-tile fastest, so pairs
+// that run at the same time share a few w tiles and all of x in L2, and w is read from HBM once.
 //
-// SwiGLU: w holds the gate rows and then the up rows; a tile takes 128 of each (the second
-// w box starts at the up rows) and writes 128 columns of silu(gate) * up.
+// Barriers: a stage's "full" barrier lives in the first block and counts the bytes of both
+// blocks' boxes; "empty" and "accumulator full" are signalled in both blocks at once by a
+// multicast tcgen05.commit; "accumulator empty" lives in the first block and takes arrivals
+// from the epilogue warps of both.
+//
+// SwiGLU: w holds the gate rows and then the up rows; of a tile's 256 accumulator columns the
+// first block supplies 128 gate rows and the second the 128 up rows of the same outputs, and
+// the epilogue writes 128 columns of silu(gate) * up.
 //
 // Rows of x beyond M and rows of w beyond its end are zero-filled by TMA and never stored.
 // Every wait on an mbarrier is bounded: when it runs out the kernel records where in
-// *error, waits for the copies it started, frees its tensor memory and returns.
+// *error, lets the copies it started land, frees its tensor memory and returns.
 #include "common.cuh"
 #include "tma.cuh"
 #include <math.h>
@@ -27,17 +35,29 @@
 
 namespace fsie {
 
-constexpr int HALF = 128;                    // rows of one MMA (UMMA M) and of one TMA box
-constexpr int TILE = 256;                    // tile rows and columns
-constexpr int BK = 64;                       // k elements per stage: 128 bytes, one swizzle row
+constexpr int HALF = 128;                    // rows per block: of x (MMA M = 2 x 128) and of w (N = 2 x 128)
+constexpr int TILE = 256;                    // tile rows and accumulator columns
+#ifndef FSIE_GT_ATOMS
+#define FSIE_GT_ATOMS 2
+#endif
+constexpr int ATOM_K = 64;                   // k elements of one TMA box: 128 bytes, one swizzle row
+constexpr int ATOMS = FSIE_GT_ATOMS;         // boxes along k per stage and operand
+constexpr int BK = ATOM_K * ATOMS;           // k elements per stage
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 3;
-constexpr uint32_t BOX_BYTES = HALF * BK * 2;            // 16 KB
-constexpr uint32_t STAGE_BYTES = 4 * BOX_BYTES;          // x rows 0-127, x rows 128-255, w 0-127, w 128-255
-constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES;
-constexpr int EPILOGUE_WARPS = 8;
+constexpr int STAGES = 6 / ATOMS;
+#ifndef FSIE_GT_PREFETCH
+#define FSIE_GT_PREFETCH 0
+#endif
+constexpr int PREFETCH = FSIE_GT_PREFETCH;   // k-blocks of w asked into L2 ahead of the ring (0: none; it measured slower)
+constexpr uint32_t BOX_BYTES = HALF * ATOM_K * 2;        // 16 KB
+constexpr uint32_t STAGE_BYTES = 2 * ATOMS * BOX_BYTES;  // this block's rows of x, then its rows of w
+constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 4 * 2 * (32 * 128);   // ring + two output boxes per epilogue warp
+constexpr int EPILOGUE_WARPS = 4;                        // one per quarter of the tensor-memory lanes
+constexpr uint32_t OUT_BOX_BYTES = 32 * 128;             // 32 rows x 64 outputs, staged for a TMA store
 constexpr int THREADS = 64 + 32 * EPILOGUE_WARPS;
-constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_COLS = 512;                      // two accumulators of 256 columns
+constexpr uint32_t FIRST_BLOCK_MASK = 0xFEFFFFFFu;       // clears the bit of a shared::cluster address that
+                                                         // tells the second block of a pair from the first
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
 enum { ERR_TMA_WAIT = 21, ERR_MMA_WAIT = 22, ERR_ACC_WAIT = 23, ERR_EPILOGUE_WAIT = 24 };
@@ -49,8 +69,32 @@ struct TileGemmParams {
     int up_row0;                    // SwiGLU: row of w where the up rows start
     int m_tiles, n_tiles;
     int out_f32;
+    int tma_store;                  // y is written through map_y (bf16, rows on 16-byte boundaries)
     int* error;
 };
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n barrier.cluster.wait.acquire;" ::: "memory");
+}
+// TMA box into this block's shared memory; its bytes are counted by the barrier at the same
+// offset in the first block of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_addr(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar) & FIRST_BLOCK_MASK) : "memory");
+}
+// Asks for a box to be brought from HBM into L2, without a destination in shared memory.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
+// Arrival on the barrier at this offset in the first block of the pair.
+__device__ __forceinline__ void mbar_arrive_first_block(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_addr(bar) & FIRST_BLOCK_MASK) : "memory");
+}
 
 // Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128
 // bytes, groups of 8 rows 1,024 bytes apart (stride byte offset), version 1, layout type 2.
@@ -67,12 +111,16 @@ __device__ __forceinline__ uint64_t umma_desc(const void* tile) {
 __device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+// One MMA over the pair: A rows and B rows at these offsets in both blocks' shared memory,
+// D at this address in both blocks' tensor memory.  Issued by the first block only.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+// When the MMAs issued so far have completed, arrive on the barrier at this offset in both blocks.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_addr(bar)), "h"((uint16_t)3) : "memory");
 }
 // 32 consecutive accumulator columns of this warp's 32 lanes: v[j] = D[lane, column + j]
 __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v) {
@@ -93,6 +141,9 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 
 // Stores 32 consecutive outputs of one row, columns n .. n + 31 as far as they lie below N.
 __device__ __forceinline__ void store_row_chunk(const TileGemmParams& p, int row, int n, const float* v, bool vector_ok) {
+#ifdef FSIE_GT_NO_STORE
+    if (v[0] != 123.25f || v[7] != -77.f) return;
+#endif
     if (row >= p.M) return;
     if (p.out_f32) {
         float* dst = reinterpret_cast<float*>(p.y) + (size_t)row * p.ldy + n;
@@ -125,32 +176,34 @@ __device__ __forceinline__ void store_row_chunk(const TileGemmParams& p, int row
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                  const TileGemmParams p) {
+                  const __grid_constant__ CUtensorMap map_y, const TileGemmParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full, acc_empty;
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_rank();            // 0: the block that issues the MMAs
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const int kblocks = (p.K + BK - 1) / BK;
     const int total_tiles = p.m_tiles * p.n_tiles;
     constexpr int TILE_COLS = EPI == EPI_SWIGLU ? TILE / 2 : TILE;      // output columns per tile
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&acc_full, 1);
-        mbar_init(&acc_empty, EPILOGUE_WARPS);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * EPILOGUE_WARPS); }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {        // one warp allocates all of tensor memory: two 128 x 256 accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {        // the same warp of both blocks allocates all of tensor memory in both
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    cluster_sync_all();     // the other block's barriers are initialised before anything arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_slot;
     // x is the output of the kernel before this one; the kernel after this one may set up now
@@ -158,42 +211,61 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     grid_dependents_go();
 
     if (warp == 0 && lane == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer (both blocks)
         int it = 0, issued = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile % p.m_tiles) * TILE, n0 = (tile / p.m_tiles) * TILE_COLS;
-            const bool two_halves = p.M - m0 > HALF;
-            const int w1_row = EPI == EPI_SWIGLU ? p.up_row0 + n0 : n0 + HALF;
+        auto w_row_of = [&](int tile) {
+            const int n0 = (tile / p.m_tiles) * TILE_COLS;
+            return EPI == EPI_SWIGLU ? (rank == 0 ? n0 : p.up_row0 + n0) : n0 + rank * HALF;
+        };
+        // w comes from HBM (x stays in L2): its boxes are asked for PREFETCH k-blocks before the
+        // ring has room for them, so the ring only has to cover the latency of L2
+        auto prefetch_w = [&](int ahead) {
+            const int tile = pair + (ahead / kblocks) * pairs;
+            if (tile < total_tiles) tma_prefetch_2d(&map_w, (ahead % kblocks) * BK, w_row_of(tile));
+        };
+        for (int j = 0; j < PREFETCH; ++j) prefetch_w(j);
+        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+            const int m0 = (tile % p.m_tiles) * TILE + rank * HALF;
+            const int w_row = w_row_of(tile);
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
                 const int s = it % STAGES;
+                if (PREFETCH > 0) prefetch_w(it + PREFETCH);
                 if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) {
                     atomicExch(p.error, ERR_TMA_WAIT); atomicExch(&abort_flag, 1);
                 }
                 if (*(volatile int*)&abort_flag) { ok = false; break; }
                 unsigned char* stage = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], two_halves ? 4 * BOX_BYTES : 3 * BOX_BYTES);
-                tma_load_2d(stage, &map_x, kb * BK, m0, &full_bar[s]);
-                if (two_halves) tma_load_2d(stage + BOX_BYTES, &map_x, kb * BK, m0 + HALF, &full_bar[s]);
-                tma_load_2d(stage + 2 * BOX_BYTES, &map_w, kb * BK, n0, &full_bar[s]);
-                tma_load_2d(stage + 3 * BOX_BYTES, &map_w, kb * BK, w1_row, &full_bar[s]);
+#ifdef FSIE_GT_NO_LOAD
+                if (rank == 0) mbar_arrive(&full_bar[s]);
+#else
+                if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);       // both blocks' boxes
+#pragma unroll
+                for (int a = 0; a < ATOMS; ++a) {
+                    tma_load_2d_pair(stage + a * BOX_BYTES, &map_x, kb * BK + a * ATOM_K, m0, &full_bar[s]);
+                    tma_load_2d_pair(stage + (ATOMS + a) * BOX_BYTES, &map_w, kb * BK + a * ATOM_K, w_row, &full_bar[s]);
+                }
+#endif
                 issued = it + 1;
             }
         }
         if (!ok) {
             // giving up: let the copies already issued land before the block's memory is released
-            for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
+            if (rank == 0) {
+                for (int j = max(0, issued - STAGES); j < issued; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
+            } else {
+                for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+            }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------ MMA issuer
-        const uint32_t idesc = umma_idesc(HALF, TILE);
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ------------------------------------------------------------ MMA issuer (first block)
+        const uint32_t idesc = umma_idesc(TILE, TILE);
         int it = 0, local_tile = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
-            const int m0 = (tile % p.m_tiles) * TILE;
-            const bool two_halves = p.M - m0 > HALF;
-            if (local_tile > 0) {       // the epilogue warps have read the previous tile out of tensor memory
-                if (!mbar_wait(&acc_empty, (local_tile - 1) & 1)) {
+        for (int tile = pair; tile < total_tiles && ok; tile += pairs, ++local_tile) {
+            const int buf = local_tile & 1;
+            if (local_tile >= 2) {      // both blocks' epilogue warps have read this accumulator's previous tile
+                if (!mbar_wait(&acc_empty[buf], ((local_tile >> 1) - 1) & 1)) {
                     atomicExch(p.error, ERR_ACC_WAIT); atomicExch(&abort_flag, 1); ok = false; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -206,81 +278,114 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned char* stage = smem + s * STAGE_BYTES;
-                const uint64_t a0 = umma_desc(stage), a1 = umma_desc(stage + BOX_BYTES), b = umma_desc(stage + 2 * BOX_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 elements further along k: 32 bytes inside the swizzled row (address field in 16-byte units)
-                    const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                    umma_bf16(tmem, a0 + 2 * k, b + 2 * k, idesc, accumulate);
-                    if (two_halves) umma_bf16(tmem + TILE, a1 + 2 * k, b + 2 * k, idesc, accumulate);
+                for (int at = 0; at < ATOMS; ++at) {
+                    const uint64_t a = umma_desc(stage + at * BOX_BYTES), b = umma_desc(stage + (ATOMS + at) * BOX_BYTES);
+#pragma unroll
+                    for (int k = 0; k < ATOM_K / UMMA_K; ++k) {
+#ifdef FSIE_GT_NO_MMA
+                        break;
+#endif
+                        // 16 elements further along k: 32 bytes inside the swizzled row (address field in 16-byte units)
+                        umma_bf16_pair(tmem + buf * TILE, a + 2 * k, b + 2 * k, idesc, (kb > 0 || at > 0 || k > 0) ? 1u : 0u);
+                    }
                 }
-                umma_commit(&empty_bar[s]);          // the stage is free once these MMAs have read it
+                umma_commit_pair(&empty_bar[s]);     // the stage is free in both blocks once these MMAs have read it
             }
-            umma_commit(&acc_full);                  // the tile's accumulators are complete
+            if (ok) umma_commit_pair(&acc_full[buf]);        // the tile's accumulators are complete in both blocks
         }
     } else if (warp >= 2) {
-        // ------------------------------------------------------------ epilogue
+        // ------------------------------------------------------------ epilogue (both blocks)
+        // A warp owns 32 rows of the block's 128.  It turns 32 accumulator columns at a time into
+        // outputs; two such chunks fill a box of 32 rows x 128 bytes in shared memory (128-byte
+        // swizzle, so that the lanes' 16-byte stores do not collide), which one TMA store writes to
+        // y: whole lines, off the load/store path that stores of a row per lane would flood.
         const int quarter = warp & 3;                // the tensor-memory lanes this warp may read
-        const int column_half = (warp - 2) >> 2;     // which half of the tile's output columns
         const bool vector_ok = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
-        int local_tile = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
-            const int m0 = (tile % p.m_tiles) * TILE, n0 = (tile / p.m_tiles) * TILE_COLS;
-            const bool two_halves = p.M - m0 > HALF;
+        unsigned char* boxes = smem + STAGES * STAGE_BYTES + (warp - 2) * 2 * OUT_BOX_BYTES;
+        int local_tile = 0, groups = 0;
+        for (int tile = pair; tile < total_tiles; tile += pairs, ++local_tile) {
+            const int buf = local_tile & 1;
+            const int row0 = (tile % p.m_tiles) * TILE + rank * HALF + quarter * 32;
+            const int n0 = (tile / p.m_tiles) * TILE_COLS;
             if (*(volatile int*)&abort_flag) break;
-            if (!mbar_wait(&acc_full, local_tile & 1)) {
+            if (!mbar_wait(&acc_full[buf], (local_tile >> 1) & 1)) {
                 atomicExch(p.error, ERR_EPILOGUE_WAIT); atomicExch(&abort_flag, 1); break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int h = 0; h < (two_halves ? 2 : 1); ++h) {
-                const int row = m0 + h * HALF + quarter * 32 + lane;
-                const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16) + h * TILE;
-                if (EPI == EPI_SWIGLU) {
+            const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16) + buf * TILE;
 #pragma unroll 1
-                    for (int c = 0; c < 2; ++c) {
-                        const int col = column_half * 64 + c * 32, n = n0 + col;
-                        if (n >= p.N) continue;
-                        float g[32], u[32];
-                        tmem_load_32(trow + col, g);
-                        tmem_load_32(trow + HALF + col, u);
-                        tmem_load_wait();
+            for (int c = 0; c < TILE_COLS / 32; ++c) {
+                const int col = c * 32, n = n0 + col;
+                if (n >= p.N) break;
+                float v[32];
+                if (EPI == EPI_SWIGLU) {
+                    float u[32];
+                    tmem_load_32(trow + col, v);
+                    tmem_load_32(trow + HALF + col, u);
+                    tmem_load_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            // gate and up are rounded to bfloat16 before the activation, as the
-                            // unfused path stores them in between
-                            const float gj = __bfloat162float(__float2bfloat16_rn(g[j]));
-                            const float uj = __bfloat162float(__float2bfloat16_rn(u[j]));
-                            g[j] = (gj / (1.0f + expf(-gj))) * uj;
-                        }
-                        store_row_chunk(p, row, n, g, vector_ok);
+                    for (int j = 0; j < 32; ++j) {
+                        // gate and up are rounded to bfloat16 before the activation, as the
+                        // unfused path stores them in between
+                        const float gj = __bfloat162float(__float2bfloat16_rn(v[j]));
+                        const float uj = __bfloat162float(__float2bfloat16_rn(u[j]));
+                        v[j] = (gj / (1.0f + expf(-gj))) * uj;
                     }
                 } else {
-#pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        const int col = column_half * 128 + c * 32, n = n0 + col;
-                        if (n >= p.N) continue;
-                        float v[32];
-                        tmem_load_32(trow + col, v);
-                        tmem_load_wait();
-                        if (p.bias) {
+                    tmem_load_32(trow + col, v);
+                    tmem_load_wait();
+                    if (p.bias) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) if (n + j < p.N) v[j] += __bfloat162float(p.bias[n + j]);
-                        }
-                        store_row_chunk(p, row, n, v, vector_ok);
+                        for (int j = 0; j < 32; ++j) if (n + j < p.N) v[j] += __bfloat162float(p.bias[n + j]);
                     }
+                }
+                if (!p.tma_store) {
+                    store_row_chunk(p, row0 + lane, n, v, vector_ok);
+                    continue;
+                }
+                unsigned char* box = boxes + (groups & 1) * OUT_BOX_BYTES;
+                const int half = c & 1;
+                if (half == 0) {        // the store that read this box two groups ago has finished reading
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int j = q * 8;
+                    uint4 w;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                    w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
+                    w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
+                    const int chunk = half * 4 + q;      // 16-byte chunk of the row, moved by the swizzle
+                    *reinterpret_cast<uint4*>(box + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = w;
+                }
+                if (half == 1 || n + 32 >= p.N) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        // columns beyond N and rows beyond M are clipped by the copy engine
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(&map_y), "r"(smem_addr(box)), "r"(n - half * 32), "r"(row0) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    ++groups;
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty);
+            if (lane == 0) mbar_arrive_first_block(&acc_empty[buf]);
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    cluster_sync_all();     // neither block frees tensor memory or leaves while the other may still signal it
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -290,7 +395,7 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     if (!encode) return ERR_UNSUPPORTED;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)HALF};
+    const cuuint32_t box[2] = {(cuuint32_t)ATOM_K, (cuuint32_t)HALF};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                                elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -298,17 +403,55 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return rc == CUDA_SUCCESS ? 0 : ERR_BAD_ARGUMENT;
 }
 
+// Launch of `pairs` clusters of two blocks as a programmatic dependent of the kernel before it.
+// bf16 output [rows, cols]: boxes of 32 rows x 64 columns, 128-byte swizzle, for the epilogue's stores
+static int make_out_map(CUtensorMap* map, void* base, long long rows, long long cols, long long ld) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {64, 32};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? 0 : ERR_BAD_ARGUMENT;
+}
+
 template <int EPI>
-static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const TileGemmParams& p, int blocks,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const CUtensorMap& map_y, const TileGemmParams& p,
+                  int pairs, cudaStream_t stream) {
     auto kernel = gemm_tiles_kernel<EPI>;
-    static bool configured = false;
-    if (!configured) {
+    static int max_pairs = 0;
+    cudaLaunchConfig_t config = {};
+    config.blockDim = dim3(THREADS, 1, 1);
+    config.dynamicSmemBytes = SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    if (max_pairs == 0) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        int device = 0, sms = 0, clusters = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        config.gridDim = dim3(sms & ~1, 1, 1);
+        config.numAttrs = 1;                         // the cluster shape alone decides how many fit
+        e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+        if (e != cudaSuccess) return (int)e;
+        if (clusters <= 0) return ERR_UNSUPPORTED;
+        max_pairs = clusters;
     }
-    return launch_dependent(kernel, dim3(blocks), dim3(THREADS), SMEM_BYTES, stream, map_w, map_x, p);
+    if (pairs > max_pairs) pairs = max_pairs;
+    config.gridDim = dim3(2 * pairs, 1, 1);
+    config.numAttrs = 2;
+    return (int)cudaLaunchKernelEx(&config, kernel, map_w, map_x, map_y, p);
 }
 
 }  // namespace fsie
@@ -330,7 +473,7 @@ int fsie_gemm_tiles_weight_map(void* map_out, const void* w, long long rows, lon
 
 // y[M, N] = x[M, K] * w^T (+ bias), or for swiglu y[M, N] = silu(x w_gate^T) * (x w_up^T) with
 // w = [gate rows (N); up rows (N)].  `blocks` is the size of the persistent grid (the number
-// of SMs; fewer when there are fewer tiles).
+// of SMs; it is cut to the pairs that can run at once and to the number of tiles).
 int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* y, long long ldy, const void* bias,
                     int M, int N, int K, int swiglu, int out_f32, int blocks, int* error, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
@@ -343,11 +486,19 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
     TileGemmParams p;
     p.y = y; p.ldy = ldy; p.bias = (const bf16*)bias; p.M = M; p.N = N; p.K = K;
     p.up_row0 = N; p.out_f32 = out_f32; p.error = error;
+    // the copy engine writes y when its rows start on 16-byte boundaries; else the lanes store their rows
+    p.tma_store = !out_f32 && ldy % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+    CUtensorMap map_y = map_x;
+    if (p.tma_store) {
+        rc = make_out_map(&map_y, y, M, N, ldy);
+        if (rc != 0) return rc;
+    }
     p.m_tiles = (M + TILE - 1) / TILE;
     p.n_tiles = swiglu ? (N + TILE / 2 - 1) / (TILE / 2) : (N + TILE - 1) / TILE;
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
-    if (tiles < blocks) blocks = (int)tiles;
-    return swiglu ? launch<EPI_SWIGLU>(map_w, map_x, p, blocks, stream) : launch<EPI_PLAIN>(map_w, map_x, p, blocks, stream);
+    int pairs = blocks / 2 > 0 ? blocks / 2 : 1;
+    if (tiles < pairs) pairs = (int)tiles;
+    return swiglu ? launch<EPI_SWIGLU>(map_w, map_x, map_y, p, pairs, stream) : launch<EPI_PLAIN>(map_w, map_x, map_y, p, pairs, stream);
 }
 
 }  // extern "C"
