@@ -330,7 +330,9 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                         // unfused path stores them in between
                         const float gj = __bfloat162float(__float2bfloat16_rn(v[j]));
                         const float uj = __bfloat162float(__float2bfloat16_rn(u[j]));
-                        v[j] = (gj / (1.0f + expf(-gj))) * uj;
+                        // (approximate division: exact to 2 ulp of float, and without the slow path that
+                        // the exact one takes when exp overflows the denominator; the quotient is 0 there)
+                        v[j] = __fdividef(gj, 1.0f + expf(-gj)) * uj;
                     }
                 } else {
                     tmem_load_32(trow + col, v);
@@ -403,7 +405,6 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return rc == CUDA_SUCCESS ? 0 : ERR_BAD_ARGUMENT;
 }
 
-// Launch of `pairs` clusters of two blocks as a programmatic dependent of the kernel before it.
 // bf16 output [rows, cols]: boxes of 32 rows x 64 columns, 128-byte swizzle, for the epilogue's stores
 static int make_out_map(CUtensorMap* map, void* base, long long rows, long long cols, long long ld) {
     EncodeTiled encode = encode_tiled();
@@ -418,12 +419,47 @@ static int make_out_map(CUtensorMap* map, void* base, long long rows, long long 
     return rc == CUDA_SUCCESS ? 0 : ERR_BAD_ARGUMENT;
 }
 
+// Sets the kernel's shared-memory size once and asks how many pairs can run at the same time.
+template <int EPI>
+static int configure(int* max_pairs_out) {
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+        auto kernel = gemm_tiles_kernel<EPI>;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        int device = 0, sms = 0, clusters = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(sms & ~1, 1, 1);
+        config.blockDim = dim3(THREADS, 1, 1);
+        config.dynamicSmemBytes = SMEM_BYTES;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+        if (e != cudaSuccess) return (int)e;
+        if (clusters <= 0) return ERR_UNSUPPORTED;
+        max_pairs = clusters;
+    }
+    *max_pairs_out = max_pairs;
+    return 0;
+}
+
+// Launch of `pairs` clusters of two blocks as a programmatic dependent of the kernel before it.
 template <int EPI>
 static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const CUtensorMap& map_y, const TileGemmParams& p,
                   int pairs, cudaStream_t stream) {
-    auto kernel = gemm_tiles_kernel<EPI>;
-    static int max_pairs = 0;
+    int max_pairs = 0;
+    const int rc = configure<EPI>(&max_pairs);
+    if (rc != 0) return rc;
+    if (pairs > max_pairs) pairs = max_pairs;
     cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * pairs, 1, 1);
     config.blockDim = dim3(THREADS, 1, 1);
     config.dynamicSmemBytes = SMEM_BYTES;
     config.stream = stream;
@@ -435,23 +471,8 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const CUte
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
-    if (max_pairs == 0) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        int device = 0, sms = 0, clusters = 0;
-        cudaGetDevice(&device);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-        config.gridDim = dim3(sms & ~1, 1, 1);
-        config.numAttrs = 1;                         // the cluster shape alone decides how many fit
-        e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
-        if (e != cudaSuccess) return (int)e;
-        if (clusters <= 0) return ERR_UNSUPPORTED;
-        max_pairs = clusters;
-    }
-    if (pairs > max_pairs) pairs = max_pairs;
-    config.gridDim = dim3(2 * pairs, 1, 1);
     config.numAttrs = 2;
-    return (int)cudaLaunchKernelEx(&config, kernel, map_w, map_x, map_y, p);
+    return (int)cudaLaunchKernelEx(&config, gemm_tiles_kernel<EPI>, map_w, map_x, map_y, p);
 }
 
 }  // namespace fsie
@@ -461,6 +482,16 @@ using namespace fsie;
 extern "C" {
 
 int fsie_gemm_tiles_map_bytes() { return (int)sizeof(CUtensorMap); }
+
+// How many pairs of blocks run at the same time (also sets the kernels up, outside any stream
+// capture); negative or a CUDA error code when the kernels cannot run here.
+int fsie_gemm_tiles_pairs() {
+    int plain = 0, swiglu = 0;
+    int rc = configure<EPI_PLAIN>(&plain);
+    if (rc == 0) rc = configure<EPI_SWIGLU>(&swiglu);
+    if (rc != 0) return rc > 0 ? -rc : rc;
+    return plain < swiglu ? plain : swiglu;
+}
 
 // Describe a bf16 weight matrix w[rows, K] (K contiguous) for the kernel below.
 int fsie_gemm_tiles_weight_map(void* map_out, const void* w, long long rows, long long K) {

@@ -238,5 +238,9 @@ class ModelRunner:
             what = {1: "token id outside the vocabulary", 2: "position outside the table",
                     11: "matrix product: the copy engine's stage never became free",
                     12: "matrix product: a tile never arrived", 13: "matrix product: the "
-                    "accumulator never completed"}
+                    "accumulator never completed",
+                    21: "tiled matrix product: the copy engine's stage never became free",
+                    22: "tiled matrix product: a stage never arrived",
+                    23: "tiled matrix product: the accumulator was never read out",
+                    24: "tiled matrix product: the accumulator never completed"}
             raise DeviceFault(what.get(code, f"device error flag {code}"))

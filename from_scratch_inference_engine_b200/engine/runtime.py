@@ -35,7 +35,8 @@ class Runtime:
     """
 
     def __init__(self, device="cuda:0", dtype=torch.bfloat16, max_positions: int = 0,
-                 few_token_min_elements: int = 32 * 1024 * 1024):
+                 few_token_min_elements: int = 32 * 1024 * 1024, products: str = "own",
+                 tiled_min_tiles: Optional[int] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this engine has no CPU path")
         self.device = torch.device(device)
@@ -50,6 +51,13 @@ class Runtime:
         self._few_token_weights: Dict[int, ops.DecodeWeight] = {}
         self.few_token_limit = 16          # steps of up to this many tokens take that product
         self.few_token_min_elements = few_token_min_elements   # ... for matrices at least this large
+        # "own": steps of many tokens take the tiled tcgen05 product (fused bias / SwiGLU) where
+        # its tiles fill the GPU; "library": they take the library product
+        if products not in ("own", "library"):
+            raise ValueError("products must be 'own' or 'library'")
+        self.products = products
+        self.tiled_min_tiles = tiled_min_tiles       # None: as many tiles as pairs of SMs run at once
+        self._tiled_weights: Dict[int, ops.TiledWeight] = {}
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -77,9 +85,28 @@ class Runtime:
         if self.dtype is not torch.bfloat16 or weight.dtype is not torch.bfloat16:
             return
         rows, k = weight.shape
-        if k % 8 or rows * k < self.few_token_min_elements or (swiglu and rows % 2):
+        if k % 8 or (swiglu and rows % 2):
             return
-        self._few_token_weights[weight.data_ptr()] = ops.DecodeWeight(weight, swiglu)
+        if self.products == "own":
+            self._tiled_weights[weight.data_ptr()] = ops.TiledWeight(weight, swiglu)
+        if rows * k >= self.few_token_min_elements:
+            self._few_token_weights[weight.data_ptr()] = ops.DecodeWeight(weight, swiglu)
+
+    def _tiled(self, x: torch.Tensor, weight: torch.Tensor) -> Optional["ops.TiledWeight"]:
+        """The weight's descriptor for the tiled product when this step is one for it: more
+        tokens than the few-token product takes, and enough tiles to give every pair of SMs
+        one (with fewer, the library's smaller tiles or split k stream the weight faster)."""
+        prepared = self._tiled_weights.get(weight.data_ptr())
+        if prepared is None or x.shape[0] <= self.few_token_limit or x.stride(0) % 8 or x.data_ptr() % 16:
+            return None
+        least = ops.gemm_tiles_lib().pairs if self.tiled_min_tiles is None else self.tiled_min_tiles
+        if ops.gemm_tiles_count(x.shape[0], prepared.n, prepared.swiglu) < least:
+            return None
+        return prepared
+
+    def _tiled_product(self, prepared, x, bias, out_dtype) -> torch.Tensor:
+        out = torch.empty((x.shape[0], prepared.n), dtype=out_dtype, device=x.device)
+        return ops.gemm_tiles(prepared, x, out, bias, self.error, self.sm_count)
 
     def _few_tokens(self, x: torch.Tensor, weight: torch.Tensor) -> Optional["ops.DecodeWeight"]:
         if x.shape[0] > self.few_token_limit or x.stride(0) % 8:
@@ -100,6 +127,9 @@ class Runtime:
         prepared = self._few_tokens(x, weight)
         if prepared is not None and not prepared.swiglu:
             return self._few_token_product(prepared, x, bias, torch.bfloat16)
+        tiled = self._tiled(x, weight)
+        if tiled is not None and not tiled.swiglu:
+            return self._tiled_product(tiled, x, bias, torch.bfloat16)
         return F.linear(x, weight, bias)
 
     def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
@@ -108,6 +138,9 @@ class Runtime:
         prepared = self._few_tokens(x, gate_up) if self.dtype is torch.bfloat16 else None
         if prepared is not None and prepared.swiglu:
             return self._few_token_product(prepared, x, None, torch.bfloat16)
+        tiled = self._tiled(x, gate_up) if self.dtype is torch.bfloat16 else None
+        if tiled is not None and tiled.swiglu:
+            return self._tiled_product(tiled, x, None, torch.bfloat16)
         both = self.linear(x, gate_up, None) if prepared is None else F.linear(x, gate_up)
         act = torch.empty((x.shape[0], gate_up.shape[0] // 2), dtype=both.dtype, device=x.device)
         return ops.swiglu(both, act)
@@ -119,6 +152,9 @@ class Runtime:
         prepared = self._few_tokens(x, weight)
         if prepared is not None and not prepared.swiglu:
             return self._few_token_product(prepared, x, None, torch.float32)
+        tiled = self._tiled(x, weight)
+        if tiled is not None and not tiled.swiglu:
+            return self._tiled_product(tiled, x, None, torch.float32)
         if self._f32_out is None:
             try:
                 torch.mm(x[:1], weight[:8].t(), out_dtype=torch.float32)

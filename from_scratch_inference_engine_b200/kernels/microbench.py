@@ -201,7 +201,7 @@ def run(args):
     elif args.kernel in ("gemm_decode", "gemm_decode_swiglu"):
         m, n, k = args.tokens, args.n, args.k
         swiglu = args.kernel == "gemm_decode_swiglu"
-        x, w = rand(m, k).to(dtype), rand(2 * n if swiglu else n, k).to(dtype)
+        x, w = rand(m, k).to(dtype), (rand(2 * n if swiglu else n, k) / math.sqrt(k)).to(dtype)
         weight = ops.DecodeWeight(w, swiglu=swiglu)
         out = torch.empty((m, n), dtype=dtype, device="cuda")
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -214,7 +214,8 @@ def run(args):
     elif args.kernel in ("gemm_tiles", "gemm_tiles_swiglu"):
         m, n, k = args.tokens, args.n, args.k
         swiglu = args.kernel == "gemm_tiles_swiglu"
-        x, w = rand(m, k).to(dtype), rand(2 * n if swiglu else n, k).to(dtype)
+        # outputs of unit scale, as a layer sees them (the activation's exp stays in range)
+        x, w = rand(m, k).to(dtype), (rand(2 * n if swiglu else n, k) / math.sqrt(k)).to(dtype)
         weight = ops.TiledWeight(w, swiglu=swiglu)
         out = torch.empty((m, n), dtype=dtype, device="cuda")
         error = torch.zeros(1, dtype=torch.int32, device="cuda")

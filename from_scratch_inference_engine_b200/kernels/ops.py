@@ -515,10 +515,21 @@ def gemm_tiles_lib():
         lib.fsie_gemm_tiles_map_bytes.argtypes = []
         lib.fsie_gemm_tiles_weight_map.argtypes = [p, p, ll, ll]
         lib.fsie_gemm_tiles.argtypes = [p, p, ll, p, ll, p, i, i, i, i, i, i, p, p]
-        for name in ("fsie_gemm_tiles_map_bytes", "fsie_gemm_tiles_weight_map", "fsie_gemm_tiles"):
+        lib.fsie_gemm_tiles_pairs.argtypes = []
+        for name in ("fsie_gemm_tiles_map_bytes", "fsie_gemm_tiles_weight_map", "fsie_gemm_tiles",
+                     "fsie_gemm_tiles_pairs"):
             getattr(lib, name).restype = i
+        pairs = lib.fsie_gemm_tiles_pairs()       # also sets the kernels up, outside any capture
+        if pairs <= 0:
+            raise KernelError(f"gemm_tiles: pairs of blocks cannot be launched here (code {pairs})")
+        lib.pairs = pairs
         _gemm_tiles = lib
     return _gemm_tiles
+
+
+def gemm_tiles_count(rows: int, n: int, swiglu: bool) -> int:
+    """Output tiles of `gemm_tiles` for a product of `rows` tokens and `n` output features."""
+    return -(-rows // 256) * -(-n // (128 if swiglu else 256))
 
 
 class TiledWeight:

@@ -140,3 +140,22 @@ def test_replay_with_the_few_token_product_on_every_matrix(folders, name, page_s
     rows = helpers.run_trace_in_process(runner, steps)
     worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], TOLERANCE["bfloat16"])
     assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+
+
+@pytest.mark.parametrize("family", ["whole", "portions", "mixed"])
+@pytest.mark.parametrize("name,page_size", [("B", 8), ("C", 16), ("E", 16)])
+def test_replay_with_the_tiled_product_on_every_matrix(folders, name, page_size, family, monkeypatch):
+    """Steps of more than 16 tokens take the tiled tcgen05 product (bias and SwiGLU in its
+    epilogue) for every matrix, however few tiles that makes at these sizes."""
+    requests = requests_for(name)
+    steps = FAMILIES[family](requests, 5)
+    need = helpers.live_tokens_needed(steps, round_to=page_size)
+    runner = build_runner(folders[name], "bfloat16", need, page_size, tiled_min_tiles=1)
+    assert runner.runtime._tiled_weights
+    from from_scratch_inference_engine_b200.kernels import ops
+    calls, original = [], ops.gemm_tiles
+    monkeypatch.setattr(ops, "gemm_tiles", lambda *a, **k: (calls.append(1), original(*a, **k))[1])
+    rows = helpers.run_trace_in_process(runner, steps)
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], TOLERANCE["bfloat16"])
+    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+    assert len(calls) >= 4 * len(runner.model.blocks)
