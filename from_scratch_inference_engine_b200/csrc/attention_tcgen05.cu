@@ -12,10 +12,11 @@
 //                   buffers in tensor memory, issued one tile ahead of the softmax;
 //                   O += P_i V_i    (128 x head_dim x 128, A = P from shared memory, B = V
 //                   MN-major straight from its [key][dim] tile)
-//   4 softmax warps one thread per row (= tensor-memory lane): read S, mask, running maximum and
-//                   sum, write P as bfloat16 into shared memory in the swizzled K-major layout,
-//                   rescale O in tensor memory when a row's maximum moved, finally normalise O
-//                   and store it (or a partial result when the key range is split)
+//   8 softmax warps two threads per row (= tensor-memory lane), 64 keys of the tile each: read S,
+//                   mask, running maximum (exchanged between the two once per tile) and sum, write
+//                   P as bfloat16 into shared memory in the swizzled K-major layout, rescale O in
+//                   tensor memory when a row's maximum moved, finally normalise O and store it
+//                   (or a partial result when the key range is split)
 //
 // Formula: src/model/nn.cpp:151-226 of the reference, as a running softmax.
 // Every wait on an mbarrier is bounded; when one runs out *error is set, all roles leave their
@@ -37,15 +38,29 @@ constexpr int HD = HEAD_DIM;
 constexpr int BM = 128;                 // query rows per block = tensor-memory lanes
 constexpr int BN = 128;                 // keys per tile
 constexpr int STAGES = 2;
+constexpr int SOFTMAX_WARPS = 8;        // two per quarter of the tensor-memory lanes
+constexpr int THREADS = 64 + 32 * SOFTMAX_WARPS;
 constexpr int HALVES = HD / 64;         // 128-byte column halves of a row of head_dim elements
 constexpr int ATOM_BYTES = 128 * 128;   // 128 rows x 128 bytes: one swizzled block
 constexpr int Q_BYTES = HALVES * ATOM_BYTES;
 constexpr int KV_BYTES = HALVES * ATOM_BYTES;          // one K or V tile
 constexpr int P_BYTES = (BN / 64) * ATOM_BYTES;        // P[128 rows, 128 keys] bf16; two of them
-constexpr int SMEM_BYTES = 1024 + Q_BYTES + 2 * P_BYTES + STAGES * 2 * KV_BYTES;
+constexpr int TILE_BYTES = Q_BYTES + 2 * P_BYTES + STAGES * 2 * KV_BYTES;
+// Barriers and the softmax warps' exchange area come first in the block's (dynamic only) shared
+// memory, the swizzled tiles follow at the next 1,024-byte boundary.  With head size 128 this is
+// all the shared memory an SM offers to a block (227 KB), so the kernel has no static shared
+// memory and relies on the window starting on such a boundary; it checks and refuses otherwise.
+struct Control {
+    uint64_t kv_full[STAGES], kv_empty[STAGES], s_full[2], p_ready, o_done[2], pair_bar[4];
+    uint32_t tmem_slot;
+    int abort_flag;
+    float pair_xchg[2][2][BM];          // [exchange parity][half of the keys][row]
+};
+static_assert(sizeof(Control) <= 3072, "control block");
+constexpr int SMEM_BYTES = 3072 + TILE_BYTES;
 constexpr uint32_t TMEM_COLS = 512;     // S0 | S1 | O  (128 + 128 + head_dim columns), power of two
 constexpr uint32_t COL_S0 = 0, COL_S1 = BN, COL_O = 2 * BN;
-enum { ERR_TC_PRODUCER = 31, ERR_TC_MMA = 32, ERR_TC_SOFTMAX = 33 };
+enum { ERR_TC_PRODUCER = 31, ERR_TC_MMA = 32, ERR_TC_SOFTMAX = 33, ERR_TC_LAYOUT = 34 };
 
 struct TcExtra { int entries, entry; int* error; };
 
@@ -135,16 +150,23 @@ __device__ __forceinline__ float fast_exp2(float v) {
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a 128-byte-swizzled block
 __device__ __forceinline__ int swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(THREADS)
 attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p, const TcExtra x) {
-    extern __shared__ unsigned char smem_unaligned[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) unsigned char smem_all[];
+    Control& ctl = *reinterpret_cast<Control*>(smem_all);
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_all) + sizeof(Control) + 1023) & ~uintptr_t(1023));
+    if (smem + TILE_BYTES > smem_all + SMEM_BYTES) {        // the window does not start on a 1,024-byte boundary
+        if (threadIdx.x == 0) atomicExch(x.error, ERR_TC_LAYOUT);
+        return;
+    }
+    uint64_t (&kv_full)[STAGES] = ctl.kv_full, (&kv_empty)[STAGES] = ctl.kv_empty, (&s_full)[2] = ctl.s_full;
+    uint64_t &p_ready = ctl.p_ready, (&o_done)[2] = ctl.o_done, (&pair_bar)[4] = ctl.pair_bar;
+    uint32_t& tmem_slot = ctl.tmem_slot;
+    int& abort_flag = ctl.abort_flag;
+    float (&pair_xchg)[2][2][BM] = ctl.pair_xchg;
     unsigned char* q_s = smem;                               // [HALVES][128 rows][128 B]
     unsigned char* p_s = q_s + Q_BYTES;                      // [2 buffers][2][128 rows][128 B]: keys 0-63 | 64-127
     unsigned char* kv_s = p_s + 2 * P_BYTES;                     // [STAGES][K | V][HALVES][128 keys][128 B]
-    __shared__ uint64_t kv_full[STAGES], kv_empty[STAGES], s_full[2], p_ready, o_done[2];
-    __shared__ uint32_t tmem_slot;
-    __shared__ int abort_flag;
 
     // later tiles of a prompt see more keys: start them first so that the last wave is short
     const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -177,7 +199,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
         mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
-        mbar_init(&p_ready, 128); mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
+        mbar_init(&p_ready, 32 * SOFTMAX_WARPS); mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
+        for (int qt = 0; qt < 4; ++qt) mbar_init(&pair_bar[qt], 64);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -278,16 +301,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax, one thread per row
+        // ------------------------------------------------------------------ softmax
+        // Two warps share the 32 rows of a tensor-memory quarter: each takes 64 of a tile's 128
+        // keys (and later half of O's columns).  Per tile they exchange one number per row, the
+        // maximum of their halves; the row sums stay apart until the end.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;                  // row of the tile = tensor-memory lane
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         const bool valid = r < nrows;
         const int pos = valid ? pos0 + (row0 + r) / group : -1;
         const int lowest = p.window > 0 ? pos - p.window : -1;       // keys <= this are unseen
         const float sc = p.scale * 1.4426950408889634f;
+        constexpr int HK = BN / 2;                          // keys per warp and tile
+        constexpr int HO = HD / 2;                          // columns of O per warp
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
+        int exchanges = 0;
+        // hands `mine` to the other warp of the pair and returns what that one handed over
+        auto exchange = [&](float mine, float& theirs) -> bool {
+            pair_xchg[exchanges & 1][half][r] = mine;
+            mbar_arrive(&pair_bar[quarter]);
+            const bool done = mbar_wait(&pair_bar[quarter], exchanges & 1);
+            theirs = pair_xchg[exchanges & 1][half ^ 1][r];
+            ++exchanges;
+            return done;
+        };
         for (int i = 0; i < ntiles && ok; ++i) {
             // (decisions to give up are taken by whole warps: the tensor-memory accesses below are
             // warp-collective)
@@ -296,21 +335,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 atomicExch(&abort_flag, 1); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t s_addr = lane_base + ((i & 1) ? COL_S1 : COL_S0);
-            const int k0 = kbegin + i * BN;
-            // the row's 128 scores in registers: four reads in flight, one wait
-            uint32_t sr[BN];
+            const uint32_t s_addr = lane_base + ((i & 1) ? COL_S1 : COL_S0) + half * HK;
+            const int k0 = kbegin + i * BN + half * HK;
+            // the row's 64 scores in registers: two reads in flight, one wait
+            uint32_t sr[HK];
 #pragma unroll
-            for (int c = 0; c < BN; c += 32) tmem_ld32_issue(s_addr + c, sr + c);
+            for (int c = 0; c < HK; c += 32) tmem_ld32_issue(s_addr + c, sr + c);
             tmem_wait_ld();
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains, not one
-            const bool clear = k0 + BN - 1 < kend && k0 + BN - 1 <= pos && k0 > lowest;   // nothing to mask
+            const bool clear = k0 + HK - 1 < kend && k0 + HK - 1 <= pos && k0 > lowest;   // nothing to mask
             if (__all_sync(0xffffffffu, clear || !valid)) {
 #pragma unroll
-                for (int j = 0; j < BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
+                for (int j = 0; j < HK; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
             } else {
 #pragma unroll
-                for (int j = 0; j < BN; ++j) {
+                for (int j = 0; j < HK; ++j) {
                     const int key = k0 + j;
                     const bool seen = key < kend && key <= pos && key > lowest;
                     if (!seen) sr[j] = 0xff800000u;                    // -inf
@@ -319,6 +358,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             if (!valid) mx = -INFINITY;
+            float other;
+            if (!__all_sync(0xffffffffu, exchange(mx, other))) {
+                if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
+                atomicExch(&abort_flag, 1); ok = false; break;
+            }
+            mx = fmaxf(mx, other);
             // The reference point of the exponentials moves only when the row's maximum has grown
             // by more than 2^8 since it was set: until then p may exceed 1 (by at most 256x, exact
             // enough in float and bfloat16), and O and the row sum need no rescaling.
@@ -337,21 +382,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 atomicExch(&abort_flag, 1); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (rescale) {
-                uint32_t orr[HD];
+            if (rescale) {                                  // this warp's half of O's columns
+                uint32_t orr[HO];
 #pragma unroll
-                for (int c = 0; c < HD; c += 32) tmem_ld32_issue(lane_base + COL_O + c, orr + c);
+                for (int c = 0; c < HO; c += 32) tmem_ld32_issue(lane_base + COL_O + half * HO + c, orr + c);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < HD; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * corr);
+                for (int j = 0; j < HO; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * corr);
 #pragma unroll
-                for (int c = 0; c < HD; c += 32) tmem_st32_issue(lane_base + COL_O + c, orr + c);
+                for (int c = 0; c < HO; c += 32) tmem_st32_issue(lane_base + COL_O + half * HO + c, orr + c);
                 tmem_wait_st();
             }
             // p = exp2(s * sc - base), row sum, P as bfloat16 in the swizzled layout
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int chunk = 0; chunk < BN / 8; ++chunk) {                 // 8 keys = one 16-byte chunk
+            for (int chunk = 0; chunk < HK / 8; ++chunk) {                 // 8 keys = one 16-byte chunk
                 float pv[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -362,7 +407,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(pv[2 * j], pv[2 * j + 1]);
-                *reinterpret_cast<uint4*>(p_s + (i & 1) * P_BYTES + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
+                // keys 0-63 of the tile are the first swizzled block of the P buffer, keys 64-127 the second
+                *reinterpret_cast<uint4*>(p_s + (i & 1) * P_BYTES + half * ATOM_BYTES + swizzled(r, chunk)) = packed;
             }
             const float sum = valid ? (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]) : 0.f;
             l_run = l_run * corr + sum;
@@ -378,11 +424,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             atomicExch(&abort_flag, 1); have = false;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float l_other = 0.f;
+        if (ok && !__all_sync(0xffffffffu, exchange(l_run, l_other))) {       // the row sum of all keys
+            if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
+            atomicExch(&abort_flag, 1); have = false;
+        }
+        const float l_all = l_run + l_other;
         const int row = row0 + (valid ? r : 0);
         const int tok = qstart + row / group, h = kvh * group + row % group;
-        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
+        for (int c = half * HO; c < (half + 1) * HO; c += 32) {
             float v[32];
             if (have) tmem_ld32(lane_base + COL_O + c, v);       // warp-collective: every lane takes part
             else {
@@ -409,10 +461,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                     *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
         }
-        if (valid && p.nsplit > 1) {
+        if (valid && half == 0 && p.nsplit > 1) {
             const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
             p.part_ml[idx * 2] = m_run == -INFINITY ? -INFINITY : m_run * p.scale;
-            p.part_ml[idx * 2 + 1] = l_run;
+            p.part_ml[idx * 2 + 1] = l_all;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -487,7 +539,7 @@ int fsie_attn_tc(const void* pages_map, int entries, int entry, const void* q, i
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attn_tc_kernel<<<dim3(tiles, kv_heads, nsplit), 192, SMEM_BYTES, stream>>>(map, p, x);
+    attn_tc_kernel<<<dim3(tiles, kv_heads, nsplit), THREADS, SMEM_BYTES, stream>>>(map, p, x);
     int rc = (int)cudaGetLastError();
     if (rc != 0 || nsplit == 1) return rc;
     const int count = combine_tokens ? num_combine : tokens;
