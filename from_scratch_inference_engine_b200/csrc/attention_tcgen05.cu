@@ -3,20 +3,22 @@
 // by TMA, bfloat16 storage, 32-bit scores / softmax statistics / accumulation.
 // Compiled per head size (-DHEAD_DIM=64 or 128).
 //
-// A block owns 128 query rows of one request and one kv head - a row is a (new token, head of
-// the group) pair as in attention_mma.cu - and walks the keys in tiles of 128:
+// A block owns 256 query rows of one request and one kv head - a row is a (new token, head of
+// the group) pair as in attention_mma.cu - as two streams A and B of 128 rows each (one
+// tensor-memory lane per row), and walks the keys in tiles of 128.  Both streams use the same
+// key and value tiles, so each tile is fetched once for 256 rows, and while the softmax of one
+// stream runs on the CUDA cores the tensor core works for the other:
 //
-//   producer warp   TMA: one cp.async.bulk.tensor per page and 128-byte column half, for K and V,
-//                   into a 2-stage ring (full/empty mbarriers), 128-byte swizzle
-//   MMA warp        S[i] = Q K_i^T  (128 x 128 x head_dim, A and B K-major) into one of two score
-//                   buffers in tensor memory, issued one tile ahead of the softmax;
-//                   O += P_i V_i    (128 x head_dim x 128, A = P from shared memory, B = V
-//                   MN-major straight from its [key][dim] tile)
-//   8 softmax warps two threads per row (= tensor-memory lane), 64 keys of the tile each: read S,
-//                   mask, running maximum (exchanged between the two once per tile) and sum, write
-//                   P as bfloat16 into shared memory in the swizzled K-major layout, rescale O in
-//                   tensor memory when a row's maximum moved, finally normalise O and store it
-//                   (or a partial result when the key range is split)
+//   producer warp   TMA: one cp.async.bulk.tensor per page and 128-byte column half; K and V
+//                   tiles take turns in a ring of three slots (full/empty mbarriers), 128-byte swizzle
+//   MMA warp        S_X = Q_X K_i^T  (128 x 128 x head_dim, A and B K-major) into the stream's score
+//                   columns of tensor memory; O_X += P_X V_i  (128 x head_dim x 128, A = P from
+//                   shared memory, B = V MN-major straight from its [key][dim] tile); for each
+//                   stream in turn: P V of tile i, then Q K^T of tile i + 1
+//   2 x 4 softmax   one thread per row: read S, mask, running maximum and sum, write P as bfloat16
+//   warps           into shared memory in the swizzled K-major layout, rescale O in tensor memory
+//                   when a row's maximum moved, finally normalise O and store it (or a partial
+//                   result when the key range is split)
 //
 // Formula: src/model/nn.cpp:151-226 of the reference, as a running softmax.
 // Every wait on an mbarrier is bounded; when one runs out *error is set, all roles leave their
@@ -35,31 +37,31 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size 64 or 128");
 namespace fsie {
 
 constexpr int HD = HEAD_DIM;
-constexpr int BM = 128;                 // query rows per block = tensor-memory lanes
+constexpr int BM = 128;                 // query rows per stream = tensor-memory lanes
+constexpr int STREAMS = 2;              // streams of query rows per block
 constexpr int BN = 128;                 // keys per tile
-constexpr int STAGES = 2;
-constexpr int SOFTMAX_WARPS = 8;        // two per quarter of the tensor-memory lanes
+constexpr int SLOTS = 3;                // ring of key / value tiles: K_i, V_i, K_i+1
+constexpr int SOFTMAX_WARPS = 4 * STREAMS;
 constexpr int THREADS = 64 + 32 * SOFTMAX_WARPS;
 constexpr int HALVES = HD / 64;         // 128-byte column halves of a row of head_dim elements
 constexpr int ATOM_BYTES = 128 * 128;   // 128 rows x 128 bytes: one swizzled block
-constexpr int Q_BYTES = HALVES * ATOM_BYTES;
+constexpr int Q_BYTES = HALVES * ATOM_BYTES;           // one stream's queries
 constexpr int KV_BYTES = HALVES * ATOM_BYTES;          // one K or V tile
-constexpr int P_BYTES = (BN / 64) * ATOM_BYTES;        // P[128 rows, 128 keys] bf16; two of them
-constexpr int TILE_BYTES = Q_BYTES + 2 * P_BYTES + STAGES * 2 * KV_BYTES;
-// Barriers and the softmax warps' exchange area come first in the block's (dynamic only) shared
-// memory, the swizzled tiles follow at the next 1,024-byte boundary.  With head size 128 this is
-// all the shared memory an SM offers to a block (227 KB), so the kernel has no static shared
-// memory and relies on the window starting on such a boundary; it checks and refuses otherwise.
+constexpr int P_BYTES = (BN / 64) * ATOM_BYTES;        // P[128 rows, 128 keys] bf16, one per stream
+constexpr int TILE_BYTES = STREAMS * Q_BYTES + STREAMS * P_BYTES + SLOTS * KV_BYTES;
+// Barriers come first in the block's (dynamic only) shared memory, the swizzled tiles follow at
+// the next 1,024-byte boundary.  With head size 128 this is all the shared memory an SM offers
+// to a block (227 KB), so the kernel has no static shared memory and relies on the window
+// starting on such a boundary; it checks and refuses otherwise.
 struct Control {
-    uint64_t kv_full[STAGES], kv_empty[STAGES], s_full[2], p_ready, o_done[2], pair_bar[4];
+    uint64_t ring_full[SLOTS], ring_empty[SLOTS], s_full[STREAMS], p_ready[STREAMS], o_done[STREAMS];
     uint32_t tmem_slot;
     int abort_flag;
-    float pair_xchg[2][2][BM];          // [exchange parity][half of the keys][row]
 };
-static_assert(sizeof(Control) <= 3072, "control block");
-constexpr int SMEM_BYTES = 3072 + TILE_BYTES;
-constexpr uint32_t TMEM_COLS = 512;     // S0 | S1 | O  (128 + 128 + head_dim columns), power of two
-constexpr uint32_t COL_S0 = 0, COL_S1 = BN, COL_O = 2 * BN;
+static_assert(sizeof(Control) <= 1024, "control block");
+constexpr int SMEM_BYTES = 1024 + TILE_BYTES;
+constexpr uint32_t TMEM_COLS = 512;     // S_A | S_B | O_A | O_B, 128 columns each
+constexpr uint32_t COL_S = 0, COL_O = STREAMS * BN;
 enum { ERR_TC_PRODUCER = 31, ERR_TC_MMA = 32, ERR_TC_SOFTMAX = 33, ERR_TC_LAYOUT = 34 };
 
 struct TcExtra { int entries, entry; int* error; };
@@ -159,14 +161,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         if (threadIdx.x == 0) atomicExch(x.error, ERR_TC_LAYOUT);
         return;
     }
-    uint64_t (&kv_full)[STAGES] = ctl.kv_full, (&kv_empty)[STAGES] = ctl.kv_empty, (&s_full)[2] = ctl.s_full;
-    uint64_t &p_ready = ctl.p_ready, (&o_done)[2] = ctl.o_done, (&pair_bar)[4] = ctl.pair_bar;
-    uint32_t& tmem_slot = ctl.tmem_slot;
+    unsigned char* q_s = smem;                               // [stream][HALVES][128 rows][128 B]
+    unsigned char* p_s = q_s + STREAMS * Q_BYTES;            // [stream][2][128 rows][128 B]: keys 0-63 | 64-127
+    unsigned char* ring = p_s + STREAMS * P_BYTES;           // [slot][HALVES][128 keys][128 B]
     int& abort_flag = ctl.abort_flag;
-    float (&pair_xchg)[2][2][BM] = ctl.pair_xchg;
-    unsigned char* q_s = smem;                               // [HALVES][128 rows][128 B]
-    unsigned char* p_s = q_s + Q_BYTES;                      // [2 buffers][2][128 rows][128 B]: keys 0-63 | 64-127
-    unsigned char* kv_s = p_s + 2 * P_BYTES;                     // [STAGES][K | V][HALVES][128 keys][128 B]
 
     // later tiles of a prompt see more keys: start them first so that the last wave is short
     const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -174,7 +172,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     const int item = p.tile_item[tile];
     const int row0 = p.tile_row0[tile];
     const int qstart = p.item_qstart[item], qlen = p.item_qlen[item], pos0 = p.item_pos0[item];
-    const int nrows = min(BM, qlen * group - row0);
+    const int nrows = min(STREAMS * BM, qlen * group - row0);
+    const int streams = nrows > BM ? 2 : 1;                  // a short tile leaves stream B idle
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bf16* q = (const bf16*)p.q;
     const int* bt = p.block_tables + (size_t)item * p.bt_stride;
@@ -194,69 +193,69 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     kbegin = kbegin / BN * BN;          // tiles hold whole pages; keys before the window are masked
     const int ntiles = kend > kbegin ? (kend - kbegin + BN - 1) / BN : 0;
 
-    // ---- set-up: barriers, tensor memory, zeroed stages (pages never fetched must read as finite
-    // numbers), the query tile in the swizzled K-major layout
+    // ---- set-up: barriers, tensor memory, zeroed P and ring (pages never fetched must read as
+    // finite numbers), the query rows in the swizzled K-major layout
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
-        mbar_init(&p_ready, 32 * SOFTMAX_WARPS); mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
-        for (int qt = 0; qt < 4; ++qt) mbar_init(&pair_bar[qt], 64);
+        for (int s = 0; s < SLOTS; ++s) { mbar_init(&ctl.ring_full[s], 1); mbar_init(&ctl.ring_empty[s], 1); }
+        for (int st = 0; st < STREAMS; ++st) {
+            mbar_init(&ctl.s_full[st], 1); mbar_init(&ctl.p_ready[st], BM); mbar_init(&ctl.o_done[st], 1);
+        }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&ctl.tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int e = tid; e < (2 * P_BYTES + STAGES * 2 * KV_BYTES) / 16; e += blockDim.x)
+    for (int e = tid; e < (STREAMS * P_BYTES + SLOTS * KV_BYTES) / 16; e += blockDim.x)
         reinterpret_cast<uint4*>(p_s)[e] = make_uint4(0, 0, 0, 0);
-    for (int e = tid; e < BM * (HD / 8); e += blockDim.x) {
-        const int r = e / (HD / 8), c = e - r * (HD / 8);     // 16-byte chunk c of row r
+    for (int e = tid; e < STREAMS * BM * (HD / 8); e += blockDim.x) {
+        const int r = e / (HD / 8), c = e - r * (HD / 8);     // 16-byte chunk c of row r of the block
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < nrows) {
             const int row = row0 + r;
             const int tok = qstart + row / group, h = kvh * group + row % group;
             v = *reinterpret_cast<const uint4*>(q + (size_t)tok * p.q_ld + h * HD + c * 8);
         }
-        *reinterpret_cast<uint4*>(q_s + (c >> 3) * ATOM_BYTES + swizzled(r, c & 7)) = v;
+        *reinterpret_cast<uint4*>(q_s + (r / BM) * Q_BYTES + (c >> 3) * ATOM_BYTES + swizzled(r % BM, c & 7)) = v;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes before async-proxy reads
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = tmem_slot;
+    const uint32_t tmem = ctl.tmem_slot;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        // lane j looks up and fetches page j of the tile: the table reads and the copy
-        // instructions of a tile go out side by side instead of one after the other
+        // ring entry 2 i is K of tile i, entry 2 i + 1 its V.  Lane j looks up and fetches page j of
+        // the tile: the table reads and the copy instructions go out side by side.
         const int ps = p.page_size, pages_per_tile = BN / ps;
         const long long rows_per_page = (long long)x.entries * 2 * p.kv_heads * ps;
         const long long k_row0 = ((long long)x.entry * 2) * p.kv_heads * ps + (long long)kvh * ps;
         const long long v_row0 = k_row0 + (long long)p.kv_heads * ps;
         for (int i = 0; i < ntiles; ++i) {
-            const int s = i % STAGES;
             const int key = kbegin + i * BN + lane * ps;
             const int page = (lane < pages_per_tile && key < kend) ? bt[key / ps] : -1;   // before the wait: overlaps it
+            const int wanted = __popc(__ballot_sync(0xffffffffu, page >= 0));
             bool ok = true;
-            if (lane == 0 && i >= STAGES) ok = mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1);
-            ok = __shfl_sync(0xffffffffu, ok, 0) && !*(volatile int*)&abort_flag;
+#pragma unroll
+            for (int kv = 0; kv < 2 && ok; ++kv) {
+                const int e = 2 * i + kv, s = e % SLOTS;
+                if (lane == 0 && e >= SLOTS) ok = mbar_wait(&ctl.ring_empty[s], ((e / SLOTS) - 1) & 1);
+                ok = __shfl_sync(0xffffffffu, ok, 0) && !*(volatile int*)&abort_flag;
+                if (!ok) break;
+                if (lane == 0) mbar_expect_tx(&ctl.ring_full[s], (uint32_t)wanted * ps * HD * 2);
+                __syncwarp();
+                if (page >= 0) {
+                    unsigned char* dst = ring + (size_t)s * KV_BYTES + lane * ps * 128;
+                    const long long row = (long long)page * rows_per_page + (kv ? v_row0 : k_row0);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * ATOM_BYTES, &pages_map, h * 64, (int)row, &ctl.ring_full[s]);
+                }
+            }
             if (!ok) {
                 if (lane == 0) { atomicExch(x.error, ERR_TC_PRODUCER); atomicExch(&abort_flag, 1); }
                 break;
-            }
-            const int wanted = __popc(__ballot_sync(0xffffffffu, page >= 0));
-            if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)wanted * ps * HD * 2 * 2);
-            __syncwarp();
-            if (page >= 0) {
-                unsigned char* kd = kv_s + (size_t)s * 2 * KV_BYTES + lane * ps * 128;
-                unsigned char* vd = kd + KV_BYTES;
-                const long long base = (long long)page * rows_per_page;
-#pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(kd + h * ATOM_BYTES, &pages_map, h * 64, (int)(base + k_row0), &kv_full[s]);
-                    tma_load_2d(vd + h * ATOM_BYTES, &pages_map, h * 64, (int)(base + v_row0), &kv_full[s]);
-                }
             }
         }
     } else if (warp == 1) {
@@ -264,92 +263,87 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         if (lane == 0 && ntiles > 0) {
             const uint32_t idesc_s = idesc_bf16(BM, BN, 0), idesc_o = idesc_bf16(BM, HD, 1);
             bool ok = true;
-            auto scores = [&](int i) {       // S[i % 2] = Q K_i^T
-                const int s = i % STAGES;
-                if (!mbar_wait(&kv_full[s], (i / STAGES) & 1)) {
-                    atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false; return;
+            auto ring_wait = [&](int e) {            // the tile of ring entry e has arrived
+                if (!mbar_wait(&ctl.ring_full[e % SLOTS], (e / SLOTS) & 1)) {
+                    atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned char* kd = kv_s + (size_t)s * 2 * KV_BYTES;
-                const uint32_t d = tmem + ((i & 1) ? COL_S1 : COL_S0);
+            };
+            auto scores = [&](int st, int i) {       // S_st = Q_st K_i^T
+                const unsigned char* kd = ring + (size_t)((2 * i) % SLOTS) * KV_BYTES;
+                const unsigned char* qd = q_s + st * Q_BYTES;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    const uint64_t a = desc_k_major(q_s + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
+                    const uint64_t a = desc_k_major(qd + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
                     const uint64_t b = desc_k_major(kd + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
-                    mma_ss(d, a, b, idesc_s, k > 0);
+                    mma_ss(tmem + COL_S + st * BN, a, b, idesc_s, k > 0);
                 }
-                mma_commit(&s_full[i & 1]);
+                mma_commit(&ctl.s_full[st]);
+                if (st == streams - 1) mma_commit(&ctl.ring_empty[(2 * i) % SLOTS]);     // K_i may be overwritten
             };
-            scores(0);
+            ring_wait(0);
+            for (int st = 0; st < streams && ok; ++st) scores(st, 0);
             for (int i = 0; i < ntiles && ok; ++i) {
-                if (i + 1 < ntiles) scores(i + 1);          // one tile ahead of the softmax
-                if (!ok) break;
-                if (!mbar_wait(&p_ready, i & 1)) {
-                    atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); break;
-                }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int s = i % STAGES;
-                const unsigned char* vd = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
+                for (int st = 0; st < streams && ok; ++st) {
+                    if (!mbar_wait(&ctl.p_ready[st], i & 1)) {
+                        atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false; break;
+                    }
+                    if (st == 0) ring_wait(2 * i + 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned char* vd = ring + (size_t)((2 * i + 1) % SLOTS) * KV_BYTES;
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k) {         // 16 keys per instruction
-                    const uint64_t a = desc_k_major(p_s + (i & 1) * P_BYTES + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
-                    const uint64_t b = desc_mn_major(vd + k * 16 * 128, ATOM_BYTES);
-                    mma_ss(tmem + COL_O, a, b, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BN / 16; ++k) {         // 16 keys per instruction
+                        const uint64_t a = desc_k_major(p_s + st * P_BYTES + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
+                        const uint64_t b = desc_mn_major(vd + k * 16 * 128, ATOM_BYTES);
+                        mma_ss(tmem + COL_O + st * BN, a, b, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit(&ctl.o_done[st]);                // O_st holds tiles 0..i; P_st may be overwritten
+                    if (st == streams - 1) mma_commit(&ctl.ring_empty[(2 * i + 1) % SLOTS]);    // V_i may be overwritten
+                    if (i + 1 < ntiles) {                       // the stream's next scores, while the other's softmax runs
+                        if (st == 0) ring_wait(2 * i + 2);
+                        if (!ok) break;
+                        scores(st, i + 1);
+                    }
                 }
-                mma_commit(&kv_empty[s]);                   // K_i and V_i may be overwritten
-                mma_commit(&o_done[i & 1]);                 // O holds tiles 0..i; this P buffer may be overwritten
             }
         }
-    } else {
-        // ------------------------------------------------------------------ softmax
-        // Two warps share the 32 rows of a tensor-memory quarter: each takes 64 of a tile's 128
-        // keys (and later half of O's columns).  Per tile they exchange one number per row, the
-        // maximum of their halves; the row sums stay apart until the end.
+    } else if ((warp - 2) / 4 < streams) {
+        // ------------------------------------------------------------------ softmax, one thread per row
+        const int st = (warp - 2) / 4;                      // stream A or B
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
-        const int r = quarter * 32 + lane;                  // row of the tile = tensor-memory lane
+        const int r = quarter * 32 + lane;                  // row of the stream = tensor-memory lane
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-        const bool valid = r < nrows;
-        const int pos = valid ? pos0 + (row0 + r) / group : -1;
+        const uint32_t s_addr = lane_base + COL_S + st * BN, o_addr = lane_base + COL_O + st * BN;
+        unsigned char* p_mine = p_s + st * P_BYTES;
+        const bool valid = st * BM + r < nrows;
+        const int pos = valid ? pos0 + (row0 + st * BM + r) / group : -1;
         const int lowest = p.window > 0 ? pos - p.window : -1;       // keys <= this are unseen
         const float sc = p.scale * 1.4426950408889634f;
-        constexpr int HK = BN / 2;                          // keys per warp and tile
-        constexpr int HO = HD / 2;                          // columns of O per warp
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        int exchanges = 0;
-        // hands `mine` to the other warp of the pair and returns what that one handed over
-        auto exchange = [&](float mine, float& theirs) -> bool {
-            pair_xchg[exchanges & 1][half][r] = mine;
-            mbar_arrive(&pair_bar[quarter]);
-            const bool done = mbar_wait(&pair_bar[quarter], exchanges & 1);
-            theirs = pair_xchg[exchanges & 1][half ^ 1][r];
-            ++exchanges;
-            return done;
-        };
         for (int i = 0; i < ntiles && ok; ++i) {
             // (decisions to give up are taken by whole warps: the tensor-memory accesses below are
             // warp-collective)
-            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1))) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&ctl.s_full[st], i & 1))) {
                 if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
                 atomicExch(&abort_flag, 1); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t s_addr = lane_base + ((i & 1) ? COL_S1 : COL_S0) + half * HK;
-            const int k0 = kbegin + i * BN + half * HK;
-            // the row's 64 scores in registers: two reads in flight, one wait
-            uint32_t sr[HK];
+            const int k0 = kbegin + i * BN;
+            // the row's 128 scores in registers: four reads in flight, one wait
+            uint32_t sr[BN];
 #pragma unroll
-            for (int c = 0; c < HK; c += 32) tmem_ld32_issue(s_addr + c, sr + c);
+            for (int c = 0; c < BN; c += 32) tmem_ld32_issue(s_addr + c, sr + c);
             tmem_wait_ld();
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains, not one
-            const bool clear = k0 + HK - 1 < kend && k0 + HK - 1 <= pos && k0 > lowest;   // nothing to mask
+            const bool clear = k0 + BN - 1 < kend && k0 + BN - 1 <= pos && k0 > lowest;   // nothing to mask
             if (__all_sync(0xffffffffu, clear || !valid)) {
 #pragma unroll
-                for (int j = 0; j < HK; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
+                for (int j = 0; j < BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sr[j]));
             } else {
 #pragma unroll
-                for (int j = 0; j < HK; ++j) {
+                for (int j = 0; j < BN; ++j) {
                     const int key = k0 + j;
                     const bool seen = key < kend && key <= pos && key > lowest;
                     if (!seen) sr[j] = 0xff800000u;                    // -inf
@@ -358,12 +352,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             if (!valid) mx = -INFINITY;
-            float other;
-            if (!__all_sync(0xffffffffu, exchange(mx, other))) {
-                if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
-                atomicExch(&abort_flag, 1); ok = false; break;
-            }
-            mx = fmaxf(mx, other);
             // The reference point of the exponentials moves only when the row's maximum has grown
             // by more than 2^8 since it was set: until then p may exceed 1 (by at most 256x, exact
             // enough in float and bfloat16), and O and the row sum need no rescaling.
@@ -371,32 +359,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * sc > 8.f)) m_new = mx;
             const float base = m_new == -INFINITY ? 0.f : m_new * sc;
             const float corr = m_new == m_run ? 1.f : fast_exp2(m_run * sc - base);    // m_run = -inf gives 0
-            // this tile's P buffer was last read by the P V of tile i - 2; O may be rescaled only
-            // after the P V of tile i - 1 (tile t reports to o_done[t % 2], phase t / 2)
             const bool rescale = i > 0 && __any_sync(0xffffffffu, valid && corr != 1.f);
-            bool waited = true;
-            if (i >= 2) waited = mbar_wait(&o_done[i & 1], ((i - 2) >> 1) & 1);
-            if (rescale && waited) waited = mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1);
-            if (!__all_sync(0xffffffffu, waited)) {
+            // P and O of this stream were last touched by the P V of tile i - 1
+            if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], (i - 1) & 1))) {
                 if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
                 atomicExch(&abort_flag, 1); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (rescale) {                                  // this warp's half of O's columns
-                uint32_t orr[HO];
+            if (rescale) {
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t orr[32];
+                    tmem_ld32_issue(o_addr + c, orr);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int c = 0; c < HO; c += 32) tmem_ld32_issue(lane_base + COL_O + half * HO + c, orr + c);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < HO; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * corr);
-#pragma unroll
-                for (int c = 0; c < HO; c += 32) tmem_st32_issue(lane_base + COL_O + half * HO + c, orr + c);
-                tmem_wait_st();
+                    for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * corr);
+                    tmem_st32_issue(o_addr + c, orr);
+                    tmem_wait_st();
+                }
             }
             // p = exp2(s * sc - base), row sum, P as bfloat16 in the swizzled layout
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int chunk = 0; chunk < HK / 8; ++chunk) {                 // 8 keys = one 16-byte chunk
+            for (int chunk = 0; chunk < BN / 8; ++chunk) {                 // 8 keys = one 16-byte chunk
                 float pv[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -407,36 +392,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(pv[2 * j], pv[2 * j + 1]);
-                // keys 0-63 of the tile are the first swizzled block of the P buffer, keys 64-127 the second
-                *reinterpret_cast<uint4*>(p_s + (i & 1) * P_BYTES + half * ATOM_BYTES + swizzled(r, chunk)) = packed;
+                *reinterpret_cast<uint4*>(p_mine + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
             }
             const float sum = valid ? (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]) : 0.f;
             l_run = l_run * corr + sum;
             m_run = m_new;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P before the tensor core reads it
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");  // O rescale before the next MMA
-            mbar_arrive(&p_ready);
+            mbar_arrive(&ctl.p_ready[st]);
         }
         // ---- the last P V, then normalise and store (or hand a partial result to the merge)
         bool have = ok && ntiles > 0;
-        if (have && !__all_sync(0xffffffffu, mbar_wait(&o_done[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1))) {
+        if (have && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], (ntiles - 1) & 1))) {
             if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
             atomicExch(&abort_flag, 1); have = false;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        float l_other = 0.f;
-        if (ok && !__all_sync(0xffffffffu, exchange(l_run, l_other))) {       // the row sum of all keys
-            if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
-            atomicExch(&abort_flag, 1); have = false;
-        }
-        const float l_all = l_run + l_other;
-        const int row = row0 + (valid ? r : 0);
+        const int row = row0 + (valid ? st * BM + r : 0);
         const int tok = qstart + row / group, h = kvh * group + row % group;
-        const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll 1
-        for (int c = half * HO; c < (half + 1) * HO; c += 32) {
+        for (int c = 0; c < HD; c += 32) {
             float v[32];
-            if (have) tmem_ld32(lane_base + COL_O + c, v);       // warp-collective: every lane takes part
+            if (have) tmem_ld32(o_addr + c, v);       // warp-collective: every lane takes part
             else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.f;
@@ -461,10 +439,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                     *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
         }
-        if (valid && half == 0 && p.nsplit > 1) {
+        if (valid && p.nsplit > 1) {
             const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
             p.part_ml[idx * 2] = m_run == -INFINITY ? -INFINITY : m_run * p.scale;
-            p.part_ml[idx * 2 + 1] = l_all;
+            p.part_ml[idx * 2 + 1] = l_run;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -482,7 +460,7 @@ using namespace fsie;
 extern "C" {
 
 int fsie_attn_tc_head_dim() { return HD; }
-int fsie_attn_tc_rows() { return BM; }
+int fsie_attn_tc_rows() { return STREAMS * BM; }
 int fsie_attn_tc_map_bytes() { return (int)sizeof(CUtensorMap); }
 
 // Tensor map of a cache group's pages [num_pages, entries, 2, kv_heads, page_size, head_dim] seen
@@ -506,7 +484,7 @@ int fsie_attn_tc_pages_map(void* map_out, const void* pages, long long total_row
     return 0;
 }
 
-// Tiles of 128 query rows.  Arguments as fsie_attn_tma (attention_tma.cu).
+// Tiles of 256 query rows.  Arguments as fsie_attn_tma (attention_tma.cu).
 int fsie_attn_tc(const void* pages_map, int entries, int entry, const void* q, int q_ld, int page_size,
                  const int* block_tables, int bt_stride, const int* tile_item, const int* tile_row0, int tiles,
                  const int* item_qstart, const int* item_qlen, const int* item_pos0, void* out, int out_ld,

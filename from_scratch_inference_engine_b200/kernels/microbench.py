@@ -111,7 +111,8 @@ def run_attention(args, timer, decode: bool):
     nsplit = args.nsplit
     if nsplit <= 0:
         from ..parts.attention import attention_splits
-        nsplit = attention_splits(tile_item.numel() * kv_heads, args.context, sms, decode)
+        nsplit = attention_splits(tile_item.numel() * kv_heads, args.context, sms, decode,
+                                  1 if args.variant == "tc" and row_class == 2 else 2)
     part_o = torch.empty(max(1, nsplit * tokens * heads * hd), device="cuda")
     part_ml = torch.empty(max(1, nsplit * tokens * heads * 2), device="cuda")
     scale = 1.0 / math.sqrt(hd)

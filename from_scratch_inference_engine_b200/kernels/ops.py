@@ -328,7 +328,7 @@ def attn_tma(head_dim: int):
 _attn_tc = {}
 ATTENTION_TC_PAGES = (8, 16, 32, 64, 128)
 ATTENTION_TC_HEAD_DIMS = (64, 128)
-ATTENTION_TC_ROWS = 128
+ATTENTION_TC_ROWS = 256
 
 
 def attn_tc(head_dim: int):

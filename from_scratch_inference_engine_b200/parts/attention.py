@@ -14,18 +14,22 @@ from ..weights.tensor_spec import TensorSpec
 from .base import LayerCache, Mixer, build_part, register_part
 
 
-def attention_splits(blocks: int, longest: int, sms: int, even_work: bool) -> int:
+def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
+                     blocks_per_sm: int = 2) -> int:
     """Into how many key ranges to split each tile (at most 32, each at least 128 keys).
 
     Tiles of decoded tokens all have the same work, so the time is waves x (fixed cost of a
     block + keys per range); measured at batch 64 and context 4,096 the fixed cost equals
     about 270 keys and three blocks fit on an SM.  Tiles of a prompt have uneven work and
-    are split only when there are fewer of them than block slots."""
+    are split only when there are fewer of them than block slots (`blocks_per_sm` per SM;
+    the tcgen05 kernel has one, and its partial results cost more than a little idling, so
+    it splits only to fill slots that would stay empty)."""
     if not even_work:
-        slots = 2 * sms
+        slots = blocks_per_sm * sms
         if blocks >= slots:
             return 1
-        return max(1, min(-(-slots // blocks), longest // 128, 32))
+        wanted = slots // blocks if blocks_per_sm == 1 else -(-slots // blocks)
+        return max(1, min(wanted, longest // 128, 32))
     slots = 3 * sms
     best, best_cost = 1, None
     for n in range(1, max(1, min(32, longest // 128)) + 1):
@@ -115,13 +119,13 @@ class GqaAttention(Mixer):
         group_size = self.num_heads // self.num_kv_heads
         sms = ctx.runtime.sm_count
 
-        def splits(blocks: int, longest: int, even_work: bool = False) -> int:
-            return attention_splits(blocks, longest, sms, even_work)
+        def splits(blocks: int, longest: int, even_work: bool = False, blocks_per_sm: int = 2) -> int:
+            return attention_splits(blocks, longest, sms, even_work, blocks_per_sm)
 
         common = (cache.k_pages, cache.v_pages, cache.page_stride, group.page_size,
                   group.block_tables)
         if qkv.dtype is torch.bfloat16 and self.head_dim % 16 == 0:
-            # prompt portions (the last row class) run on tcgen05 in tiles of 128 rows where the
+            # prompt portions (the last row class) run on tcgen05 in tiles of 256 rows where the
             # head size and the page size allow it
             pages_map = ctx.runtime.pages_map(cache.pages) if cache.pages is not None else None
             class_rows = ops.ATTENTION_ROW_CLASSES
@@ -129,12 +133,14 @@ class GqaAttention(Mixer):
                 class_rows = class_rows[:-1] + (ops.ATTENTION_TC_ROWS,)
             for row_class, tiles, class_tokens, count, longest in \
                     ctx.attention_row_classes(group_size, class_rows):
-                nsplit = splits(tiles.count * self.num_kv_heads, longest, row_class == 0)
+                on_tcgen05 = pages_map is not None and row_class == len(class_rows) - 1
+                nsplit = splits(tiles.count * self.num_kv_heads, longest, row_class == 0,
+                                1 if on_tcgen05 else 2)
                 part_o = part_ml = None
                 if nsplit > 1:
                     part_o = ctx.scratch("attention.part_o", nsplit * tokens * self.q_width)
                     part_ml = ctx.scratch("attention.part_ml", nsplit * tokens * self.num_heads * 2)
-                if pages_map is not None and row_class == len(class_rows) - 1:
+                if on_tcgen05:
                     ops.attention_tc(pages_map, cache.entry_index, qkv, qkv.stride(0),
                                      group.block_tables, tiles.item, tiles.row0, tiles.count,
                                      ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out, tokens,
