@@ -10,15 +10,19 @@
 // stream runs on the CUDA cores the tensor core works for the other:
 //
 //   producer warp   TMA: one cp.async.bulk.tensor per page and 128-byte column half; K and V
-//                   tiles take turns in a ring of three slots (full/empty mbarriers), 128-byte swizzle
-//   MMA warp        S_X = Q_X K_i^T  (128 x 128 x head_dim, A and B K-major) into the stream's score
-//                   columns of tensor memory; O_X += P_X V_i  (128 x head_dim x 128, A = P from
-//                   shared memory, B = V MN-major straight from its [key][dim] tile); for each
-//                   stream in turn: P V of tile i, then Q K^T of tile i + 1
+//                   tiles take turns in a ring of five slots (full/empty mbarriers), 128-byte swizzle
+//   MMA warp        S_X = Q_X K_i^T  (128 x 128 x head_dim, A and B K-major from shared memory) into
+//                   the stream's score columns of tensor memory; O_X += P_X V_i  (128 x head_dim x
+//                   128, A = P from tensor memory, B = V MN-major straight from its [key][dim]
+//                   tile); for each stream in turn: P V of tile i, then Q K^T of tile i + 1.
+//                   (A second issuing thread, one per stream, measured slower: 685 against 833
+//                   TFLOP/s at 8,192 tokens.)
 //   2 x 4 softmax   one thread per row: read S, mask, running maximum and sum, write P as bfloat16
-//   warps           into shared memory in the swizzled K-major layout, rescale O in tensor memory
-//                   when a row's maximum moved, finally normalise O and store it (or a partial
-//                   result when the key range is split)
+//   warps           pairs over the first half of the S columns it has just read (shared memory is
+//                   the scarce resource here: operands read by the MMAs, tiles written by TMA;
+//                   P never passes through it), rescale O in tensor memory when a row's maximum
+//                   moved, finally normalise O and store it (or a partial result when the key
+//                   range is split)
 //
 // Formula: src/model/nn.cpp:151-226 of the reference, as a running softmax.
 // Every wait on an mbarrier is bounded; when one runs out *error is set, all roles leave their
@@ -40,15 +44,14 @@ constexpr int HD = HEAD_DIM;
 constexpr int BM = 128;                 // query rows per stream = tensor-memory lanes
 constexpr int STREAMS = 2;              // streams of query rows per block
 constexpr int BN = 128;                 // keys per tile
-constexpr int SLOTS = 3;                // ring of key / value tiles: K_i, V_i, K_i+1
+constexpr int SLOTS = 5;                // ring of key / value tiles: K_i, V_i, K_i+1, ...
 constexpr int SOFTMAX_WARPS = 4 * STREAMS;
 constexpr int THREADS = 64 + 32 * SOFTMAX_WARPS;
 constexpr int HALVES = HD / 64;         // 128-byte column halves of a row of head_dim elements
 constexpr int ATOM_BYTES = 128 * 128;   // 128 rows x 128 bytes: one swizzled block
 constexpr int Q_BYTES = HALVES * ATOM_BYTES;           // one stream's queries
 constexpr int KV_BYTES = HALVES * ATOM_BYTES;          // one K or V tile
-constexpr int P_BYTES = (BN / 64) * ATOM_BYTES;        // P[128 rows, 128 keys] bf16, one per stream
-constexpr int TILE_BYTES = STREAMS * Q_BYTES + STREAMS * P_BYTES + SLOTS * KV_BYTES;
+constexpr int TILE_BYTES = STREAMS * Q_BYTES + SLOTS * KV_BYTES;
 // Barriers come first in the block's (dynamic only) shared memory, the swizzled tiles follow at
 // the next 1,024-byte boundary.  With head size 128 this is all the shared memory an SM offers
 // to a block (227 KB), so the kernel has no static shared memory and relies on the window
@@ -60,11 +63,19 @@ struct Control {
 };
 static_assert(sizeof(Control) <= 1024, "control block");
 constexpr int SMEM_BYTES = 1024 + TILE_BYTES;
-constexpr uint32_t TMEM_COLS = 512;     // S_A | S_B | O_A | O_B, 128 columns each
+constexpr uint32_t TMEM_COLS = 512;     // S_A | S_B | O_A | O_B, 128 columns each; P_X (bfloat16 pairs) over the first 64 of S_X
 constexpr uint32_t COL_S = 0, COL_O = STREAMS * BN;
 enum { ERR_TC_PRODUCER = 31, ERR_TC_MMA = 32, ERR_TC_SOFTMAX = 33, ERR_TC_LAYOUT = 34 };
 
 struct TcExtra { int entries, entry; int* error; };
+#ifdef FSIE_TC_TIMING
+// cycles spent by one softmax warp (with FSIE_TC_TIMING_MMA: by the MMA thread) per phase, summed
+// over all blocks (measurement builds only)
+__device__ unsigned long long fsie_tc_timing[8];
+#define TC_MARK(slot) do { const long long now_ = clock64(); phase_[slot] += (unsigned)(now_ - mark_); mark_ = now_; } while (0)
+#else
+#define TC_MARK(slot) do { } while (0)
+#endif
 
 }  // namespace fsie
 #include "attention_combine.cuh"
@@ -91,6 +102,11 @@ __device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int b_mn_major) {
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// the same with A[128, 16] read from tensor memory (lane = row, 8 columns of bfloat16 pairs)
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -162,8 +178,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         return;
     }
     unsigned char* q_s = smem;                               // [stream][HALVES][128 rows][128 B]
-    unsigned char* p_s = q_s + STREAMS * Q_BYTES;            // [stream][2][128 rows][128 B]: keys 0-63 | 64-127
-    unsigned char* ring = p_s + STREAMS * P_BYTES;           // [slot][HALVES][128 keys][128 B]
+    unsigned char* ring = q_s + STREAMS * Q_BYTES;           // [slot][HALVES][128 keys][128 B]
     int& abort_flag = ctl.abort_flag;
 
     // later tiles of a prompt see more keys: start them first so that the last wave is short
@@ -193,8 +208,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     kbegin = kbegin / BN * BN;          // tiles hold whole pages; keys before the window are masked
     const int ntiles = kend > kbegin ? (kend - kbegin + BN - 1) / BN : 0;
 
-    // ---- set-up: barriers, tensor memory, zeroed P and ring (pages never fetched must read as
-    // finite numbers), the query rows in the swizzled K-major layout
+    // ---- set-up: barriers, tensor memory, zeroed ring (pages never fetched must read as finite
+    // numbers), the query rows in the swizzled K-major layout
     if (tid == 0) {
         for (int s = 0; s < SLOTS; ++s) { mbar_init(&ctl.ring_full[s], 1); mbar_init(&ctl.ring_empty[s], 1); }
         for (int st = 0; st < STREAMS; ++st) {
@@ -207,8 +222,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&ctl.tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int e = tid; e < (STREAMS * P_BYTES + SLOTS * KV_BYTES) / 16; e += blockDim.x)
-        reinterpret_cast<uint4*>(p_s)[e] = make_uint4(0, 0, 0, 0);
+    for (int e = tid; e < (SLOTS * KV_BYTES) / 16; e += blockDim.x)
+        reinterpret_cast<uint4*>(ring)[e] = make_uint4(0, 0, 0, 0);
     for (int e = tid; e < STREAMS * BM * (HD / 8); e += blockDim.x) {
         const int r = e / (HD / 8), c = e - r * (HD / 8);     // 16-byte chunk c of row r of the block
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -263,20 +278,36 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         if (lane == 0 && ntiles > 0) {
             const uint32_t idesc_s = idesc_bf16(BM, BN, 0), idesc_o = idesc_bf16(BM, HD, 1);
             bool ok = true;
+#ifdef FSIE_TC_TIMING_MMA
+            unsigned long long t_ring = 0, t_p = 0;
+            const long long t_begin = clock64();
+#endif
             auto ring_wait = [&](int e) {            // the tile of ring entry e has arrived
+#ifdef FSIE_TC_TIMING_MMA
+                const long long t0_ = clock64();
+#endif
                 if (!mbar_wait(&ctl.ring_full[e % SLOTS], (e / SLOTS) & 1)) {
                     atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#ifdef FSIE_TC_TIMING_MMA
+                t_ring += clock64() - t0_;
+#endif
             };
+            // Descriptors differ from one MMA to the next only by a constant in their address field
+            // (16-byte units): the issuing thread adds it to a base made once.
+            const uint64_t q_base = desc_k_major(q_s), k_base = desc_k_major(ring), v_base = desc_mn_major(ring, ATOM_BYTES);
             auto scores = [&](int st, int i) {       // S_st = Q_st K_i^T
-                const unsigned char* kd = ring + (size_t)((2 * i) % SLOTS) * KV_BYTES;
-                const unsigned char* qd = q_s + st * Q_BYTES;
+                const uint64_t qd = q_base + (uint64_t)(st * (Q_BYTES >> 4));
+                const uint64_t kd = k_base + (uint64_t)(((2 * i) % SLOTS) * (KV_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    const uint64_t a = desc_k_major(qd + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
-                    const uint64_t b = desc_k_major(kd + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
-                    mma_ss(tmem + COL_S + st * BN, a, b, idesc_s, k > 0);
+#ifdef FSIE_TC_SKIP_QK
+                    break;
+#endif
+                    // 16 elements along the head: 32 bytes inside the swizzled row; 64: the next block
+                    const uint32_t step = (k >> 2) * (ATOM_BYTES >> 4) + 2 * (k & 3);
+                    mma_ss(tmem + COL_S + st * BN, qd + step, kd + step, idesc_s, k > 0);
                 }
                 mma_commit(&ctl.s_full[st]);
                 if (st == streams - 1) mma_commit(&ctl.ring_empty[(2 * i) % SLOTS]);     // K_i may be overwritten
@@ -285,20 +316,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             for (int st = 0; st < streams && ok; ++st) scores(st, 0);
             for (int i = 0; i < ntiles && ok; ++i) {
                 for (int st = 0; st < streams && ok; ++st) {
+#ifdef FSIE_TC_TIMING_MMA
+                    const long long t0_ = clock64();
+#endif
                     if (!mbar_wait(&ctl.p_ready[st], i & 1)) {
                         atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false; break;
                     }
+#ifdef FSIE_TC_TIMING_MMA
+                    t_p += clock64() - t0_;
+#endif
                     if (st == 0) ring_wait(2 * i + 1);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned char* vd = ring + (size_t)((2 * i + 1) % SLOTS) * KV_BYTES;
+                    const uint64_t vd = v_base + (uint64_t)(((2 * i + 1) % SLOTS) * (KV_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < BN / 16; ++k) {         // 16 keys per instruction
-                        const uint64_t a = desc_k_major(p_s + st * P_BYTES + (k >> 2) * ATOM_BYTES) + 2 * (k & 3);
-                        const uint64_t b = desc_mn_major(vd + k * 16 * 128, ATOM_BYTES);
-                        mma_ss(tmem + COL_O + st * BN, a, b, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+#ifdef FSIE_TC_SKIP_PV
+                        break;
+#endif
+                        // 16 keys of P: 8 columns of bfloat16 pairs in the stream's score columns;
+                        // 16 keys of V: 16 rows of 128 bytes
+                        mma_ts(tmem + COL_O + st * BN, tmem + COL_S + st * BN + k * 8, vd + (uint64_t)(k * (16 * 128 >> 4)),
+                               idesc_o, (i > 0 || k > 0) ? 1u : 0u);
                     }
-                    mma_commit(&ctl.o_done[st]);                // O_st holds tiles 0..i; P_st may be overwritten
+                    mma_commit(&ctl.o_done[st]);                // O_st holds tiles 0..i
                     if (st == streams - 1) mma_commit(&ctl.ring_empty[(2 * i + 1) % SLOTS]);    // V_i may be overwritten
                     if (i + 1 < ntiles) {                       // the stream's next scores, while the other's softmax runs
                         if (st == 0) ring_wait(2 * i + 2);
@@ -307,6 +348,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                     }
                 }
             }
+#ifdef FSIE_TC_TIMING_MMA
+            atomicAdd(&fsie_tc_timing[0], t_p);
+            atomicAdd(&fsie_tc_timing[1], t_ring);
+            atomicAdd(&fsie_tc_timing[2], (unsigned long long)(clock64() - t_begin) - t_p - t_ring);
+            atomicAdd(&fsie_tc_timing[6], (unsigned long long)ntiles);
+#endif
         }
     } else if ((warp - 2) / 4 < streams) {
         // ------------------------------------------------------------------ softmax, one thread per row
@@ -315,13 +362,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         const int r = quarter * 32 + lane;                  // row of the stream = tensor-memory lane
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         const uint32_t s_addr = lane_base + COL_S + st * BN, o_addr = lane_base + COL_O + st * BN;
-        unsigned char* p_mine = p_s + st * P_BYTES;
         const bool valid = st * BM + r < nrows;
         const int pos = valid ? pos0 + (row0 + st * BM + r) / group : -1;
         const int lowest = p.window > 0 ? pos - p.window : -1;       // keys <= this are unseen
         const float sc = p.scale * 1.4426950408889634f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
+#ifdef FSIE_TC_TIMING
+        unsigned phase_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long mark_ = clock64();
+#endif
         for (int i = 0; i < ntiles && ok; ++i) {
             // (decisions to give up are taken by whole warps: the tensor-memory accesses below are
             // warp-collective)
@@ -330,12 +380,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 atomicExch(&abort_flag, 1); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            TC_MARK(0);
+#ifdef FSIE_TC_NO_SOFTMAX
+            if (i > 0) mbar_wait(&ctl.o_done[st], (i - 1) & 1);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&ctl.p_ready[st]);
+            continue;
+#endif
             const int k0 = kbegin + i * BN;
             // the row's 128 scores in registers: four reads in flight, one wait
             uint32_t sr[BN];
 #pragma unroll
             for (int c = 0; c < BN; c += 32) tmem_ld32_issue(s_addr + c, sr + c);
             tmem_wait_ld();
+            TC_MARK(1);
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains, not one
             const bool clear = k0 + BN - 1 < kend && k0 + BN - 1 <= pos && k0 > lowest;   // nothing to mask
             if (__all_sync(0xffffffffu, clear || !valid)) {
@@ -360,12 +418,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             const float base = m_new == -INFINITY ? 0.f : m_new * sc;
             const float corr = m_new == m_run ? 1.f : fast_exp2(m_run * sc - base);    // m_run = -inf gives 0
             const bool rescale = i > 0 && __any_sync(0xffffffffu, valid && corr != 1.f);
-            // P and O of this stream were last touched by the P V of tile i - 1
-            if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], (i - 1) & 1))) {
+            TC_MARK(2);
+            // O of this stream was last touched by the P V of tile i - 1.  (P needs no such wait: it
+            // lies over S, and the tensor core finished that P V before it wrote this S.)
+            if (rescale && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], (i - 1) & 1))) {
                 if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
                 atomicExch(&abort_flag, 1); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            TC_MARK(3);
             if (rescale) {
 #pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
@@ -378,29 +439,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                     tmem_wait_st();
                 }
             }
-            // p = exp2(s * sc - base), row sum, P as bfloat16 in the swizzled layout
+            // p = exp2(s * sc - base), row sum, P as bfloat16 pairs (key 2 c low, key 2 c + 1 high in
+            // column c) over the registers that held the scores
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int chunk = 0; chunk < BN / 8; ++chunk) {                 // 8 keys = one 16-byte chunk
-                float pv[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    pv[j] = fast_exp2(fmaf(__uint_as_float(sr[chunk * 8 + j]), sc, -base));
-                    sum4[j & 3] += pv[j];
-                }
-                uint4 packed;
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(pv[2 * j], pv[2 * j + 1]);
-                *reinterpret_cast<uint4*>(p_mine + (chunk >> 3) * ATOM_BYTES + swizzled(r, chunk & 7)) = packed;
+            for (int j = 0; j < BN; j += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[j]), sc, -base));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[j + 1]), sc, -base));
+                sum4[(j >> 1) & 1] += p0;
+                sum4[2 + ((j >> 1) & 1)] += p1;
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                sr[j >> 1] = *reinterpret_cast<uint32_t*>(&h2);
             }
+#pragma unroll
+            for (int c = 0; c < BN / 2; c += 32) tmem_st32_issue(s_addr + c, sr + c);
+            tmem_wait_st();
             const float sum = valid ? (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]) : 0.f;
             l_run = l_run * corr + sum;
             m_run = m_new;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P before the tensor core reads it
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");  // O rescale before the next MMA
+            TC_MARK(4);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");  // P (and a rescaled O) before the next MMA
             mbar_arrive(&ctl.p_ready[st]);
+            TC_MARK(5);
         }
+#if defined(FSIE_TC_TIMING) && !defined(FSIE_TC_TIMING_MMA)
+        if (warp == 2 && lane == 0) {
+            for (int k = 0; k < 6; ++k) atomicAdd(&fsie_tc_timing[k], (unsigned long long)phase_[k]);
+            atomicAdd(&fsie_tc_timing[6], (unsigned long long)ntiles);
+        }
+#endif
         // ---- the last P V, then normalise and store (or hand a partial result to the merge)
         bool have = ok && ntiles > 0;
         if (have && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], (ntiles - 1) & 1))) {
@@ -458,6 +525,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
 using namespace fsie;
 
 extern "C" {
+
+#ifdef FSIE_TC_TIMING
+// out[0..5]: cycles per phase - of a softmax warp: wait for S, read S, maximum, wait for P V,
+// exponentials and P, hand-over; with FSIE_TC_TIMING_MMA of the MMA thread: wait for P, wait for
+// the ring, everything else - out[6]: tiles; the counters are reset.
+int fsie_attn_tc_timing(unsigned long long* out) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, fsie_tc_timing, sizeof(fsie_tc_timing));
+    if (e != cudaSuccess) return (int)e;
+    unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    return (int)cudaMemcpyToSymbol(fsie_tc_timing, zero, sizeof(zero));
+}
+#endif
 
 int fsie_attn_tc_head_dim() { return HD; }
 int fsie_attn_tc_rows() { return STREAMS * BM; }

@@ -143,15 +143,27 @@ def run_attention(args, timer, decode: bool):
                                   qlen, pos0, out, tokens, heads, kv_heads, hd, 0, scale, nsplit,
                                   part_o, part_ml)
     ms = timer(launch)
+    extra = {}
+    if use_tc and any("FSIE_TC_TIMING" in d for d in args.build_defines):
+        # cycles per key tile that one warp spent in each phase, summed over all blocks by the kernel
+        import ctypes
+        lib = ops.attn_tc(hd)
+        counters = (ctypes.c_ulonglong * 8)()
+        torch.cuda.synchronize()
+        lib.fsie_attn_tc_timing.argtypes = [ctypes.c_void_p]
+        lib.fsie_attn_tc_timing(counters)
+        names = (["wait_p", "wait_ring", "issue"] if any("TIMING_MMA" in d for d in args.build_defines)
+                 else ["wait_s", "read_s", "max", "wait_pv", "exp_p", "hand_over"])
+        extra["cycles_per_tile"] = {n: round(counters[k] / max(1, counters[6])) for k, n in enumerate(names)}
     elem = 2 if dtype is torch.bfloat16 else 4
     kv_bytes = args.batch * args.context * 2 * kv_heads * hd * elem
     io_bytes = kv_bytes + 2 * tokens * heads * hd * elem
     # causal: query t of a portion sees past + t + 1 keys
     pairs = args.batch * (new * past + new * (new + 1) / 2)
     flops = 4.0 * heads * hd * pairs
-    return ms, io_bytes, flops, {"nsplit": nsplit, "tiles": tile_item.numel(),
-                                 "variant": ("tc" if use_tc else "tma" if use_tma else "mma") if row_class >= 0
-                                 else "generic"}
+    extra.update({"nsplit": nsplit, "tiles": tile_item.numel(),
+                  "variant": ("tc" if use_tc else "tma" if use_tma else "mma") if row_class >= 0 else "generic"})
+    return ms, io_bytes, flops, extra
 
 
 def run(args):
@@ -243,7 +255,7 @@ def run(args):
               "frac_hbm": round(gbs / peak["hbm_gbs"], 3),
               "frac_bf16": round(tflops / peak["bf16_tflops"], 3), "peaks": peak["source"],
               "sizes": {k: v for k, v in vars(args).items()
-                        if k not in ("kernel", "dtype", "warmup", "iters", "no_flush")}}
+                        if k not in ("kernel", "dtype", "warmup", "iters", "no_flush", "build_defines")}}
     record.update(extra)
     print(json.dumps(record))
 
@@ -274,7 +286,24 @@ def main(argv=None) -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--no-flush", action="store_true")
-    run(parser.parse_args(argv))
+    parser.add_argument("--build-defines", default="", help="extra -D flags for the kernel library under "
+                        "test: a measurement build, e.g. '-DFSIE_TC_TIMING' (cycles per phase of the tcgen05 "
+                        "attention's softmax warps; with -DFSIE_TC_TIMING_MMA of its MMA thread) or "
+                        "'-DFSIE_GT_NO_MMA' / '-DFSIE_GT_NO_LOAD' / '-DFSIE_GT_NO_EPILOGUE' (the tiled product "
+                        "with a stage of its pipeline left out; results are then wrong on purpose)")
+    args = parser.parse_args(argv)
+    args.build_defines = tuple(args.build_defines.split())
+    if args.build_defines:
+        # the measurement build replaces the library of the kernel under test for this process
+        from ..csrc import build
+        target = {"attention_prefill": "attn_tc", "attention_decode": "attn_mma"}.get(
+            args.kernel, "gemm_tiles" if args.kernel.startswith("gemm_tiles") else None)
+        if target is None:
+            raise SystemExit("--build-defines: no measurement build for this kernel")
+        plain_load = build.load_library
+        build.load_library = lambda name, defines=(): plain_load(
+            name, tuple(defines) + (args.build_defines if name == target else ()))
+    run(args)
     return 0
 
 
