@@ -339,7 +339,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                         mma_ts(tmem + COL_O + st * BN, tmem + COL_S + st * BN + k * 8, vd + (uint64_t)(k * (16 * 128 >> 4)),
                                idesc_o, (i > 0 || k > 0) ? 1u : 0u);
                     }
-                    mma_commit(&ctl.o_done[st]);                // O_st holds tiles 0..i
+                    if (i + 1 == ntiles) mma_commit(&ctl.o_done[st]);       // O_st is complete
                     if (st == streams - 1) mma_commit(&ctl.ring_empty[(2 * i + 1) % SLOTS]);    // V_i may be overwritten
                     if (i + 1 < ntiles) {                       // the stream's next scores, while the other's softmax runs
                         if (st == 0) ring_wait(2 * i + 2);
@@ -382,7 +382,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             TC_MARK(0);
 #ifdef FSIE_TC_NO_SOFTMAX
-            if (i > 0) mbar_wait(&ctl.o_done[st], (i - 1) & 1);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&ctl.p_ready[st]);
             continue;
@@ -419,13 +418,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             const float corr = m_new == m_run ? 1.f : fast_exp2(m_run * sc - base);    // m_run = -inf gives 0
             const bool rescale = i > 0 && __any_sync(0xffffffffu, valid && corr != 1.f);
             TC_MARK(2);
-            // O of this stream was last touched by the P V of tile i - 1.  (P needs no such wait: it
-            // lies over S, and the tensor core finished that P V before it wrote this S.)
-            if (rescale && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], (i - 1) & 1))) {
-                if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
-                atomicExch(&abort_flag, 1); ok = false; break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // O and P of this stream were last touched by the P V of tile i - 1, which the tensor core
+            // finished before it wrote this S: neither needs a wait of its own.
             TC_MARK(3);
             if (rescale) {
 #pragma unroll 1
@@ -470,7 +464,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
 #endif
         // ---- the last P V, then normalise and store (or hand a partial result to the merge)
         bool have = ok && ntiles > 0;
-        if (have && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], (ntiles - 1) & 1))) {
+        if (have && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], 0))) {
             if (lane == 0) atomicExch(x.error, ERR_TC_SOFTMAX);
             atomicExch(&abort_flag, 1); have = false;
         }
