@@ -57,6 +57,9 @@ class Runtime:
             raise ValueError("products must be 'own' or 'library'")
         self.products = products
         self.tiled_min_tiles = tiled_min_tiles       # None: as many tiles as pairs of SMs run at once
+        # decode steps of 17-64 tokens keep the library product: alone the tiled kernel ties with it
+        # there, inside a captured decode step it measured 6 % slower (batch 64)
+        self.tiled_min_rows = 65 if tiled_min_tiles is None else self.few_token_limit + 1
         self._tiled_weights: Dict[int, ops.TiledWeight] = {}
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
@@ -97,7 +100,7 @@ class Runtime:
         tokens than the few-token product takes, and enough tiles to give every pair of SMs
         one (with fewer, the library's smaller tiles or split k stream the weight faster)."""
         prepared = self._tiled_weights.get(weight.data_ptr())
-        if prepared is None or x.shape[0] <= self.few_token_limit or x.stride(0) % 8 or x.data_ptr() % 16:
+        if prepared is None or x.shape[0] < self.tiled_min_rows or x.stride(0) % 8 or x.data_ptr() % 16:
             return None
         least = ops.gemm_tiles_lib().pairs if self.tiled_min_tiles is None else self.tiled_min_tiles
         if ops.gemm_tiles_count(x.shape[0], prepared.n, prepared.swiglu) < least:
