@@ -302,6 +302,15 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ act,
     store8(act + t * inter + i, o);
 }
 
+// --------------------------------------------------------------------------- token feedback
+// ids[dst[i]] = chosen[row[i]]: tokens that the step before sampled enter this step's ids on
+// the device, before the host has seen them.
+__global__ void place_tokens_kernel(int* __restrict__ ids, const int* __restrict__ dst,
+                                    const int* __restrict__ row, const int* __restrict__ chosen, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) ids[dst[i]] = chosen[row[i]];
+}
+
 }  // namespace fsie
 
 using namespace fsie;
@@ -415,6 +424,12 @@ int fsie_swiglu(const void* gu, void* act, long long tokens, int inter, int dtyp
         swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)act, inter, total);
     else
         swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)act, inter, total);
+    return FSIE_LAUNCH_CHECK();
+}
+
+int fsie_place_tokens(int* ids, const int* dst, const int* row, const int* chosen, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    place_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, dst, row, chosen, n);
     return FSIE_LAUNCH_CHECK();
 }
 

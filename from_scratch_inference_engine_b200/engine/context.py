@@ -30,10 +30,12 @@ class Tiles:
 
 
 class PinnedRing:
-    """A few pinned staging buffers used in turn; a buffer is reused only after the copy
-    that last read it has finished."""
+    """Pinned staging buffers used in turn; a buffer is reused only after the copy that last
+    read it has finished.  Deep enough that the copies of two steps never meet: a step is
+    staged while the step before it still runs, and waiting for a buffer would stall the host
+    until the GPU has caught up."""
 
-    def __init__(self, depth: int = 4):
+    def __init__(self, depth: int = 32):
         self.depth = depth
         self.buffers: List[Optional[torch.Tensor]] = [None] * depth
         self.events: List[Optional[torch.cuda.Event]] = [None] * depth

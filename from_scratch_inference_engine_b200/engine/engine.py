@@ -4,6 +4,14 @@ Same control surface as the reference's `Engine` (include/engine/engine.hpp:39-8
 bindings/module.cpp:104-147): add_request, step, has_work, output, status, preemptions,
 prefix_hits, generate - with the same option names and defaults (block_size, num_blocks,
 seed, max_batch, enable_prefix_cache; max_tokens = 16, eos_id = -1 disables the stop).
+
+Steps overlap (`pipeline=True`, the default): `step()` plans and launches the next batch
+while the tokens that the batch before it sampled are still on their way to the host -
+their ids enter the new batch on the device - and only then waits for them and records
+them.  The GPU therefore does not idle while Python plans, stages and launches, and
+`output()` lags one step behind the GPU.  The tokens are the same as without the overlap:
+a request whose pending token turns out to be its end of sequence has run one token for
+nothing, which is dropped.
 """
 
 from __future__ import annotations
@@ -88,7 +96,7 @@ class LoadedModel:
 class Engine:
     def __init__(self, model: LoadedModel, block_size: int = 16, num_blocks: int = 2048,
                  seed: int = 0, max_batch: int = 256, enable_prefix_cache: bool = False,
-                 max_step_tokens: int = 2048):
+                 max_step_tokens: int = 2048, pipeline: bool = True):
         self.model = model
         self.runner = ModelRunner(model.model, model.runtime, page_size=block_size,
                                   num_pages=num_blocks, max_requests=max_batch,
@@ -97,6 +105,8 @@ class Engine:
                                    self.runner.max_positions)
         self.sampler = Sampler(model.runtime.device)
         self.seed = int(seed)
+        self.pipeline = bool(pipeline)
+        self._in_flight = None          # (items, Picked) of a launched step whose tokens are not read yet
         self.steps = 0
         self.tokens_prefilled = 0
         self.tokens_decoded = 0
@@ -113,7 +123,7 @@ class Engine:
         return self.scheduler.add(prompt, params, max_tokens, eos_id, seed)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._in_flight is not None
 
     def output(self, request_id: int) -> List[int]:
         return self.scheduler.sequences[request_id].output
@@ -130,22 +140,62 @@ class Engine:
     # ---------------------------------------------------------------------- step
     def step(self) -> int:
         """One batched step; returns the number of tokens it ran (0 = nothing could run)."""
-        items = self.scheduler.plan()
+        if not self.pipeline:
+            items = self.scheduler.plan()
+            if not items:
+                return 0
+            picked = self._launch(items)
+            tokens = self._tokens_of(items, picked)
+            self.scheduler.finish_step(items, tokens)
+            return self._count(items)
+        # plan and launch the next step before the one in flight is read; a plan that would
+        # have to preempt (or finds nothing to do) waits until the pending tokens are settled
+        settled = 0
+        items = self.scheduler.plan(can_preempt=self._in_flight is None)
+        if not items and self._in_flight is not None:
+            settled = self._settle()
+            items = self.scheduler.plan()
         if not items:
-            return 0
+            return settled
+        picked = self._launch(items)
+        if self._in_flight is not None:
+            self._settle()
+        self.scheduler.begin_step(items)
+        if picked is None:                     # nothing sampled: nothing to wait for
+            self.scheduler.resolve_step(items, [None] * len(items))
+        else:
+            self._in_flight = (items, picked)
+        return self._count(items)
+
+    def _launch(self, items):
+        """Queue the step on the GPU; returns the sampled tokens' handle (None: no item samples)."""
         entries = [StepEntry(item.seq.handle, item.tokens,
-                             [len(item.tokens) - 1] if item.samples else [])
+                             [len(item.tokens) - 1] if item.samples else [], item.source_row)
                    for item in items]
-        logits = self.runner.step(entries)
+        before = self._in_flight[1].device if self._in_flight is not None else None
+        logits = self.runner.step(entries, before)
         sampling = [item for item in items if item.samples]
-        tokens: List[Optional[int]] = [None] * len(items)
-        if sampling:
-            picked = self.sampler.sample(logits, [i.seq.params for i in sampling],
+        if not sampling:
+            return None
+        return self.sampler.sample_async(logits, [i.seq.params for i in sampling],
                                          [i.seq.seed for i in sampling],
-                                         [len(i.seq.output) for i in sampling])
-            picked_iter = iter(picked)
-            tokens = [next(picked_iter) if item.samples else None for item in items]
-        self.scheduler.finish_step(items, tokens)
+                                         [len(i.seq.output) + i.seq.pending for i in sampling])
+
+    @staticmethod
+    def _tokens_of(items, picked) -> List[Optional[int]]:
+        if picked is None:
+            return [None] * len(items)
+        chosen = iter(picked.result())
+        return [next(chosen) if item.samples else None for item in items]
+
+    def _settle(self) -> int:
+        """Wait for the tokens of the step in flight and record them."""
+        items, picked = self._in_flight
+        self._in_flight = None
+        self.scheduler.resolve_step(items, self._tokens_of(items, picked))
+        return sum(len(item.tokens) for item in items)
+
+    def _count(self, items) -> int:
         self.steps += 1
         for item in items:
             if item.was_prefill:

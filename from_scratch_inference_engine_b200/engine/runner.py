@@ -31,6 +31,9 @@ class StepEntry:
     handle: RequestCache
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    # >= 0: the single token is not known on the host yet; it is row `source_row` of the
+    # `device_tokens` given to step() (what the step before sampled)
+    source_row: int = -1
 
 
 class DeviceFault(RuntimeError):
@@ -147,6 +150,10 @@ class ModelRunner:
                 raise ValueError(f"step: request {entry.handle.request_id!r} brings no tokens")
             low, high = (entry.tokens[0], entry.tokens[0]) if n == 1 else \
                 (min(entry.tokens), max(entry.tokens))
+            if entry.source_row >= 0:
+                if n != 1:
+                    raise ValueError("step: only a single token can come from the device")
+                low = high = 0                    # the embedding kernel checks the id it finds
             if low < 0 or high >= self.vocab_size:
                 raise IndexError(f"step: token id out of range [0, {self.vocab_size}) in request "
                                  f"{entry.handle.request_id!r}")
@@ -162,7 +169,20 @@ class ModelRunner:
             self._graph_pool = torch.cuda.graph_pool_handle()
         return self._graph_pool
 
-    def _decode_step(self, entries: Sequence[StepEntry]):
+    def _place_device_tokens(self, ctx: StepContext, entries: Sequence[StepEntry], starts,
+                             device_tokens: Optional[torch.Tensor]) -> None:
+        """Tokens that the step before sampled go from its result on the device straight into
+        this step's ids (entry e's token sits at ids[starts[e]])."""
+        pairs = [(starts[e], entry.source_row) for e, entry in enumerate(entries) if entry.source_row >= 0]
+        if not pairs:
+            return
+        if device_tokens is None:
+            raise ValueError("step: entries take tokens from the device, but none were given")
+        host = np.asarray([d for d, _ in pairs] + [r for _, r in pairs], dtype=np.int32)
+        from ..kernels import ops
+        ops.place_tokens(ctx.token_ids, self._ring.stage(host, self.runtime.device), device_tokens)
+
+    def _decode_step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor]):
         """A step of single tokens through a captured graph: (whether it ran, logits)."""
         cache = self.cache
         count = len(entries)
@@ -175,9 +195,10 @@ class ModelRunner:
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._graphs[key] = _DecodeGraph(self, batch, width)
-        graph.fill([e.tokens[0] for e in entries], [e.handle.length for e in entries],
-                   [e.handle.slot for e in entries],
-                   [[e.handle.table_array(g) for e in entries] for g in range(len(cache.groups))])
+        ctx = graph.fill([max(0, e.tokens[0]) for e in entries], [e.handle.length for e in entries],
+                         [e.handle.slot for e in entries],
+                         [[e.handle.table_array(g) for e in entries] for g in range(len(cache.groups))])
+        self._place_device_tokens(ctx, entries, range(count), device_tokens)
         logits = graph.replay()
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if not wanted:
@@ -188,16 +209,18 @@ class ModelRunner:
         return True, logits.index_select(0, index)
 
     # --------------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry],
+             device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits [wanted places, vocab] in the order of the
         entries and of their `want`, or None when nothing is wanted.  The returned tensor
-        may be reused by the next step: read it before stepping again."""
+        may be reused by the next step: read it before stepping again.  `device_tokens`
+        (int32, on the device) holds the tokens of entries with a `source_row`."""
         self._validate(entries)
         cache = self.cache
         for entry in entries:
             cache.reserve(entry.handle, len(entry.tokens))
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
-            ran, logits = self._decode_step(entries)
+            ran, logits = self._decode_step(entries, device_tokens)
             if ran:
                 for entry in entries:
                     cache.commit(entry.handle, 1)
@@ -213,11 +236,12 @@ class ModelRunner:
             if entry.handle.length == 0:
                 fresh_slots.append(entry.handle.slot)
             want_rows += [len(token_ids) + w for w in entry.want]
-            token_ids += list(entry.tokens)
+            token_ids += [0] if entry.source_row >= 0 else list(entry.tokens)
         tables = [(cache.page_size, [e.handle.table_array(g) for e in entries])
                   for g in range(len(cache.groups))]
         ctx = StepContext(self.runtime, self._ring, self._scratch, self.error, token_ids, q_start,
                           q_len, pos0, slots, tables)
+        self._place_device_tokens(ctx, entries, q_start, device_tokens)
         if fresh_slots and any(s is not None for s in self.states):
             index = torch.tensor(fresh_slots, dtype=torch.long, device=self.runtime.device)
             for state in self.states:

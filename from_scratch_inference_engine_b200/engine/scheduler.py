@@ -17,6 +17,12 @@ Policy (the reference's, src/engine/engine.cpp:53-178, plus portions):
 * A request that could never fit (prompt + max_tokens beyond one request's share of the
   pool or beyond the position limit) is refused when it is added, instead of spinning
   as the reference does (src/engine/engine.cpp:120-126).
+* A step may be planned while the tokens sampled by the step before it are still on their
+  way from the GPU (`begin_step` / `resolve_step` instead of `finish_step`): such a request
+  counts its pending token in its length, brings a token that the GPU fills in, is left out
+  if the pending token is its last, and is never preempted - a plan that would have to
+  preempt is given up (`can_preempt=False`), the caller settles the pending tokens and
+  plans again.
 
 This file decides only; `Engine` in engine.py runs the plans on the GPU.
 """
@@ -51,12 +57,14 @@ class Sequence_:
     prefilled: bool = False
     handle: Optional[RequestCache] = None
     preempted: int = 0
+    pending: int = 0          # 1 while a sampled token has not been read from the GPU yet
+    pending_row: int = -1     # ... and the row of that step's samples it will be found in
 
     def context(self) -> List[int]:
         return self.prompt + self.output
 
     def context_length(self) -> int:
-        return len(self.prompt) + len(self.output)
+        return len(self.prompt) + len(self.output) + self.pending
 
     def context_slice(self, start: int, stop: int) -> List[int]:
         """context()[start:stop] without building the whole list."""
@@ -68,12 +76,16 @@ class Sequence_:
         return self.prompt[start:] + self.output[:stop - n]
 
 
+PENDING_TOKEN = -1        # placeholder in a plan for a token the GPU still holds
+
+
 @dataclass
 class PlanItem:
     seq: Sequence_
     tokens: List[int]
     samples: bool          # the portion ends the context: logits of its last token are wanted
     was_prefill: bool
+    source_row: int = -1   # >= 0: the single token is row source_row of the previous step's samples
 
 
 class Scheduler:
@@ -129,10 +141,11 @@ class Scheduler:
             seq.status = SeqStatus.Running
             self.running.append(seq.id)
 
-    def plan(self) -> List[PlanItem]:
-        """Admit, then choose this step's items.  May preempt.  Returns [] when nothing can
-        run (then nothing is running, or a single request waits for nothing: cannot happen
-        for requests that passed `add`)."""
+    def plan(self, can_preempt: bool = True) -> List[PlanItem]:
+        """Admit, then choose this step's items.  May preempt (unless told not to: then a
+        plan that needs a preemption comes back empty).  Returns [] when nothing can run
+        (then nothing is running, or a single request waits for nothing: cannot happen for
+        requests that passed `add`; or every running request waits for its last token)."""
         self._admit()
         cache = self.cache
         while True:
@@ -152,8 +165,15 @@ class Scheduler:
 
             for sid in self.running:                      # decodes first
                 seq = self.sequences[sid]
-                if seq.prefilled and tokens_left > 0 and take(seq.handle, 1):
-                    items.append(PlanItem(seq, [seq.output[-1]], True, False))
+                if not seq.prefilled or tokens_left <= 0:
+                    continue
+                if len(seq.output) + seq.pending >= seq.max_tokens:
+                    continue                              # its pending token is its last
+                if take(seq.handle, 1):
+                    if seq.pending:
+                        items.append(PlanItem(seq, [PENDING_TOKEN], True, False, seq.pending_row))
+                    else:
+                        items.append(PlanItem(seq, [seq.output[-1]], True, False))
                     tokens_left -= 1
             for sid in self.running:                      # then prompt portions
                 seq = self.sequences[sid]
@@ -178,7 +198,7 @@ class Scheduler:
                 portion = seq.context_slice(handle.length, handle.length + chunk)
                 items.append(PlanItem(seq, portion, chunk == remaining, True))
                 tokens_left -= chunk
-            if items or len(self.running) <= 1 or not self._preempt_youngest():
+            if items or len(self.running) <= 1 or not can_preempt or not self._preempt_youngest():
                 return items
 
     def _preempt_youngest(self) -> bool:
@@ -201,11 +221,32 @@ class Scheduler:
     def finish_step(self, items: Sequence[PlanItem], tokens: Sequence[Optional[int]]) -> None:
         """Record the sampled token of every item that sampled (None for the others), retire
         what is finished and register freshly prefilled pages for sharing."""
-        for item, token in zip(items, tokens):
-            seq = item.seq
+        self.begin_step(items)
+        self.resolve_step(items, tokens)
+
+    def begin_step(self, items: Sequence[PlanItem]) -> None:
+        """The step has been launched: every item that samples now has a token pending, in
+        the row of the step's samples that its place among the sampling items gives."""
+        row = 0
+        for item in items:
             if not item.samples:
                 continue
-            seq.prefilled = True
+            seq = item.seq
+            if seq.status is SeqStatus.Running and seq.handle is not None:
+                seq.prefilled = True
+                seq.pending, seq.pending_row = 1, row
+            row += 1
+
+    def resolve_step(self, items: Sequence[PlanItem], tokens: Sequence[Optional[int]]) -> None:
+        """The step's sampled tokens have arrived (None for items that did not sample).  A
+        request that an earlier step's token has finished meanwhile is passed over: its item
+        ran for nothing."""
+        for item, token in zip(items, tokens):
+            seq = item.seq
+            if not item.samples or seq.status is not SeqStatus.Running or seq.handle is None \
+                    or not seq.pending:
+                continue
+            seq.pending, seq.pending_row = 0, -1
             seq.output.append(int(token))
             hit_eos = seq.eos_id >= 0 and token == seq.eos_id
             if hit_eos or len(seq.output) >= seq.max_tokens:
@@ -214,4 +255,5 @@ class Scheduler:
                 seq.handle = None
                 self.running.remove(seq.id)
             elif item.was_prefill and self.cache.prefix_enabled:
-                self.cache.register_prefix(seq.handle, seq.context_slice(0, seq.handle.length))
+                known = min(seq.handle.length, len(seq.prompt) + len(seq.output))
+                self.cache.register_prefix(seq.handle, seq.context_slice(0, known))

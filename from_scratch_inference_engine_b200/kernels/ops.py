@@ -30,12 +30,20 @@ def _tag(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16 storage, not {dtype}")
 
 
-def _ptr(tensor: Optional[torch.Tensor]) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    """The address for a pointer argument (ctypes takes an int or None for c_void_p)."""
+    return None if tensor is None else tensor.data_ptr()
 
 
-def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _stream() -> int:
+    """The current CUDA stream's handle.  Asked for at every launch (streams change under
+    graph capture), so by the cheapest route torch offers."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def _need(tensor: torch.Tensor, dtype, name: str, contiguous: bool = True) -> None:
@@ -75,6 +83,7 @@ def core():
         lib.fsie_add_rmsnorm.argtypes = [p, p, p, i, p, p, i, i, f, i, i, p]
         lib.fsie_rope_kv_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p]
         lib.fsie_swiglu.argtypes = [p, p, ll, i, i, p]
+        lib.fsie_place_tokens.argtypes = [p, p, p, p, i, p]
         lib.fsie_gemm_f32.argtypes = [p, p, p, p, i, i, i, i, i, p]
         lib.fsie_attn_generic.argtypes = [p, i, p, p, ll, i, p, i, p, p, i, p, p, p, p, i, p, p,
                                           i, i, i, i, i, i, f, i, p]
@@ -184,6 +193,15 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _check(core().fsie_swiglu(_ptr(gate_up), _ptr(out), tokens, inter, _tag(out.dtype), _stream()),
            "swiglu")
     return out
+
+
+def place_tokens(ids: torch.Tensor, dst_and_row: torch.Tensor, chosen: torch.Tensor) -> None:
+    """ids[dst[i]] = chosen[row[i]] for dst_and_row = [dst (n), row (n)], all int32 on the device."""
+    for name, t in (("ids", ids), ("dst_and_row", dst_and_row), ("chosen", chosen)):
+        _need(t, torch.int32, name)
+    n = dst_and_row.numel() // 2
+    _check(core().fsie_place_tokens(_ptr(ids), _ptr(dst_and_row), _ptr(dst_and_row[n:]),
+                                    _ptr(chosen), n, _stream()), "place_tokens")
 
 
 # --------------------------------------------------------------------- float32 product

@@ -51,12 +51,31 @@ def request_seed(engine_seed: int, request_id: int) -> int:
     return _splitmix((engine_seed & _MASK) ^ _splitmix(request_id + 0x51ED270B))
 
 
+class Picked:
+    """The tokens one sampling call chose: on the device at once (`device`, int32 [rows]), on
+    the host after `result()`, which waits for the copy that was started with the call."""
+
+    def __init__(self, device: torch.Tensor, host: np.ndarray, event, rows: int):
+        self.device, self._host, self._event, self.rows = device, host, event, rows
+        self._list: Optional[List[int]] = None
+
+    def result(self) -> List[int]:
+        if self._list is None:
+            self._event.synchronize()
+            self._list = self._host[:self.rows].tolist()
+        return self._list
+
+
 class Sampler:
     """Chooses one token per row of logits with the device kernels."""
+
+    HOST_BUFFERS = 4           # pinned result buffers in rotation: a result is read at most two calls later
 
     def __init__(self, device):
         self.device = torch.device(device)
         self._scratch = None
+        self._pinned: List[torch.Tensor] = []
+        self._turn = 0
         self.bytes_to_device = 0     # sampling parameters copied in (benchmarks read these)
         self.bytes_to_host = 0       # chosen ids copied out
 
@@ -64,6 +83,20 @@ class Sampler:
                seeds: Sequence[int], indices: Sequence[int]) -> List[int]:
         """logits float32 [rows, vocab]; row r is output token indices[r] of a request whose
         seed is seeds[r].  Returns the chosen ids (one device-to-host copy of rows ints)."""
+        return self.sample_async(logits, params, seeds, indices).result()
+
+    def _host_buffer(self, rows: int) -> torch.Tensor:
+        if not self._pinned or self._pinned[0].numel() < rows:
+            size = max(256, 1 << (rows - 1).bit_length())
+            self._pinned = [torch.empty(size, dtype=torch.int32, pin_memory=True)
+                            for _ in range(self.HOST_BUFFERS)]
+        self._turn = (self._turn + 1) % self.HOST_BUFFERS
+        return self._pinned[self._turn]
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                     seeds: Sequence[int], indices: Sequence[int]) -> Picked:
+        """The same without waiting: the kernels and the copy to pinned host memory are queued,
+        the chosen ids stay on the device for a step that feeds them back in."""
         rows = logits.shape[0]
         if rows != len(params):
             raise ValueError("one SamplingParams per row of logits is needed")
@@ -77,17 +110,24 @@ class Sampler:
                                             device=self.device)
             ops.argmax(logits, picks[0], self._scratch)
         if any_random:
-            host = np.empty((4, rows), dtype=np.float32)
+            host = np.empty((5, rows), dtype=np.float32)
             for r, p in enumerate(params):
                 host[0, r] = p.temperature if not p.greedy else 0.0
                 host[1, r] = min(p.top_p, 1.0)
                 host[2, r] = uniform_draw(seeds[r], indices[r])
                 host[3, r] = 0.0
+                host[4, r] = 1.0 if p.greedy else 0.0
             dev = torch.from_numpy(host).to(self.device)
             self.bytes_to_device += host.nbytes + 4 * rows
             top_k = torch.tensor([max(0, int(p.top_k)) for p in params], dtype=torch.int32,
                                  device=self.device)
             ops.sample(logits, dev[0], top_k, dev[1], dev[2], picks[1])
-        got = picks.cpu().numpy()
-        self.bytes_to_host += got.nbytes
-        return [int(got[0, r] if params[r].greedy else got[1, r]) for r in range(rows)]
+            chosen = torch.where(dev[4] > 0, picks[0], picks[1]) if any_greedy else picks[1]
+        else:
+            chosen = picks[0]
+        pinned = self._host_buffer(rows)
+        pinned[:rows].copy_(chosen, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.bytes_to_host += 4 * rows
+        return Picked(chosen, pinned.numpy(), event, rows)

@@ -166,3 +166,40 @@ def test_requests_beyond_the_pool_are_refused(folders):
         engine.add_request(list(range(10)), None, 8)
     with pytest.raises(IndexError):
         engine.add_request([1, 256], None, 2)
+
+
+def test_overlapped_steps_give_the_same_tokens_as_one_step_at_a_time(folders):
+    """The engine launches a step before it has read the tokens of the step before it (their
+    ids enter the batch on the device).  Same outputs as without the overlap, with requests
+    that stop at an end-of-sequence token (one token run for nothing and dropped), stop at
+    their length, are preempted under a tight pool and share a prefix."""
+    from from_scratch_inference_engine_b200 import SamplingParams
+    shared = helpers.random_ids(384, 19, 77)
+    prompts = [helpers.random_ids(384, n, s) for n, s in ((5, 1), (33, 2), (12, 3), (47, 4), (2, 5))]
+    prompts += [shared + helpers.random_ids(384, 4, 6), shared + helpers.random_ids(384, 9, 7)]
+    params = [SamplingParams(temperature=0.0), SamplingParams(temperature=0.9, seed=5),
+              SamplingParams(temperature=0.0), SamplingParams(temperature=1.2, top_k=30, seed=6),
+              SamplingParams(temperature=0.0), SamplingParams(temperature=0.0),
+              SamplingParams(temperature=0.7, top_p=0.8, seed=7)]
+    lengths = [9, 14, 1, 11, 20, 7, 13]
+    free_run = engine_for(folders["B"], block_size=8, pipeline=False).generate(prompts[4], params[4], 20)
+    eos = {4: free_run[6]}                       # request 4 stops where that token first appears
+    stopped = free_run[:free_run.index(free_run[6]) + 1]
+    results = {}
+    for pipeline in (False, True):
+        for blocks in (64, 9):                   # roomy; 72 tokens of cache: forces preemption
+            engine = engine_for(folders["B"], block_size=8, num_blocks=blocks, max_batch=4,
+                                enable_prefix_cache=True, pipeline=pipeline)
+            ids = [engine.add_request(p, q, n, eos_id=eos.get(i, -1))
+                   for i, (p, q, n) in enumerate(zip(prompts, params, lengths))]
+            engine.run_until_done()
+            assert not engine.has_work()
+            results[pipeline, blocks] = [list(engine.output(i)) for i in ids]
+            engine.runner.cache.check()
+            if blocks == 9:
+                assert engine.preemptions() > 0
+            engine.runner.raise_on_device_error()
+    first = results[False, 64]
+    assert first[4] == stopped and len(stopped) < 20
+    assert [len(o) for o in first] == [9, 14, 1, 11, len(stopped), 7, 13]
+    assert all(other == first for other in results.values())
