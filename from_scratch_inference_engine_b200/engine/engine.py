@@ -122,6 +122,12 @@ class Engine:
         seed = params.seed if params.seed is not None else request_seed(self.seed, rid)
         return self.scheduler.add(prompt, params, max_tokens, eos_id, seed)
 
+    def warm_up(self, max_context: int = 0) -> int:
+        """Capture the decode graphs for contexts of up to `max_context` tokens (default: what
+        one request may hold) before serving starts; returns their number."""
+        limit = max_context or min(self.runner.cache.max_tokens_per_request(), self.runner.max_positions)
+        return self.runner.capture_decode_graphs(limit, self.scheduler.max_batch)
+
     def has_work(self) -> bool:
         return self.scheduler.has_work() or self._in_flight is not None
 

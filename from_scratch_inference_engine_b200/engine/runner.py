@@ -182,6 +182,23 @@ class ModelRunner:
         from ..kernels import ops
         ops.place_tokens(ctx.token_ids, self._ring.stage(host, self.runtime.device), device_tokens)
 
+    def capture_decode_graphs(self, max_context: int, max_batch: int = 0) -> int:
+        """Capture ahead of time the decode steps that requests of up to `max_context` tokens
+        in batches of up to `max_batch` (default: all the runner takes) will replay, instead of
+        at their first use in the middle of serving.  Returns how many graphs now exist."""
+        if not self.cuda_graphs:
+            return 0
+        limit = max_batch or self.cache.slots.num_slots
+        pages = -(-max(1, max_context) // self.cache.page_size)
+        widths = range(TABLE_STEP, -(-pages // TABLE_STEP) * TABLE_STEP + 1, TABLE_STEP)
+        for batch in DECODE_BATCHES:
+            for width in widths:
+                if (batch, width) not in self._graphs:
+                    self._graphs[batch, width] = _DecodeGraph(self, batch, width)
+            if batch >= limit:
+                break
+        return len(self._graphs)
+
     def _decode_step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor]):
         """A step of single tokens through a captured graph: (whether it ran, logits)."""
         cache = self.cache
