@@ -155,7 +155,7 @@ def serving_workload(args) -> int:
     requests = args.requests
     model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16", max_positions=4096)
     engine = Engine(model, block_size=16, num_blocks=args.num_blocks, max_batch=256,
-                    enable_prefix_cache=True, max_step_tokens=2048)
+                    enable_prefix_cache=True, max_step_tokens=args.step_tokens)
     prefix = rng.integers(0, config.vocab_size, size=512).tolist()
     prompts, outputs = [], []
     for r in range(requests):
@@ -219,6 +219,7 @@ def main() -> int:
                         help="decode: the default measurement; serving: continuous batching of 256 "
                              "requests at the 1.5B shape")
     parser.add_argument("--requests", type=int, default=256)
+    parser.add_argument("--step-tokens", type=int, default=2048, help="serving: token budget of one step")
     parser.add_argument("--num-blocks", type=int, default=16384)
     args = parser.parse_args()
 

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Makes the golden outputs in this folder from the reference's own CPU model.
 
-    python tests/golden/make_golden.py [--reference /path/to/reference]
+    python tests/golden/make_golden.py --reference /path/to/reference
 
 It compiles, unmodified, the reference's src/model/{model,model_config,safetensors,nn}.cpp,
 src/kvcache/{block_manager,paged_kv_cache}.cpp, src/sampler/sampler.cpp,
@@ -52,7 +52,7 @@ def find_json_header() -> Path:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="checkout of the reference project")
     args = parser.parse_args()
     ref = Path(args.reference)
     import torch
