@@ -57,7 +57,7 @@ constexpr int TILE_BYTES = STREAMS * Q_BYTES + SLOTS * KV_BYTES;
 // to a block (227 KB), so the kernel has no static shared memory and relies on the window
 // starting on such a boundary; it checks and refuses otherwise.
 struct Control {
-    uint64_t ring_full[SLOTS], ring_empty[SLOTS], s_full[STREAMS], p_ready[STREAMS], o_done[STREAMS];
+    uint64_t ring_full[SLOTS], ring_empty[SLOTS], s_full[STREAMS], p_ready[STREAMS], o_done[STREAMS], q_ready;
     uint32_t tmem_slot;
     int abort_flag;
 };
@@ -71,7 +71,7 @@ struct TcExtra { int entries, entry; int* error; };
 #ifdef FSIE_TC_TIMING
 // cycles spent by one softmax warp (with FSIE_TC_TIMING_MMA: by the MMA thread) per phase, summed
 // over all blocks (measurement builds only)
-__device__ unsigned long long fsie_tc_timing[8];
+__device__ unsigned long long fsie_tc_timing[10];
 #define TC_MARK(slot) do { const long long now_ = clock64(); phase_[slot] += (unsigned)(now_ - mark_); mark_ = now_; } while (0)
 #else
 #define TC_MARK(slot) do { } while (0)
@@ -182,6 +182,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     int& abort_flag = ctl.abort_flag;
 
     // later tiles of a prompt see more keys: start them first so that the last wave is short
+#ifdef FSIE_TC_TIMING
+    const long long block_begin_ = clock64();
+#endif
     const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     const int item = p.tile_item[tile];
@@ -208,13 +211,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     kbegin = kbegin / BN * BN;          // tiles hold whole pages; keys before the window are masked
     const int ntiles = kend > kbegin ? (kend - kbegin + BN - 1) / BN : 0;
 
-    // ---- set-up: barriers, tensor memory, zeroed ring (pages never fetched must read as finite
-    // numbers), the query rows in the swizzled K-major layout
+    // ---- set-up: barriers and tensor memory; then the producer starts fetching keys at once while
+    // the other warps bring the query rows into the swizzled K-major layout
     if (tid == 0) {
         for (int s = 0; s < SLOTS; ++s) { mbar_init(&ctl.ring_full[s], 1); mbar_init(&ctl.ring_empty[s], 1); }
         for (int st = 0; st < STREAMS; ++st) {
             mbar_init(&ctl.s_full[st], 1); mbar_init(&ctl.p_ready[st], BM); mbar_init(&ctl.o_done[st], 1);
         }
+        mbar_init(&ctl.q_ready, THREADS - 32);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -222,23 +226,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&ctl.tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int e = tid; e < (SLOTS * KV_BYTES) / 16; e += blockDim.x)
-        reinterpret_cast<uint4*>(ring)[e] = make_uint4(0, 0, 0, 0);
-    for (int e = tid; e < STREAMS * BM * (HD / 8); e += blockDim.x) {
-        const int r = e / (HD / 8), c = e - r * (HD / 8);     // 16-byte chunk c of row r of the block
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < nrows) {
-            const int row = row0 + r;
-            const int tok = qstart + row / group, h = kvh * group + row % group;
-            v = *reinterpret_cast<const uint4*>(q + (size_t)tok * p.q_ld + h * HD + c * 8);
-        }
-        *reinterpret_cast<uint4*>(q_s + (r / BM) * Q_BYTES + (c >> 3) * ATOM_BYTES + swizzled(r % BM, c & 7)) = v;
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes before async-proxy reads
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = ctl.tmem_slot;
+    if (warp != 0) {
+        // all of a thread's loads go out before the first of its stores: one trip to memory, not one
+        // per 16 bytes
+        constexpr int CHUNKS = STREAMS * BM * (HD / 8), LOADERS = THREADS - 32;
+        constexpr int PER_THREAD = (CHUNKS + LOADERS - 1) / LOADERS;
+        uint4 held[PER_THREAD];
+#pragma unroll
+        for (int j = 0; j < PER_THREAD; ++j) {
+            const int e = tid - 32 + j * LOADERS;
+            const int r = e / (HD / 8), c = e - r * (HD / 8);     // 16-byte chunk c of row r of the block
+            held[j] = make_uint4(0, 0, 0, 0);
+            if (e < CHUNKS && r < nrows) {
+                const int row = row0 + r;
+                const int tok = qstart + row / group, h = kvh * group + row % group;
+                held[j] = *reinterpret_cast<const uint4*>(q + (size_t)tok * p.q_ld + h * HD + c * 8);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < PER_THREAD; ++j) {
+            const int e = tid - 32 + j * LOADERS;
+            const int r = e / (HD / 8), c = e - r * (HD / 8);
+            if (e < CHUNKS)
+                *reinterpret_cast<uint4*>(q_s + (r / BM) * Q_BYTES + (c >> 3) * ATOM_BYTES + swizzled(r % BM, c & 7)) = held[j];
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes before async-proxy reads
+        mbar_arrive(&ctl.q_ready);
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -249,8 +267,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         const long long k_row0 = ((long long)x.entry * 2) * p.kv_heads * ps + (long long)kvh * ps;
         const long long v_row0 = k_row0 + (long long)p.kv_heads * ps;
         for (int i = 0; i < ntiles; ++i) {
+            // Every part of a tile is fetched, so that what the MMAs read is always finite: where the
+            // tile reaches beyond the last key, or into pages that a window has given back, the page
+            // of the last key stands in (those keys are masked).
             const int key = kbegin + i * BN + lane * ps;
-            const int page = (lane < pages_per_tile && key < kend) ? bt[key / ps] : -1;   // before the wait: overlaps it
+            int page = -1;
+            if (lane < pages_per_tile) {                  // before the wait: overlaps it
+                page = key < kend ? bt[key / ps] : -1;
+                if (page < 0) page = bt[(kend - 1) / ps];
+            }
             const int wanted = __popc(__ballot_sync(0xffffffffu, page >= 0));
             bool ok = true;
 #pragma unroll
@@ -312,6 +337,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 mma_commit(&ctl.s_full[st]);
                 if (st == streams - 1) mma_commit(&ctl.ring_empty[(2 * i) % SLOTS]);     // K_i may be overwritten
             };
+            if (!mbar_wait(&ctl.q_ready, 0)) {
+                atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false;
+            }
             ring_wait(0);
             for (int st = 0; st < streams && ok; ++st) scores(st, 0);
             for (int i = 0; i < ntiles && ok; ++i) {
@@ -457,10 +485,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             TC_MARK(5);
         }
 #if defined(FSIE_TC_TIMING) && !defined(FSIE_TC_TIMING_MMA)
-        if (warp == 2 && lane == 0) {
-            for (int k = 0; k < 6; ++k) atomicAdd(&fsie_tc_timing[k], (unsigned long long)phase_[k]);
-            atomicAdd(&fsie_tc_timing[6], (unsigned long long)ntiles);
-        }
+        const long long loop_end_ = clock64();
 #endif
         // ---- the last P V, then normalise and store (or hand a partial result to the merge)
         bool have = ok && ntiles > 0;
@@ -505,6 +530,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             p.part_ml[idx * 2] = m_run == -INFINITY ? -INFINITY : m_run * p.scale;
             p.part_ml[idx * 2 + 1] = l_run;
         }
+#if defined(FSIE_TC_TIMING) && !defined(FSIE_TC_TIMING_MMA)
+        if (warp == 2 && lane == 0) {
+            for (int k = 0; k < 6; ++k) atomicAdd(&fsie_tc_timing[k], (unsigned long long)phase_[k]);
+            atomicAdd(&fsie_tc_timing[6], (unsigned long long)ntiles);
+            // everything outside the loop over key tiles: set-up before it, the output after it
+            atomicAdd(&fsie_tc_timing[7], (unsigned long long)(loop_end_ - block_begin_) -
+                                          (unsigned long long)(phase_[0] + phase_[1] + phase_[2] + phase_[3] + phase_[4] + phase_[5]));
+            atomicAdd(&fsie_tc_timing[8], (unsigned long long)(clock64() - loop_end_));
+        }
+#endif
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -527,7 +562,7 @@ extern "C" {
 int fsie_attn_tc_timing(unsigned long long* out) {
     cudaError_t e = cudaMemcpyFromSymbol(out, fsie_tc_timing, sizeof(fsie_tc_timing));
     if (e != cudaSuccess) return (int)e;
-    unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    unsigned long long zero[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     return (int)cudaMemcpyToSymbol(fsie_tc_timing, zero, sizeof(zero));
 }
 #endif

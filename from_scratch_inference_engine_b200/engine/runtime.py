@@ -60,7 +60,9 @@ class Runtime:
         # decode steps of 17-64 tokens keep the library product: alone the tiled kernel ties with it
         # there, inside a captured decode step it measured 6 % slower (batch 64)
         self.tiled_min_rows = 65 if tiled_min_tiles is None else self.few_token_limit + 1
-        self._tiled_weights: Dict[int, ops.TiledWeight] = {}
+        # matrices that may take the tiled product: storage address -> (weight, swiglu) until a step
+        # qualifies, then its descriptor (made, and the kernel library compiled, only then)
+        self._tiled_weights: Dict[int, object] = {}
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -91,7 +93,7 @@ class Runtime:
         if k % 8 or (swiglu and rows % 2):
             return
         if self.products == "own":
-            self._tiled_weights[weight.data_ptr()] = ops.TiledWeight(weight, swiglu)
+            self._tiled_weights[weight.data_ptr()] = (weight, swiglu)
         if rows * k >= self.few_token_min_elements:
             self._few_token_weights[weight.data_ptr()] = ops.DecodeWeight(weight, swiglu)
 
@@ -102,9 +104,14 @@ class Runtime:
         prepared = self._tiled_weights.get(weight.data_ptr())
         if prepared is None or x.shape[0] < self.tiled_min_rows or x.stride(0) % 8 or x.data_ptr() % 16:
             return None
-        least = ops.gemm_tiles_lib().pairs if self.tiled_min_tiles is None else self.tiled_min_tiles
-        if ops.gemm_tiles_count(x.shape[0], prepared.n, prepared.swiglu) < least:
+        known = isinstance(prepared, ops.TiledWeight)
+        swiglu = prepared.swiglu if known else prepared[1]
+        n = prepared.n if known else prepared[0].shape[0] // (2 if swiglu else 1)
+        least = self.sm_count // 2 if self.tiled_min_tiles is None else self.tiled_min_tiles
+        if ops.gemm_tiles_count(x.shape[0], n, swiglu) < least:
             return None
+        if not known:
+            prepared = self._tiled_weights[weight.data_ptr()] = ops.TiledWeight(prepared[0], swiglu)
         return prepared
 
     def _tiled_product(self, prepared, x, bias, out_dtype) -> torch.Tensor:

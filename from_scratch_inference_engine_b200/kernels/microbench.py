@@ -148,13 +148,18 @@ def run_attention(args, timer, decode: bool):
         # cycles per key tile that one warp spent in each phase, summed over all blocks by the kernel
         import ctypes
         lib = ops.attn_tc(hd)
-        counters = (ctypes.c_ulonglong * 8)()
+        counters = (ctypes.c_ulonglong * 10)()
         torch.cuda.synchronize()
         lib.fsie_attn_tc_timing.argtypes = [ctypes.c_void_p]
         lib.fsie_attn_tc_timing(counters)
         names = (["wait_p", "wait_ring", "issue"] if any("TIMING_MMA" in d for d in args.build_defines)
                  else ["wait_s", "read_s", "max", "wait_pv", "exp_p", "hand_over"])
         extra["cycles_per_tile"] = {n: round(counters[k] / max(1, counters[6])) for k, n in enumerate(names)}
+        blocks = tile_item.numel() * kv_heads * nsplit
+        launches = args.warmup + args.iters
+        extra["cycles_per_block_before_the_loop"] = round(counters[7] / max(1, blocks * launches))
+        extra["cycles_per_block_after_the_loop"] = round(counters[8] / max(1, blocks * launches))
+        extra["tiles_per_block"] = round(counters[6] / max(1, blocks * launches), 2)
     elem = 2 if dtype is torch.bfloat16 else 4
     kv_bytes = args.batch * args.context * 2 * kv_heads * hd * elem
     io_bytes = kv_bytes + 2 * tokens * heads * hd * elem
