@@ -76,16 +76,44 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int voca
                                       float* __restrict__ part_v, int* __restrict__ part_i) {
     __shared__ float best_v[8];
     __shared__ int best_i[8];
+    grid_dependency_wait();
+    grid_dependents_go();
     const int row = blockIdx.y, part = blockIdx.x;
     const float* src = logits + (size_t)row * vocab;
-    const int seg = (vocab + parts - 1) / parts;
-    const int begin = part * seg, end = min(vocab, begin + seg);
+    const int seg = (((vocab + parts - 1) / parts) + 3) & ~3;
+    const int begin = min(vocab, part * seg), end = min(vocab, begin + seg);
+    // a thread meets its indices in rising order: "greater" alone keeps the first of equals
     float bv = -INFINITY;
     int bi = 0x7fffffff;
+    if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        // 16 bytes per load, two loads in flight
+        int i = begin + 4 * threadIdx.x;
+        const int step = 4 * blockDim.x;
+        for (; i + step + 3 < end; i += 2 * step) {
+            const float4 a = *reinterpret_cast<const float4*>(src + i);
+            const float4 b = *reinterpret_cast<const float4*>(src + i + step);
+            if (a.x > bv) { bv = a.x; bi = i; }
+            if (a.y > bv) { bv = a.y; bi = i + 1; }
+            if (a.z > bv) { bv = a.z; bi = i + 2; }
+            if (a.w > bv) { bv = a.w; bi = i + 3; }
+            if (b.x > bv) { bv = b.x; bi = i + step; }
+            if (b.y > bv) { bv = b.y; bi = i + step + 1; }
+            if (b.z > bv) { bv = b.z; bi = i + step + 2; }
+            if (b.w > bv) { bv = b.w; bi = i + step + 3; }
+        }
+        for (; i + 3 < end; i += step) {
+            const float4 a = *reinterpret_cast<const float4*>(src + i);
+            if (a.x > bv) { bv = a.x; bi = i; }
+            if (a.y > bv) { bv = a.y; bi = i + 1; }
+            if (a.z > bv) { bv = a.z; bi = i + 2; }
+            if (a.w > bv) { bv = a.w; bi = i + 3; }
+        }
+    } else {
 #pragma unroll 4
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        const float v = src[i];
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+            const float v = src[i];
+            if (v > bv) { bv = v; bi = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -107,6 +135,8 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int voca
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                                     int parts, int* __restrict__ out) {
+    grid_dependency_wait();
+    grid_dependents_go();
     const int row = blockIdx.x;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -515,8 +545,9 @@ int fsie_argmax_staged(const float* logits, int rows, int vocab, int* out, void*
     if (vocab <= 0 || parts <= 0 || !scratch) return fsie::ERR_BAD_ARGUMENT;
     float* part_v = (float*)scratch;
     int* part_i = (int*)scratch + (size_t)rows * parts;
-    fsie::argmax_partial_kernel<<<dim3(parts, rows), 256, 0, stream>>>(logits, vocab, parts, part_v, part_i);
-    fsie::argmax_final_kernel<<<rows, 32, 0, stream>>>(part_v, part_i, parts, out);
+    int rc = fsie::launch_dependent(fsie::argmax_partial_kernel, dim3(parts, rows), dim3(256), 0, stream, logits, vocab, parts, part_v, part_i);
+    if (rc != 0) return rc;
+    return fsie::launch_dependent(fsie::argmax_final_kernel, dim3(rows), dim3(32), 0, stream, (const float*)part_v, (const int*)part_i, parts, out);
     return FSIE_LAUNCH_CHECK();
 }
 

@@ -9,7 +9,7 @@ machine without the compiled library or without a GPU they raise.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 
@@ -596,23 +596,34 @@ def gemm_tiles(weight: TiledWeight, x: torch.Tensor, out: torch.Tensor,
 
 
 # --------------------------------------------------------------------------- sampling
-ARGMAX_PARTS = 32      # blocks per row of the two-stage argmax
+ARGMAX_PARTS = 64      # blocks per row of the two-stage argmax
+_argmax_scratch: Dict[int, torch.Tensor] = {}
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor,
            scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[r] = index of the largest logit of row r, ties to the smallest index.  With
-    `scratch` (float32, at least 2 * rows * ARGMAX_PARTS elements) a wide row is reduced by
-    ARGMAX_PARTS blocks and a second small kernel; without it one block takes each row."""
+    """out[r] = index of the largest logit of row r, ties to the smallest index.  A wide row is
+    reduced by ARGMAX_PARTS blocks and a second small kernel (in `scratch`, float32, at least
+    2 * rows * ARGMAX_PARTS elements; the module keeps one per device when none is given -
+    pass your own inside a stream capture); a narrow row by one block."""
     _need(logits, torch.float32, "logits")
     _need(out, torch.int32, "out")
     rows, vocab = logits.shape
-    if scratch is not None and vocab >= 8192:
+    if vocab >= 8192:
+        need = 2 * rows * ARGMAX_PARTS
+        if scratch is None:
+            key = logits.device.index or 0
+            scratch = _argmax_scratch.get(key)
+            if scratch is None or scratch.numel() < need:
+                scratch = _argmax_scratch[key] = torch.empty(max(need, 1 << 16), dtype=torch.float32,
+                                                             device=logits.device)
         _need(scratch, torch.float32, "scratch")
-        if scratch.numel() < 2 * rows * ARGMAX_PARTS:
+        if scratch.numel() < need:
             raise KernelError("argmax: scratch is too small")
+        # enough blocks to fill the GPU several times over, each with more than a few loads per thread
+        parts = max(4, min(ARGMAX_PARTS, 2048 // rows))
         _check(core().fsie_argmax_staged(_ptr(logits), rows, vocab, _ptr(out), _ptr(scratch),
-                                         ARGMAX_PARTS, _stream()), "argmax")
+                                         parts, _stream()), "argmax")
         return out
     _check(core().fsie_argmax(_ptr(logits), rows, vocab, _ptr(out), _stream()), "argmax")
     return out
