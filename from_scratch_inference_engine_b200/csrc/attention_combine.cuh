@@ -26,11 +26,19 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     const float inv = denom > 0.f ? 1.0f / denom : 0.f;
     for (int d = threadIdx.x * 2; d < HD; d += blockDim.x * 2) {
         float a0 = 0.f, a1 = 0.f;
-        for (int z = 0; z < nsplit; ++z) {
-            const float w = __shfl_sync(0xffffffffu, wz, z);
-            if (w != 0.f) {
-                const float2 v = *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d);
-                a0 += v.x * w; a1 += v.y * w;
+        for (int z0 = 0; z0 < nsplit; z0 += 8) {
+            // eight splits' values are asked for before the first is used: one trip to memory for
+            // eight, not eight trips
+            float2 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int z = min(z0 + j, nsplit - 1);
+                v[j] = *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float w = __shfl_sync(0xffffffffu, wz, min(z0 + j, 31));
+                if (z0 + j < nsplit && w != 0.f) { a0 += v[j].x * w; a1 += v[j].y * w; }   // a split without keys may hold anything
             }
         }
         *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * out_ld + h * HD + d) =
