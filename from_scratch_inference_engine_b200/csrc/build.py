@@ -42,6 +42,8 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     "gemm_decode": ("gemm_decode_tcgen05.cu",),
     # tcgen05 / TMA matrix product for steps of many tokens, with fused bias or SwiGLU
     "gemm_tiles": ("gemm_tiles_tcgen05.cu",),
+    # mma.sync product without set-up for steps of few tokens against small matrices
+    "gemm_skinny": ("gemm_skinny.cu",),
 }
 # specialisations compiled by build_all() beside the default form of every library
 DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)], "attn_tma": [("-DHEAD_DIM=128",)],

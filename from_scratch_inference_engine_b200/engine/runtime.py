@@ -140,6 +140,10 @@ class Runtime:
         tiled = self._tiled(x, weight)
         if tiled is not None and not tiled.swiglu:
             return self._tiled_product(tiled, x, bias, torch.bfloat16)
+        if self.products == "own" and ops.gemm_skinny_fits(x.shape[0], x.shape[1]) and x.stride(0) % 8 == 0 \
+                and weight.dtype is torch.bfloat16 and weight.is_contiguous():
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+            return ops.gemm_skinny(weight, x, out, bias)
         return F.linear(x, weight, bias)
 
     def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:

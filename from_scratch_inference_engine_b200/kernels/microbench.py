@@ -229,6 +229,12 @@ def run(args):
         ms = timer(lambda: ops.gemm_decode(weight, x, out, None, error, splits))
         extra = {"splits": splits, "error": int(error.item())}
         nbytes, flops = (m * k + w.shape[0] * k + m * n) * elem, 2.0 * m * w.shape[0] * k
+    elif args.kernel == "gemm_skinny":
+        m, n, k = args.tokens, args.n, args.k
+        x, w = rand(m, k).to(dtype), (rand(n, k) / math.sqrt(k)).to(dtype)
+        out = torch.empty((m, n), dtype=dtype, device="cuda")
+        ms = timer(lambda: ops.gemm_skinny(w, x, out, None))
+        nbytes, flops = (m * k + n * k + m * n) * elem, 2.0 * m * n * k
     elif args.kernel in ("gemm_tiles", "gemm_tiles_swiglu"):
         m, n, k = args.tokens, args.n, args.k
         swiglu = args.kernel == "gemm_tiles_swiglu"

@@ -522,6 +522,45 @@ def gemm_decode(weight: DecodeWeight, x: torch.Tensor, out: torch.Tensor,
     return out
 
 
+_gemm_skinny = None
+GEMM_SKINNY_MAX_TOKENS = 16
+
+
+def gemm_skinny_fits(tokens: int, k: int) -> bool:
+    """Whether `gemm_skinny` takes a product of `tokens` rows over `k`."""
+    return 0 < tokens <= GEMM_SKINNY_MAX_TOKENS and k % 32 == 0
+
+
+def gemm_skinny(weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor,
+                bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ weight.T (+ bias) for T <= 16: no pipeline to fill, every lane asks
+    for its weights straight from global memory (for matrices so small that set-up would
+    dominate).  out is bfloat16 or float32."""
+    global _gemm_skinny
+    if _gemm_skinny is None:
+        lib = build.load_library("gemm_skinny")
+        i, ll, p = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_gemm_skinny.argtypes = [p, p, ll, p, ll, p, i, i, i, i, p]
+        lib.fsie_gemm_skinny.restype = i
+        _gemm_skinny = lib
+    _need(weight, torch.bfloat16, "weight")
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(out, None, "out", contiguous=False)
+    tokens, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or x.stride(1) != 1 or not gemm_skinny_fits(tokens, k):
+        raise KernelError("gemm_skinny: x does not fit the weight, or the sizes are beyond the kernel")
+    if out.shape[0] != tokens or out.shape[1] != n or out.stride(1) != 1 or \
+            out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_skinny: out does not fit")
+    if bias is not None:
+        _need(bias, torch.bfloat16, "bias")
+    _check(_gemm_skinny.fsie_gemm_skinny(_ptr(weight), _ptr(x), x.stride(0), _ptr(out), out.stride(0),
+                                         _ptr(bias), tokens, n, k, int(out.dtype is torch.float32),
+                                         _stream()), "gemm_skinny")
+    return out
+
+
 _gemm_tiles = None
 
 

@@ -539,3 +539,39 @@ def test_gemm_tiles_one_key_block_stands_out(ops):
     want = dev(x, torch.bfloat16).double() @ dev(w, torch.bfloat16).double().T
     assert error.item() == 0
     assert (out.double() - want).abs().max().item() < 1e-3 * want.abs().max().item()
+
+
+# -------------------------------------------------------- product without set-up for small matrices
+@pytest.mark.parametrize("tokens", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(384, 512), (200, 96), (37, 1024), (4608, 3584)])
+def test_gemm_skinny(ops, tokens, n, k):
+    """Rows of w in blocks of 16 (a ragged last block), k in chunks of 32 taken in turn by eight
+    warps (fewer chunks than warps at k = 96), tokens padded to 8 or 16."""
+    torch.manual_seed(tokens * 1000 + n)
+    x_full = dev(torch.randn(tokens, k + 8), torch.bfloat16)
+    x = x_full[:, :k]
+    w = dev(torch.randn(n, k) / math.sqrt(k), torch.bfloat16)
+    bias = dev(torch.randn(n), torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.full((tokens, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_skinny(w, x, out, None)
+    assert (out.double() - want).abs().max().item() < 1.6e-2 * want.abs().max().item()
+    out32 = torch.full((tokens, n), float("nan"), dtype=torch.float32, device="cuda")
+    ops.gemm_skinny(w, x, out32, bias)
+    assert (out32.double() - want - bias.double()).abs().max().item() < 2e-3 * want.abs().max().item()
+
+
+def test_gemm_skinny_one_element_stands_out(ops):
+    """A single k position of a single row and token carries the result: a lane that pairs the
+    wrong 16 bytes of x with its weights shows at once."""
+    tokens, n, k = 7, 64, 256
+    for kk, row, token in ((0, 0, 0), (37, 9, 3), (255, 63, 6), (130, 24, 5)):
+        x = torch.zeros(tokens, k)
+        w = torch.zeros(n, k)
+        x[token, kk] = 3.0
+        w[row, kk] = 0.5
+        out = torch.empty((tokens, n), dtype=torch.float32, device="cuda")
+        ops.gemm_skinny(dev(w, torch.bfloat16), dev(x, torch.bfloat16), out, None)
+        want = torch.zeros(tokens, n)
+        want[token, row] = 1.5
+        assert torch.equal(out.cpu(), want), (kk, row, token)
