@@ -70,8 +70,18 @@ class _DecodeGraph:
         from ..kernels import ops
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launches
-        with torch.cuda.graph(self.graph, pool=runner.graph_pool()):
-            self.logits = runner.model.forward(self.context, runner.layer_caches, self.rows)
+        # Nothing may free pinned or device memory while the stream is capturing; the garbage
+        # collector would, if it came across a dropped engine's staging buffers just then.
+        import gc
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, pool=runner.graph_pool(), capture_error_mode="thread_local"):
+                self.logits = runner.model.forward(self.context, runner.layer_caches, self.rows)
+        finally:
+            if was_enabled:
+                gc.enable()
         self.launches = ops.launches - before
 
     def fill(self, token_ids, pos0, slots, tables) -> StepContext:

@@ -140,11 +140,17 @@ class Runtime:
         tiled = self._tiled(x, weight)
         if tiled is not None and not tiled.swiglu:
             return self._tiled_product(tiled, x, bias, torch.bfloat16)
-        if self.products == "own" and ops.gemm_skinny_fits(x.shape[0], x.shape[1]) and x.stride(0) % 8 == 0 \
-                and weight.dtype is torch.bfloat16 and weight.is_contiguous():
+        if self._skinny(x, weight):
             out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
             return ops.gemm_skinny(weight, x, out, bias)
         return F.linear(x, weight, bias)
+
+    def _skinny(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
+        """Whether the set-up-free product takes this step: few tokens, and a matrix that the
+        tcgen05 few-token product was not prepared for (a small one)."""
+        return (self.products == "own" and ops.gemm_skinny_fits(x.shape[0], x.shape[1])
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+                and weight.dtype is torch.bfloat16 and weight.is_contiguous())
 
     def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
         """silu(x @ gate.T) * (x @ up.T) for the stacked weight [gate rows; up rows]: one fused
@@ -169,6 +175,9 @@ class Runtime:
         tiled = self._tiled(x, weight)
         if tiled is not None and not tiled.swiglu:
             return self._tiled_product(tiled, x, None, torch.float32)
+        if self._skinny(x, weight):
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+            return ops.gemm_skinny(weight, x, out, None)
         if self._f32_out is None:
             try:
                 torch.mm(x[:1], weight[:8].t(), out_dtype=torch.float32)
