@@ -94,8 +94,6 @@ attn_mma_kernel(const AttnParams p) {
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw + S::Q_BYTES);
     bf16* Vs = Ks + (size_t)STAGES * BN * LDS;
 
-    grid_dependency_wait();
-    grid_dependents_go();
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     const int item = p.tile_item[tile];
@@ -124,16 +122,6 @@ attn_mma_kernel(const AttnParams p) {
         kbegin = b;
     }
     const int ntiles = kend > kbegin ? (kend - kbegin + BN - 1) / BN : 0;
-
-    // ---- stage the query rows (rows beyond the tile's count are zero)
-    for (int e = tid; e < BM * CHUNKS; e += THREADS) {
-        const int r = e / CHUNKS, c = e - r * CHUNKS;
-        const bool ok = r < nrows;
-        const int row = row0 + (ok ? r : 0);
-        const int tok = qstart + row / group, h = kvh * group + row % group;
-        cp_async16(Qs + r * LDS + c * 8, q + (size_t)tok * p.q_ld + h * HD + c * 8, ok);
-    }
-    cp_async_commit();
 
     // Element offset of every key row of a tile inside the pages (-1: not to be read), worked
     // out one loop iteration before the tile is fetched, so that the fetch itself is a
@@ -170,8 +158,27 @@ attn_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) find_rows(s, kbegin + s * BN);
     __syncthreads();
+    // Under programmatic dependent launch the kernel before this one (which writes this step's
+    // new keys, values and rotated queries) may still be running.  The lists and block tables
+    // read so far were staged before the step; keys older than every new token of the request
+    // were written by earlier steps: a first tile of only such keys is asked for at once.
+    const bool early = ntiles > 0 && kbegin + BN <= pos0;
+    if (early) load_tile(0);
+    cp_async_commit();
+    grid_dependency_wait();
+    grid_dependents_go();
+    // ---- stage the query rows (rows beyond the tile's count are zero)
+    for (int e = tid; e < BM * CHUNKS; e += THREADS) {
+        const int r = e / CHUNKS, c = e - r * CHUNKS;
+        const bool ok = r < nrows;
+        const int row = row0 + (ok ? r : 0);
+        const int tok = qstart + row / group, h = kvh * group + row % group;
+        cp_async16(Qs + r * LDS + c * 8, q + (size_t)tok * p.q_ld + h * HD + c * 8, ok);
+    }
+    if (!early && ntiles > 0) load_tile(0);
+    cp_async_commit();
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
+    for (int s = 1; s < STAGES - 1; ++s) {
         if (s < ntiles) load_tile(s);
         cp_async_commit();
     }
