@@ -168,7 +168,7 @@ __device__ __forceinline__ float fast_exp2(float v) {
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a 128-byte-swizzled block
 __device__ __forceinline__ int swizzled(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p, const TcExtra x) {
     extern __shared__ __align__(1024) unsigned char smem_all[];
     Control& ctl = *reinterpret_cast<Control*>(smem_all);
