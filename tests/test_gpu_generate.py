@@ -203,3 +203,18 @@ def test_overlapped_steps_give_the_same_tokens_as_one_step_at_a_time(folders):
     assert first[4] == stopped and len(stopped) < 20
     assert [len(o) for o in first] == [9, 14, 1, 11, len(stopped), 7, 13]
     assert all(other == first for other in results.values())
+
+
+def test_warm_up_captures_the_decode_graphs_and_changes_no_token(folders):
+    from from_scratch_inference_engine_b200 import SamplingParams
+    greedy = SamplingParams(temperature=0.0)
+    prompts = [helpers.random_ids(384, n, s) for n, s in ((9, 1), (20, 2), (3, 3))]
+    cold = engine_for(folders["B"], block_size=8, dtype="bfloat16")
+    want = [cold.generate(p, greedy, 8) for p in prompts]
+    warm = engine_for(folders["B"], block_size=8, dtype="bfloat16", max_batch=4)
+    graphs = warm.warm_up(100)
+    assert graphs == 3 and len(warm.runner._graphs) == 3          # batches 1, 2 and 4 at one table width
+    ids = [warm.add_request(p, greedy, 8) for p in prompts]
+    warm.run_until_done()
+    assert len(warm.runner._graphs) == 3                            # nothing was captured while serving
+    assert sorted(warm.output(i) for i in ids) == sorted(want)
