@@ -204,3 +204,104 @@ def test_windowed_group_bounds_what_a_request_holds():
         if s.sequences[rid].handle is not None:
             peak = max(peak, sum(p >= 0 for p in s.sequences[rid].handle.tables[1]))
     assert len(s.sequences[rid].output) == 30 and peak <= 5
+
+
+# ------------------------------------------------------------------ overlapped steps
+def run_overlapped(s, cache, limit=10_000):
+    """Drives the scheduler as the engine does with overlapped steps: the next step is planned
+    and 'launched' (pages reserved and committed) before the tokens of the step before it are
+    known; only then are those tokens computed and recorded.  The stand-in model needs the whole
+    context, so a token is computed when it is resolved - which also proves that no plan ever
+    needed a token that was still pending."""
+    from from_scratch_inference_engine_b200.engine.scheduler import PENDING_TOKEN
+    in_flight = None
+    wasted = 0
+
+    def settle():
+        nonlocal in_flight, wasted
+        items = in_flight
+        in_flight = None
+        tokens = []
+        for item in items:
+            seq = item.seq
+            if item.samples and seq.status is SeqStatus.Running and seq.handle is not None and seq.pending:
+                context = seq.context()
+                tokens.append((sum(context) * 31 + len(context)) % 97)
+            else:
+                wasted += bool(item.samples)
+                tokens.append(None if not item.samples else 0)      # a dropped token: any value
+        s.resolve_step(items, tokens)
+        cache.check()
+
+    for _ in range(limit):
+        if not s.has_work() and in_flight is None:
+            return wasted
+        items = s.plan(can_preempt=in_flight is None)
+        if not items and in_flight is not None:
+            settle()
+            items = s.plan()
+        if not items:
+            assert not s.has_work(), "no progress"
+            continue
+        for item in items:
+            assert item.seq.status is SeqStatus.Running
+            if item.source_row >= 0:
+                assert item.tokens == [PENDING_TOKEN] and item.seq.pending == 1
+            else:
+                context = item.seq.context()
+                at = item.seq.handle.length
+                assert context[at:at + len(item.tokens)] == item.tokens
+            cache.reserve(item.seq.handle, len(item.tokens))
+            cache.commit(item.seq.handle, len(item.tokens))
+        if in_flight is not None:
+            settle()
+        s.begin_step(items)
+        in_flight = items
+    raise AssertionError("did not finish")
+
+
+@pytest.mark.parametrize("num_pages", [64, 9])
+def test_overlapped_steps_record_the_same_tokens(num_pages):
+    """With a roomy pool and with one that forces preemption: every request ends with the tokens it
+    gets alone; a request that stops at an end-of-sequence token costs one dropped token."""
+    prompts = [[5, 6, 7], list(range(1, 20)), [9] * 11, [3, 1, 4, 1, 5, 9, 2, 6], [8]]
+    lengths = [6, 9, 4, 12, 7]
+    eos_of = {3: alone(prompts[3], 12)[4]}
+    want = [alone(p, n, eos_of.get(i, -1)) for i, (p, n) in enumerate(zip(prompts, lengths))]
+    s, cache = make(num_pages=num_pages, max_batch=3, max_step_tokens=8)
+    ids = [s.add(p, GREEDY, n, eos_of.get(i, -1), seed=0) for i, (p, n) in enumerate(zip(prompts, lengths))]
+    wasted = run_overlapped(s, cache)
+    assert [s.sequences[i].output for i in ids] == want
+    assert len(want[3]) < 12 and wasted >= 1
+    assert all(seq.pending == 0 and seq.status is SeqStatus.Finished for seq in s.sequences.values())
+    assert cache.free_pages() == [num_pages]
+    if num_pages == 9:
+        assert s.preemptions > 0
+
+
+def test_a_plan_that_would_preempt_is_given_up_while_tokens_are_pending():
+    s, cache = make(num_pages=4, max_batch=2, max_step_tokens=8)          # 16 tokens of cache
+    a = s.add([1] * 7, GREEDY, 8, -1, seed=0)
+    b = s.add([2] * 7, GREEDY, 8, -1, seed=0)
+    items = s.plan()
+    for item in items:
+        cache.reserve(item.seq.handle, len(item.tokens))
+        cache.commit(item.seq.handle, len(item.tokens))
+    s.begin_step(items)
+    pending = [i for i in items if i.samples]
+    assert pending and all(i.seq.pending == 1 for i in pending)
+    # fill the pool: both requests now hold all four pages between them
+    while True:
+        items2 = s.plan(can_preempt=False)
+        if not items2:
+            break
+        for item in items2:
+            cache.reserve(item.seq.handle, len(item.tokens))
+            cache.commit(item.seq.handle, len(item.tokens))
+        s.resolve_step(items, [1 if i.samples else None for i in items])
+        s.begin_step(items2)
+        items = items2
+    assert s.preemptions == 0                  # it came back empty instead of preempting
+    s.resolve_step(items, [1 if i.samples else None for i in items])
+    assert s.plan() and s.preemptions >= 1    # with nothing pending the youngest is preempted
+    assert {s.sequences[a].status, s.sequences[b].status} == {SeqStatus.Running, SeqStatus.Waiting}
