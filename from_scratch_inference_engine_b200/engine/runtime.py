@@ -50,6 +50,7 @@ class Runtime:
         # weights prepared for the tcgen05 product of steps with few tokens, by storage address
         self._few_token_weights: Dict[int, ops.DecodeWeight] = {}
         self.few_token_limit = 16          # steps of up to this many tokens take that product
+        self.few_token_limit_fused = 16    # ... the same for the product with the fused SwiGLU
         self.few_token_min_elements = few_token_min_elements   # ... for matrices at least this large
         # "own": steps of many tokens take the tiled tcgen05 product (fused bias / SwiGLU) where
         # its tiles fill the GPU; "library": they take the library product
@@ -119,9 +120,13 @@ class Runtime:
         return ops.gemm_tiles(prepared, x, out, bias, self.error, self.sm_count)
 
     def _few_tokens(self, x: torch.Tensor, weight: torch.Tensor) -> Optional["ops.DecodeWeight"]:
-        if x.shape[0] > self.few_token_limit or x.stride(0) % 8:
+        if x.shape[0] > max(self.few_token_limit, self.few_token_limit_fused) or x.stride(0) % 8:
             return None
-        return self._few_token_weights.get(weight.data_ptr())
+        prepared = self._few_token_weights.get(weight.data_ptr())
+        if prepared is None:
+            return None
+        limit = self.few_token_limit_fused if prepared.swiglu else self.few_token_limit
+        return prepared if x.shape[0] <= limit else None
 
     def _few_token_product(self, prepared, x, bias, out_dtype) -> torch.Tensor:
         out = torch.empty((x.shape[0], prepared.n), dtype=out_dtype, device=x.device)
