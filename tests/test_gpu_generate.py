@@ -218,3 +218,24 @@ def test_warm_up_captures_the_decode_graphs_and_changes_no_token(folders):
     warm.run_until_done()
     assert len(warm.runner._graphs) == 3                            # nothing was captured while serving
     assert sorted(warm.output(i) for i in ids) == sorted(want)
+
+
+def test_command_line_generates_from_a_random_weights_folder(tmp_path, capsys):
+    """The command line writes a random model from a configuration, generates for several requests
+    and reports JSON; the same tokens as the Python entry point on that folder."""
+    import json
+    from from_scratch_inference_engine_b200 import LLM, GenerationConfig, cli
+    config = dict(helpers.TINY["E"]["config"])
+    config_path = tmp_path / "config_in.json"
+    config_path.write_text(json.dumps(config))
+    folder = tmp_path / "model"
+    code = cli.main(["--model-dir", str(folder), "--random-weights", str(config_path), "--weights-seed", "5",
+                     "--std", "0.08", "--prompt-ids", "5,17,3,88,41", "--num-requests", "3", "--max-tokens", "9",
+                     "--block-size", "16", "--num-blocks", "32", "--json"])
+    assert code == 0
+    report = json.loads(capsys.readouterr().out)
+    assert report["requests"] == 3 and report["total_output_tokens"] == 27
+    assert report["outputs"][0] == report["outputs"][1] == report["outputs"][2]      # greedy, same prompt
+    assert (folder / "config.json").exists() and (folder / "model.safetensors").exists()
+    llm = LLM(str(folder), block_size=16, num_blocks=32)
+    assert llm.generate_ids([5, 17, 3, 88, 41], GenerationConfig(max_tokens=9, temperature=0.0)) == report["outputs"][0]
