@@ -181,11 +181,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     unsigned char* ring = q_s + STREAMS * Q_BYTES;           // [slot][HALVES][128 keys][128 B]
     int& abort_flag = ctl.abort_flag;
 
-    // later tiles of a prompt see more keys: start them first so that the last wave is short
 #ifdef FSIE_TC_TIMING
     const long long block_begin_ = clock64();
 #endif
-    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // Blocks are handed out in the order of blockIdx.x, and the caller lists the tiles with the most
+    // keys first: all kv heads of the longest tile start first, so that the last wave is short.
+    const int tile = blockIdx.x / p.kv_heads, kvh = blockIdx.x % p.kv_heads, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     const int item = p.tile_item[tile];
     const int row0 = p.tile_row0[tile];
@@ -625,7 +626,7 @@ int fsie_attn_tc(const void* pages_map, int entries, int entry, const void* q, i
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attn_tc_kernel<<<dim3(tiles, kv_heads, nsplit), THREADS, SMEM_BYTES, stream>>>(map, p, x);
+    attn_tc_kernel<<<dim3(tiles * kv_heads, 1, nsplit), THREADS, SMEM_BYTES, stream>>>(map, p, x);
     int rc = (int)cudaGetLastError();
     if (rc != 0 || nsplit == 1) return rc;
     const int count = combine_tokens ? num_combine : tokens;

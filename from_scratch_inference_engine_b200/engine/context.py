@@ -164,6 +164,13 @@ class StepContext:
             item = np.repeat(members.astype(np.int32), counts)
             first = np.cumsum(counts) - counts
             row0 = ((np.arange(int(counts.sum())) - np.repeat(first, counts)) * per_tile)
+            if item.size > 1:
+                # tiles that see the most keys first: blocks start in list order, and the longest
+                # should not start last
+                last_row = np.minimum(row0 + per_tile, rows[item]) - 1
+                keys = self.h_pos0[item] + last_row // group_size + 1
+                order = np.argsort(-keys, kind="stable")
+                item, row0 = item[order], row0[order]
             tokens = np.concatenate([np.arange(self.h_qstart[i], self.h_qstart[i] + self.h_qlen[i],
                                                dtype=np.int32) for i in members])
             longest = self.fixed_context or int((self.h_pos0[members] + self.h_qlen[members]).max())

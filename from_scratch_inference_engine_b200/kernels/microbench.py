@@ -107,6 +107,9 @@ def run_attention(args, timer, decode: bool):
             tile_item.append(i)
             tile_row0.append(r0)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    # as the engine lists them: the tiles that see the most keys first
+    by_keys = sorted(range(len(tile_item)), key=lambda n: -(past + (min(tile_row0[n] + per_tile, rows) - 1) // group))
+    tile_item, tile_row0 = [tile_item[n] for n in by_keys], [tile_row0[n] for n in by_keys]
     tile_item, tile_row0 = i32(tile_item), i32(tile_row0)
     nsplit = args.nsplit
     if nsplit <= 0:
