@@ -36,7 +36,9 @@ attn_generic_kernel(const AttnParams p) {
     float* vs = ks + KT * (hd + 1);           // [KT][hd]
     __shared__ long long key_base[KT];
 
-    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // blocks start in the order of blockIdx.x: all kv heads of a tile, then the next tile (the
+    // caller lists the tiles that see the most keys first)
+    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     const int item = p.tile_item[tile];
     const int row0 = p.tile_row0[tile];
@@ -206,6 +208,7 @@ int fsie_attn_generic(const void* q, int q_ld, const void* k_pages, const void* 
                       int kv_heads, int head_dim, int window, int nsplit, float scale, int dtype,
                       cudaStream_t stream) {
     if (tiles <= 0 || tokens <= 0) return 0;
+    if (tiles > 65535) return ERR_UNSUPPORTED;          // tiles are the grid's y dimension
     if (head_dim <= 0 || head_dim > 32 * MAX_DPL || kv_heads <= 0 || heads % kv_heads != 0 ||
         nsplit < 1 || page_size <= 0)
         return ERR_BAD_ARGUMENT;
@@ -221,7 +224,7 @@ int fsie_attn_generic(const void* q, int q_ld, const void* k_pages, const void* 
     p.window = window; p.nsplit = nsplit; p.scale = scale;
     const size_t smem = sizeof(float) * ((size_t)ROWS * head_dim + (size_t)KT * (head_dim + 1) +
                                          (size_t)KT * head_dim);
-    dim3 grid(tiles, kv_heads, nsplit);
+    dim3 grid(kv_heads, tiles, nsplit);
     if (dtype == DTYPE_F32) {
         cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attn_generic_kernel<float><<<grid, WARPS * 32, smem, stream>>>(p);

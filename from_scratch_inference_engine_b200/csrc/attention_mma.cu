@@ -94,7 +94,9 @@ attn_mma_kernel(const AttnParams p) {
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw + S::Q_BYTES);
     bf16* Vs = Ks + (size_t)STAGES * BN * LDS;
 
-    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // blocks start in the order of blockIdx.x: all kv heads of a tile, then the next tile (the
+    // caller lists the tiles that see the most keys first)
+    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     const int item = p.tile_item[tile];
     const int row0 = p.tile_row0[tile];
@@ -392,7 +394,7 @@ static int launch(const AttnParams& p, int tiles, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(tiles, p.kv_heads, p.nsplit);
+    dim3 grid(p.kv_heads, tiles, p.nsplit);
     return launch_dependent(kernel, grid, dim3(S::THREADS), S::SMEM, stream, p);
 }
 
@@ -419,6 +421,7 @@ int fsie_attn_mma(int row_class, const void* q, int q_ld, const void* k_pages, c
                   int nsplit, float scale, const int* combine_tokens, int num_combine,
                   cudaStream_t stream) {
     if (tiles <= 0 || tokens <= 0) return 0;
+    if (tiles > 65535) return ERR_UNSUPPORTED;          // tiles are the grid's y dimension
     if (head_dim != HD) return ERR_UNSUPPORTED;
     if (kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 || page_size <= 0 || (q_ld % 8) != 0 ||
         (out_ld % 2) != 0 || (page_stride % 8) != 0)

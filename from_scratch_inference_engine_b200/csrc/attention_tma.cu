@@ -106,7 +106,9 @@ attn_tma_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams 
     unsigned char* Vs = Ks + (size_t)STAGES * TILE_BYTES;
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES];
 
-    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // blocks start in the order of blockIdx.x: all kv heads of a tile, then the next tile (the
+    // caller lists the tiles that see the most keys first)
+    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
     const int item = p.tile_item[tile];
     const int row0 = p.tile_row0[tile];
@@ -408,7 +410,7 @@ static int launch(const CUtensorMap& map, const AttnParams& p, const TmaExtra& x
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(tiles, p.kv_heads, p.nsplit);
+    dim3 grid(p.kv_heads, tiles, p.nsplit);
     kernel<<<grid, S::THREADS, S::SMEM, stream>>>(map, p, x);
     return (int)cudaGetLastError();
 }
@@ -453,6 +455,7 @@ int fsie_attn_tma(int row_class, const void* pages_map, int entries, int entry, 
                   int nsplit, float scale, const int* combine_tokens, int num_combine, int* error,
                   cudaStream_t stream) {
     if (tiles <= 0 || tokens <= 0) return 0;
+    if (tiles > 65535) return ERR_UNSUPPORTED;          // tiles are the grid's y dimension
     if (head_dim != HD) return ERR_UNSUPPORTED;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return ERR_UNSUPPORTED;
     if (kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 || nsplit > 32 || (q_ld % 8) != 0 ||
