@@ -203,6 +203,94 @@ def serving_workload(args) -> int:
     return 0
 
 
+def long_context_workload(args) -> int:
+    """The Qwen2.5-14B shape on one GPU: decode at batch 32 with contexts of 8,192 tokens, and
+    chunked prefill (2,048-token portions) of an 8,192-token prompt.  One JSON line."""
+    import numpy as np
+    import torch
+    from from_scratch_inference_engine_b200 import LoadedModel, ModelRunner, StepEntry
+    from from_scratch_inference_engine_b200.config import config_from_dict
+    from from_scratch_inference_engine_b200.kernels import ops
+
+    shape = dict(SHAPE_14B)
+    layers = args.layers or shape["num_hidden_layers"]
+    shape["num_hidden_layers"] = layers
+    config = config_from_dict(shape)
+    peak, peak_source = peaks()
+    batch, context, portion, page = 32, 8192, 2048, 16
+    steps, warmup = min(args.steps, 32), max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16", max_positions=context + 64)
+    device = model.runtime.device
+
+    def timed(fn):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end)
+
+    # ---- chunked prefill of one prompt (the second run is timed: kernels are compiled by the first)
+    runner = ModelRunner(model.model, model.runtime, page_size=page, num_pages=2 * (context // page + 1),
+                         max_requests=2)
+    prompt = rng.integers(0, config.vocab_size, size=context).tolist()
+    portions_ms = []
+    for attempt in range(2):
+        handle = runner.cache.open(("p", attempt))
+        portions_ms = [timed(lambda at=at: runner.step([StepEntry(handle, prompt[at:at + portion],
+                                                                  [portion - 1] if at + portion == context else [])]))
+                       for at in range(0, context, portion)]
+        runner.cache.close(handle)
+    runner.raise_on_device_error()
+    del runner
+    torch.cuda.empty_cache()
+    prefill_ms = sum(portions_ms)
+    flops = prefill_flops(config, layers, context)
+
+    # ---- decode at batch 32: contexts are reserved, not computed (the cache holds zeros; the
+    # kernels read and multiply them all the same)
+    runner = ModelRunner(model.model, model.runtime, page_size=page,
+                         num_pages=batch * (context // page + 1), max_requests=batch)
+    start_len = context - (steps + warmup)
+    handles = []
+    for r in range(batch):
+        handle = runner.cache.open(r)
+        runner.cache.reserve(handle, start_len)
+        runner.cache.commit(handle, start_len)
+        handles.append(handle)
+    tokens = rng.integers(0, config.vocab_size, size=(steps + warmup, batch))
+    picks = torch.empty(batch, dtype=torch.int32, device=device)
+
+    def step(index):
+        logits = runner.step([StepEntry(h, [int(tokens[index, b])], [0]) for b, h in enumerate(handles)])
+        ops.argmax(logits, picks)
+    for index in range(warmup):
+        step(index)
+    clocks = ClockSampler()
+    clocks.start()
+    ms_step = timed(lambda: [step(warmup + index) for index in range(steps)]) / steps
+    clock_record = clocks.stop()
+    runner.raise_on_device_error()
+    read_bytes = weight_bytes(config, layers) + batch * (context - steps / 2) * kv_bytes_per_token(config, layers)
+    print(json.dumps({
+        "metric": "decode tok/s @ batch 32, context 8,192; chunked prefill of 8,192 tokens (Qwen2.5-14B shape)",
+        "impl": "engine", "value": batch * 1000.0 / ms_step, "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_step, "dtype": "bf16",
+        "roofline": {"bound": "hbm", "achieved": read_bytes / (ms_step * 1e-3) / 1e9, "peak": peak["hbm_gbs"],
+                     "unit": "GB/s", "frac": read_bytes / (ms_step * 1e-3) / 1e9 / peak["hbm_gbs"],
+                     "peaks": peak_source},
+        "prefill": {"value": context * 1000.0 / prefill_ms, "tokens": context, "ms": prefill_ms,
+                    "portion_ms": [round(m, 2) for m in portions_ms],
+                    "frac": flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12)},
+        "config": {"model": "Qwen2.5-14B shape", "layers": layers, "layers_of_shape": SHAPE_14B["num_hidden_layers"],
+                   "global_batch": batch, "seq_len": context, "prefill_portion": portion, "kv_page": page},
+        "clocks": clock_record,
+        "data": "synthetic: random bf16 weights N(0,0.02), uniform random token ids; decode contexts reserved, not computed"}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -215,9 +303,10 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has")
     parser.add_argument("--prefill-tokens", type=int, default=2048)
     parser.add_argument("--points", default="1,64", help="extra decode batch sizes ('' = none)")
-    parser.add_argument("--workload", default="decode", choices=["decode", "serving"],
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long"],
                         help="decode: the default measurement; serving: continuous batching of 256 "
-                             "requests at the 1.5B shape")
+                             "requests at the 1.5B shape; long: the 14B shape, decode at batch 32 with "
+                             "8,192-token contexts and chunked prefill of an 8,192-token prompt")
     parser.add_argument("--requests", type=int, default=256)
     parser.add_argument("--step-tokens", type=int, default=2048, help="serving: token budget of one step")
     parser.add_argument("--num-blocks", type=int, default=16384)
@@ -235,6 +324,8 @@ def main() -> int:
         return 2
     if args.workload == "serving":
         return serving_workload(args)
+    if args.workload == "long":
+        return long_context_workload(args)
 
     import numpy as np
     import torch
