@@ -550,6 +550,432 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     }
 }
 
+
+// =====================================================================================
+// Decoded tokens (and portions of up to 16 rows): the keys are the M side.
+//
+// A decoded token has as many query rows as its group has heads (5-8), far too few for the
+// 128 rows of an MMA, and with mma.sync tiles the CUDA cores spend more instructions per key
+// than the memory system needs time to deliver it.  Here a tile is 128 keys x 16 rows:
+//
+//   S^T[key, row] = K_tile[128 keys, head] . Q^T         (A = the K tile, K-major, as TMA wrote it;
+//                                                         B = 16 query rows, K-major; N = 16)
+//   O^T[dim, row] += V_tile^T[128 dims, 128 keys] . P^T  (A = the V tile as it lies, [key][dim] =
+//                                                         MN-major; B = P^T [row][key], K-major)
+//
+// so every byte of K and V is read from shared memory once by the tensor core, and the 128
+// softmax threads hold one key each: 16 scores per thread and tile.  The maximum of a row over
+// the keys of a tile is found with a warp reduction and a shared atomic per row; the row sums
+// stay per thread until the end.  As in the kernel above the reference point of a row's
+// exponentials moves only when its maximum has grown by more than 2^8.
+//
+//   producer warp   TMA, K and V tiles take turns in a ring of DSLOTS slots
+//   MMA warp        scores of tile i + 1 (second S buffer) are issued before P V of tile i
+//   4 softmax warps thread t = key t of the tile = tensor-memory lane t; at the end lane t holds
+//                   dimension t of the 16 outputs
+#if HEAD_DIM == 128
+namespace dec {
+
+#ifndef FSIE_TCD_SLOTS
+#define FSIE_TCD_SLOTS 3
+#endif
+constexpr int KEYS = 128;               // keys per tile
+constexpr int ROWS = 16;                // query rows per tile
+constexpr int DSLOTS = FSIE_TCD_SLOTS;  // ring of K / V tiles; with 3 two blocks fit on an SM
+constexpr int DTHREADS = 64 + 128;
+constexpr int QP_ATOM = ROWS * 128;     // 16 rows x 128 bytes of a K-major operand with N = 16
+constexpr int DQ_BYTES = HALVES * QP_ATOM;
+constexpr int DP_BYTES = (KEYS / 64) * QP_ATOM;
+constexpr int DTILE_BYTES = DQ_BYTES + DP_BYTES + DSLOTS * KV_BYTES;
+struct DControl {
+    uint64_t ring_full[DSLOTS], ring_empty[DSLOTS], s_full[2], p_ready, pv_done, q_ready;
+    uint32_t tmem_slot;
+    int abort_flag;
+    int row_max[1][ROWS];               // a tile's row maxima (as ordered integers), when reference points move
+    float row_sum[4][ROWS];             // the softmax warps' sums at the end
+};
+static_assert(sizeof(DControl) <= 1024, "control block");
+constexpr int DSMEM_BYTES = 1024 + DTILE_BYTES;
+constexpr uint32_t DTMEM_COLS = 64;     // S (tile parity 0) | S (parity 1) | O, 16 columns each
+constexpr uint32_t DCOL_O = 32;
+enum { ERR_TCD_PRODUCER = 35, ERR_TCD_MMA = 36, ERR_TCD_SOFTMAX = 37, ERR_TCD_LAYOUT = 38 };
+
+// floats as integers of the same order (for atomicMax / redux)
+__device__ __forceinline__ int ordered(float f) { const int i = __float_as_int(f); return i >= 0 ? i : i ^ 0x7fffffff; }
+__device__ __forceinline__ float unordered(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
+
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16_issue(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
+// all 128 softmax threads meet; returns whether any of them brought `flag`
+__device__ __forceinline__ bool softmax_meet(bool flag) {
+    uint32_t any;
+    asm volatile("{\n .reg .pred pin, pout;\n setp.ne.u32 pin, %1, 0;\n bar.red.or.pred pout, 1, 128, pin;\n selp.u32 %0, 1, 0, pout;\n}\n"
+                 : "=r"(any) : "r"((uint32_t)flag) : "memory");
+    return any != 0;
+}
+
+__global__ void __launch_bounds__(DTHREADS, DSLOTS <= 3 ? 2 : 1)
+attn_tc_decode_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p, const TcExtra x) {
+    extern __shared__ __align__(1024) unsigned char smem_all[];
+    DControl& ctl = *reinterpret_cast<DControl*>(smem_all);
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_all) + sizeof(DControl) + 1023) & ~uintptr_t(1023));
+    if (smem + DTILE_BYTES > smem_all + DSMEM_BYTES) {       // the window does not start on a 1,024-byte boundary
+        if (threadIdx.x == 0) atomicExch(x.error, ERR_TCD_LAYOUT);
+        return;
+    }
+    unsigned char* q_s = smem;                               // [HALVES][16 rows][128 B]
+    unsigned char* p_s = q_s + DQ_BYTES;                     // [2 halves of the keys][16 rows][128 B]
+    unsigned char* ring = p_s + DP_BYTES;                    // [slot][HALVES][128 keys][128 B]
+    int& abort_flag = ctl.abort_flag;
+#ifdef FSIE_TC_TIMING
+    const long long block_begin_ = clock64();
+#endif
+
+    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
+    const int group = p.heads / p.kv_heads;
+    const int item = p.tile_item[tile];
+    const int row0 = p.tile_row0[tile];
+    const int qstart = p.item_qstart[item], qlen = p.item_qlen[item], pos0 = p.item_pos0[item];
+    const int nrows = min(ROWS, qlen * group - row0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bf16* q = (const bf16*)p.q;
+    const int* bt = p.block_tables + (size_t)item * p.bt_stride;
+
+    const int pos_first = pos0 + row0 / group;
+    const int pos_last = pos0 + (row0 + nrows - 1) / group;
+    int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int kend = pos_last + 1;
+    if (p.nsplit > 1) {
+        const int span = kend - kbegin;
+        int chunk = (span + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + KEYS - 1) / KEYS) * KEYS;
+        const int b = kbegin + split * chunk;
+        kend = min(kend, b + chunk);
+        kbegin = b;
+    }
+    kbegin = kbegin / KEYS * KEYS;      // tiles hold whole pages; keys before the window are masked
+    const int ntiles = kend > kbegin ? (kend - kbegin + KEYS - 1) / KEYS : 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < DSLOTS; ++s) { mbar_init(&ctl.ring_full[s], 1); mbar_init(&ctl.ring_empty[s], 1); }
+        mbar_init(&ctl.s_full[0], 1); mbar_init(&ctl.s_full[1], 1);
+        mbar_init(&ctl.p_ready, 128); mbar_init(&ctl.pv_done, 1); mbar_init(&ctl.q_ready, 128);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid == 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&pages_map) : "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&ctl.tmem_slot)), "r"(DTMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = ctl.tmem_slot;
+    grid_dependents_go();
+    // Under programmatic dependent launch the kernel before this one, which writes this step's
+    // queries, keys and values, may still be running.  The lists and block tables were staged
+    // before the step, and keys older than every new token of the request were written by earlier
+    // steps: the producer fetches tiles of only such keys at once and waits before the first tile
+    // with new ones; everyone else waits here.
+    if (warp != 0) grid_dependency_wait();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        // ring entry 2 i is K of tile i, entry 2 i + 1 its V; lane j fetches page j of the tile
+        const int ps = p.page_size, pages_per_tile = KEYS / ps;
+        const long long rows_per_page = (long long)x.entries * 2 * p.kv_heads * ps;
+        const long long k_row0 = ((long long)x.entry * 2) * p.kv_heads * ps + (long long)kvh * ps;
+        const long long v_row0 = k_row0 + (long long)p.kv_heads * ps;
+        bool waited = false;
+        // every part of a tile is fetched (finite operands): beyond the last key, or where a window
+        // has given pages back, the page of the last key stands in; those keys are masked.  The
+        // table entries of a tile are read one tile ahead of their use.
+        const int last_page = ntiles > 0 ? bt[(kend - 1) / ps] : -1;
+        auto look_up = [&](int i) {
+            const int key = kbegin + i * KEYS + lane * ps;
+            return (lane < pages_per_tile && i < ntiles && key < kend) ? bt[key / ps] : -1;
+        };
+        int page_ahead = look_up(0);
+        for (int i = 0; i < ntiles; ++i) {
+            if (!waited && kbegin + (i + 1) * KEYS > pos0) { grid_dependency_wait(); waited = true; }
+            int page = page_ahead;
+            page_ahead = look_up(i + 1);
+            if (lane < pages_per_tile && page < 0) page = last_page;
+            const int wanted = __popc(__ballot_sync(0xffffffffu, page >= 0));
+            bool ok = true;
+#pragma unroll
+            for (int kv = 0; kv < 2 && ok; ++kv) {
+                const int e = 2 * i + kv, s = e % DSLOTS;
+                if (lane == 0 && e >= DSLOTS) ok = mbar_wait(&ctl.ring_empty[s], ((e / DSLOTS) - 1) & 1);
+                ok = __shfl_sync(0xffffffffu, ok, 0) && !*(volatile int*)&abort_flag;
+                if (!ok) break;
+                if (lane == 0) mbar_expect_tx(&ctl.ring_full[s], (uint32_t)wanted * ps * HD * 2);
+                __syncwarp();
+                if (page >= 0) {
+                    unsigned char* dst = ring + (size_t)s * KV_BYTES + lane * ps * 128;
+                    const long long row = (long long)page * rows_per_page + (kv ? v_row0 : k_row0);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * ATOM_BYTES, &pages_map, h * 64, (int)row, &ctl.ring_full[s]);
+                }
+            }
+            if (!ok) {
+                if (lane == 0) { atomicExch(x.error, ERR_TCD_PRODUCER); atomicExch(&abort_flag, 1); }
+                break;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && ntiles > 0) {
+            const uint32_t idesc_s = idesc_bf16(KEYS, ROWS, 0);                  // A = K tile, B = Q: both K-major
+            const uint32_t idesc_o = idesc_bf16(HD, ROWS, 0) | (1u << 15);       // A = V tile, MN-major
+            bool ok = true;
+            auto give_up = [&]() { atomicExch(x.error, ERR_TCD_MMA); atomicExch(&abort_flag, 1); ok = false; };
+            auto ring_wait = [&](int e) {
+                if (!mbar_wait(&ctl.ring_full[e % DSLOTS], (e / DSLOTS) & 1)) give_up();
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            };
+            const uint64_t q_base = desc_k_major(q_s), p_base = desc_k_major(p_s);
+            const uint64_t k_base = desc_k_major(ring), v_base = desc_mn_major(ring, ATOM_BYTES);
+            auto scores = [&](int i) {               // S^T (parity of i) = K_i Q^T
+                const uint64_t kd = k_base + (uint64_t)(((2 * i) % DSLOTS) * (KV_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k)    // 16 elements along the head per instruction
+                    mma_ss(tmem + (i & 1) * ROWS, kd + (uint64_t)((k >> 2) * (ATOM_BYTES >> 4) + 2 * (k & 3)),
+                           q_base + (uint64_t)((k >> 2) * (QP_ATOM >> 4) + 2 * (k & 3)), idesc_s, k > 0);
+                mma_commit(&ctl.s_full[i & 1]);
+                mma_commit(&ctl.ring_empty[(2 * i) % DSLOTS]);                   // K_i may be overwritten
+            };
+            if (!mbar_wait(&ctl.q_ready, 0)) give_up();
+            if (ok) ring_wait(0);
+            if (ok) scores(0);
+            for (int i = 0; i < ntiles && ok; ++i) {
+                if (i + 1 < ntiles) {                // the next scores, while the softmax works on these
+                    ring_wait(2 * i + 2);
+                    if (!ok) break;
+                    scores(i + 1);
+                }
+                if (!mbar_wait(&ctl.p_ready, i & 1)) { give_up(); break; }
+                ring_wait(2 * i + 1);
+                if (!ok) break;
+                const uint64_t vd = v_base + (uint64_t)(((2 * i + 1) % DSLOTS) * (KV_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < KEYS / 16; ++k)  // 16 keys per instruction: 16 rows of 128 bytes of V
+                    mma_ss(tmem + DCOL_O, vd + (uint64_t)(k * (16 * 128 >> 4)),
+                           p_base + (uint64_t)((k >> 2) * (QP_ATOM >> 4) + 2 * (k & 3)), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                mma_commit(&ctl.pv_done);
+                mma_commit(&ctl.ring_empty[(2 * i + 1) % DSLOTS]);               // V_i may be overwritten
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax: one key per thread
+        const int quarter = warp & 3;
+        const int t = quarter * 32 + lane;                  // key of the tile = tensor-memory lane
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        // the query rows, K-major and swizzled (rows beyond the tile's count are zero)
+#pragma unroll
+        for (int j = 0; j < ROWS * (HD / 8) / 128; ++j) {
+            const int e = t + j * 128;
+            const int r = e / (HD / 8), c = e - r * (HD / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < nrows) {
+                const int row = row0 + r;
+                const int tok = qstart + row / group, h = kvh * group + row % group;
+                v = *reinterpret_cast<const uint4*>(q + (size_t)tok * p.q_ld + h * HD + c * 8);
+            }
+            *reinterpret_cast<uint4*>(q_s + (c >> 3) * QP_ATOM + swizzled(r, c & 7)) = v;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&ctl.q_ready);
+
+        int pos[ROWS], low[ROWS];
+        int pos_min = 0x7fffffff, low_max = -1;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            pos[r] = r < nrows ? pos0 + (row0 + r) / group : -1;
+            low[r] = p.window > 0 ? pos[r] - p.window : -1;      // keys <= this are unseen
+            if (r < nrows) { pos_min = min(pos_min, pos[r]); low_max = max(low_max, low[r]); }
+        }
+        const float sc = p.scale * 1.4426950408889634f;
+        // base[r]: the reference point of row r's exponentials in base-2 units (-inf: none yet)
+        float base[ROWS], l_run[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) { base[r] = -INFINITY; l_run[r] = 0.f; }
+        // where P^T [row][key] takes this thread's key: 2 bytes in each row's 128-byte line
+        unsigned char* p_mine = p_s + (t >> 6) * QP_ATOM + (t & 7) * 2;
+        const int p_chunk = (t & 63) >> 3;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)          // rows beyond the tile's count stay zero
+            if (r >= nrows) *reinterpret_cast<bf16*>(p_mine + r * 128 + ((p_chunk ^ (r & 7)) << 4)) = __float2bfloat16_rn(0.f);
+        bool fail = false, left = false;
+#ifdef FSIE_TC_TIMING
+        unsigned phase_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const long long loop_begin_ = clock64();
+        long long mark_ = loop_begin_;
+#endif
+        for (int i = 0; i < ntiles; ++i) {
+            if (!mbar_wait(&ctl.s_full[i & 1], (i >> 1) & 1)) fail = true;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            TC_MARK(0);
+            uint32_t sr[ROWS];
+            tmem_ld16_issue(lane_base + (i & 1) * ROWS, sr);
+            tmem_wait_ld();
+            TC_MARK(1);
+            const int k0 = kbegin + i * KEYS, key = k0 + t;
+            const bool clear = k0 + KEYS - 1 < kend && k0 + KEYS - 1 <= pos_min && k0 > low_max;   // nothing to mask
+            // Exponent of every score against its row's reference point.  The point moves only when
+            // some score lies more than 2^8 above it (or the row has none yet): p may exceed 1 by
+            // at most 256x, exact enough in float and bfloat16, and in almost every tile nobody
+            // needs the row maxima, O and the row sums need no rescaling, and the 128 threads
+            // exchange one bit.
+            float arg[ROWS];
+            bool exceeds = false;
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (r < nrows) {
+                    if (!clear && !(key < kend && key <= pos[r] && key > low[r])) sr[r] = 0xff800000u;   // -inf
+                    arg[r] = fmaf(__uint_as_float(sr[r]), sc, -base[r]);     // no reference yet: +inf (NaN for an unseen key)
+                    exceeds = exceeds || arg[r] > 8.f;
+                }
+            }
+            bool rescale = false;
+            float corr[ROWS];
+            if (softmax_meet(exceeds || fail || *(volatile int*)&abort_flag)) {
+                // ---- rare: some row's reference point moves (always in a row's first tile)
+                if (t < ROWS) ctl.row_max[0][t] = ordered(-INFINITY);
+                if (softmax_meet(fail || *(volatile int*)&abort_flag)) { left = true; break; }
+                int mine = ordered(-INFINITY);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) {
+                    if (r < nrows) {
+                        const int best = __reduce_max_sync(0xffffffffu, ordered(__uint_as_float(sr[r])));
+                        if (lane == r) mine = best;
+                    }
+                }
+                if (lane < nrows) atomicMax(&ctl.row_max[0][lane], mine);    // lane r carries row r
+                softmax_meet(false);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) {
+                    corr[r] = 1.f;
+                    if (r < nrows) {
+                        const float top = unordered(ctl.row_max[0][r]) * sc;    // the tile's maximum, base-2 units
+                        if (top != -INFINITY && (base[r] == -INFINITY || top - base[r] > 8.f)) {
+                            if (base[r] == -INFINITY) corr[r] = 0.f;
+                            else { corr[r] = fast_exp2(base[r] - top); rescale = true; }
+                            base[r] = top;
+                            l_run[r] *= corr[r];
+                        }
+                        arg[r] = fmaf(__uint_as_float(sr[r]), sc, -base[r]);
+                    }
+                }
+            }
+            TC_MARK(2);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (r < nrows) {
+                    // a key that the row does not see has score -inf: arg is -inf, or NaN while the
+                    // row has no reference point yet; both count as 0
+                    const float pr = arg[r] == arg[r] ? fast_exp2(arg[r]) : 0.f;
+                    l_run[r] += pr;
+                    sr[r] = __float_as_uint(pr);
+                }
+            }
+            TC_MARK(4);
+            // P^T and O belong to the tensor core until P V of the tile before has completed
+            if (i > 0 && !mbar_wait(&ctl.pv_done, (i - 1) & 1)) fail = true;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            TC_MARK(3);
+            if (rescale) {                                   // the same decision in every thread
+                uint32_t orr[ROWS];
+                tmem_ld16_issue(lane_base + DCOL_O, orr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) orr[r] = __float_as_uint(__uint_as_float(orr[r]) * corr[r]);
+                tmem_st16_issue(lane_base + DCOL_O, orr);
+                tmem_wait_st();
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (r < nrows)
+                    *reinterpret_cast<bf16*>(p_mine + r * 128 + ((p_chunk ^ (r & 7)) << 4)) = __float2bfloat16_rn(__uint_as_float(sr[r]));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P^T before the tensor core reads it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            TC_MARK(4);
+            mbar_arrive(&ctl.p_ready);
+            TC_MARK(5);
+        }
+#ifdef FSIE_TC_TIMING
+        const long long loop_end_ = clock64();
+#endif
+        // ---- the last P V, the row sums, then dimension t of every row
+        bool have = !left && !fail && ntiles > 0;
+        if (have && !mbar_wait(&ctl.pv_done, (ntiles - 1) & 1)) have = false;
+        have = __all_sync(0xffffffffu, have);
+        if (!have && ntiles > 0 && lane == 0) { atomicExch(x.error, ERR_TCD_SOFTMAX); atomicExch(&abort_flag, 1); }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (r < nrows) {
+                const float s = warp_sum(l_run[r]);
+                if (lane == 0) ctl.row_sum[quarter][r] = s;
+            }
+        }
+        softmax_meet(false);
+        uint32_t orr[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) orr[r] = 0u;
+        if (have) { tmem_ld16_issue(lane_base + DCOL_O, orr); tmem_wait_ld(); }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (r < nrows) {
+                const float l = (ctl.row_sum[0][r] + ctl.row_sum[1][r]) + (ctl.row_sum[2][r] + ctl.row_sum[3][r]);
+                const int row = row0 + r;
+                const int tok = qstart + row / group, h = kvh * group + row % group;
+                if (p.nsplit == 1) {
+                    const float inv = l > 0.f ? 1.0f / l : 0.f;
+                    ((bf16*)p.out)[(size_t)tok * p.out_ld + h * HD + t] = __float2bfloat16_rn(__uint_as_float(orr[r]) * inv);
+                } else {
+                    const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
+                    p.part_o[idx * HD + t] = __uint_as_float(orr[r]);
+                    if (t == 0) {
+                        p.part_ml[idx * 2] = base[r] * 0.6931471805599453f;      // natural units; -inf stays -inf
+                        p.part_ml[idx * 2 + 1] = l;
+                    }
+                }
+            }
+        }
+#ifdef FSIE_TC_TIMING
+        if (warp == 2 && lane == 0) {
+            for (int k = 0; k < 6; ++k) atomicAdd(&fsie_tc_timing[k], (unsigned long long)phase_[k]);
+            atomicAdd(&fsie_tc_timing[6], (unsigned long long)ntiles);
+            atomicAdd(&fsie_tc_timing[7], (unsigned long long)(loop_begin_ - block_begin_));
+            atomicAdd(&fsie_tc_timing[8], (unsigned long long)(clock64() - loop_end_));
+        }
+#endif
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(DTMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace dec
+#endif  // HEAD_DIM == 128
+
 }  // namespace fsie
 
 using namespace fsie;
@@ -635,5 +1061,59 @@ int fsie_attn_tc(const void* pages_map, int entries, int entry, const void* q, i
         part_o, part_ml, (bf16*)out, out_ld, tokens, heads, nsplit, combine_tokens);
     return (int)cudaGetLastError();
 }
+
+// Tiles of up to 16 query rows (decoded tokens, two-token portions): attn_tc_decode_kernel.
+// Arguments as fsie_attn_tc; head size 128 only (a library built for another head size refuses).
+#if HEAD_DIM == 128
+int fsie_attn_tc_decode_rows() { return dec::ROWS; }
+int fsie_attn_tc_decode(const void* pages_map, int entries, int entry, const void* q, int q_ld, int page_size,
+                        const int* block_tables, int bt_stride, const int* tile_item, const int* tile_row0, int tiles,
+                        const int* item_qstart, const int* item_qlen, const int* item_pos0, void* out, int out_ld,
+                        float* part_o, float* part_ml, int tokens, int heads, int kv_heads, int head_dim, int window,
+                        int nsplit, float scale, const int* combine_tokens, int num_combine, int* error,
+                        cudaStream_t stream) {
+    if (tiles <= 0 || tokens <= 0) return 0;
+    if (head_dim != HD || tiles > 65535) return ERR_UNSUPPORTED;     // tiles are the grid's y dimension
+    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return ERR_UNSUPPORTED;
+    if (kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 || nsplit > 32 || (q_ld % 8) != 0 ||
+        entries <= 0 || entry < 0 || entry >= entries || !error)
+        return ERR_BAD_ARGUMENT;
+    if (nsplit > 1 && (!part_o || !part_ml)) return ERR_BAD_ARGUMENT;
+    CUtensorMap map;
+    memcpy(&map, pages_map, sizeof(map));
+    AttnParams p;
+    p.q = q; p.q_ld = q_ld; p.k_pages = nullptr; p.v_pages = nullptr;
+    p.page_stride = 0; p.page_size = page_size;
+    p.block_tables = block_tables; p.bt_stride = bt_stride;
+    p.tile_item = tile_item; p.tile_row0 = tile_row0;
+    p.item_qstart = item_qstart; p.item_qlen = item_qlen; p.item_pos0 = item_pos0;
+    p.out = out; p.out_ld = out_ld; p.part_o = part_o; p.part_ml = part_ml;
+    p.tokens = tokens; p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
+    p.window = window; p.nsplit = nsplit; p.scale = scale;
+    TcExtra x;
+    x.entries = entries; x.entry = entry; x.error = error;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(dec::attn_tc_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dec::DSMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    int rc = launch_dependent(dec::attn_tc_decode_kernel, dim3(kv_heads, tiles, nsplit), dim3(dec::DTHREADS),
+                              (size_t)dec::DSMEM_BYTES, stream, map, p, x);
+    if (rc != 0 || nsplit == 1) return rc;
+    const int count = combine_tokens ? num_combine : tokens;
+    if (count <= 0) return 0;
+    return launch_dependent(attn_combine_kernel, dim3(count, heads), dim3(HD >= 128 ? 64 : 32), 0, stream,
+                            (const float*)part_o, (const float*)part_ml, (bf16*)out, out_ld, tokens, heads, nsplit,
+                            combine_tokens);
+}
+#else
+int fsie_attn_tc_decode_rows() { return 0; }
+int fsie_attn_tc_decode(const void*, int, int, const void*, int, int, const int*, int, const int*, const int*, int,
+                        const int*, const int*, const int*, void*, int, float*, float*, int, int, int, int, int, int,
+                        float, const int*, int, int*, cudaStream_t) {
+    return ERR_UNSUPPORTED;
+}
+#endif
 
 }  // extern "C"

@@ -293,5 +293,14 @@ class ModelRunner:
                     21: "tiled matrix product: the copy engine's stage never became free",
                     22: "tiled matrix product: a stage never arrived",
                     23: "tiled matrix product: the accumulator was never read out",
-                    24: "tiled matrix product: the accumulator never completed"}
+                    24: "tiled matrix product: the accumulator never completed",
+                    31: "tcgen05 attention: the copy engine's slot never became free",
+                    32: "tcgen05 attention: a tile or the softmax never arrived",
+                    33: "tcgen05 attention: scores or outputs never completed",
+                    34: "tcgen05 attention: shared memory does not start on a 1,024-byte boundary",
+                    35: "tcgen05 decode attention: the copy engine's slot never became free",
+                    36: "tcgen05 decode attention: a tile or the softmax never arrived",
+                    37: "tcgen05 decode attention: scores or outputs never completed",
+                    38: "tcgen05 decode attention: shared memory does not start on a 1,024-byte "
+                        "boundary"}
             raise DeviceFault(what.get(code, f"device error flag {code}"))

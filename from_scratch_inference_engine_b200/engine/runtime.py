@@ -36,7 +36,8 @@ class Runtime:
 
     def __init__(self, device="cuda:0", dtype=torch.bfloat16, max_positions: int = 0,
                  few_token_min_elements: int = 32 * 1024 * 1024, products: str = "own",
-                 tiled_min_tiles: Optional[int] = None):
+                 tiled_min_tiles: Optional[int] = None,
+                 decode_tcgen05_min_blocks: Optional[int] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this engine has no CPU path")
         self.device = torch.device(device)
@@ -64,6 +65,10 @@ class Runtime:
         # matrices that may take the tiled product: storage address -> (weight, swiglu) until a step
         # qualifies, then its descriptor (made, and the kernel library compiled, only then)
         self._tiled_weights: Dict[int, object] = {}
+        # decoded tokens take the tcgen05 attention kernel when their (request, kv head) pairs
+        # number at least this many (None: one per SM; below that the mma.sync kernel is ahead)
+        self.decode_tcgen05_min_blocks = (self.sm_count if decode_tcgen05_min_blocks is None
+                                          else int(decode_tcgen05_min_blocks))
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 

@@ -122,12 +122,17 @@ def run_attention(args, timer, decode: bool):
 
     use_tma = args.variant == "tma" and row_class >= 0
     use_tc = args.variant == "tc" and row_class == 2
-    if use_tma or use_tc:
-        pages_map = ops.PagesMap(pages, "tc" if use_tc else "tma")
+    use_tcd = args.variant == "tc" and row_class == 0 and hd in ops.ATTENTION_TC_DECODE_HEAD_DIMS
+    if use_tma or use_tc or use_tcd:
+        pages_map = ops.PagesMap(pages, "tc" if use_tc or use_tcd else "tma")
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def launch():
-        if use_tc:
+        if use_tcd:
+            ops.attention_tc_decode(pages_map, 0, q, q.stride(0), tables, tile_item, tile_row0,
+                                    tile_item.numel(), qstart, qlen, pos0, out, tokens, heads,
+                                    kv_heads, 0, scale, error, nsplit, part_o, part_ml, None, 0)
+        elif use_tc:
             ops.attention_tc(pages_map, 0, q, q.stride(0), tables, tile_item, tile_row0,
                              tile_item.numel(), qstart, qlen, pos0, out, tokens, heads, kv_heads,
                              0, scale, error, nsplit, part_o, part_ml, None, 0)
@@ -147,7 +152,7 @@ def run_attention(args, timer, decode: bool):
                                   part_o, part_ml)
     ms = timer(launch)
     extra = {}
-    if use_tc and any("FSIE_TC_TIMING" in d for d in args.build_defines):
+    if (use_tc or use_tcd) and any("FSIE_TC_TIMING" in d for d in args.build_defines):
         # cycles per key tile that one warp spent in each phase, summed over all blocks by the kernel
         import ctypes
         lib = ops.attn_tc(hd)
@@ -169,8 +174,11 @@ def run_attention(args, timer, decode: bool):
     # causal: query t of a portion sees past + t + 1 keys
     pairs = args.batch * (new * past + new * (new + 1) / 2)
     flops = 4.0 * heads * hd * pairs
+    if use_tma or use_tc or use_tcd:
+        extra["error"] = int(error.item())
     extra.update({"nsplit": nsplit, "tiles": tile_item.numel(),
-                  "variant": ("tc" if use_tc else "tma" if use_tma else "mma") if row_class >= 0 else "generic"})
+                  "variant": ("tc" if use_tc else "tc_decode" if use_tcd else "tma" if use_tma else "mma")
+                  if row_class >= 0 else "generic"})
     return ms, io_bytes, flops, extra
 
 
@@ -310,7 +318,8 @@ def main(argv=None) -> int:
     if args.build_defines:
         # the measurement build replaces the library of the kernel under test for this process
         from ..csrc import build
-        target = {"attention_prefill": "attn_tc", "attention_decode": "attn_mma"}.get(
+        target = {"attention_prefill": "attn_tc",
+                  "attention_decode": "attn_tc" if args.variant == "tc" else "attn_mma"}.get(
             args.kernel, "gemm_tiles" if args.kernel.startswith("gemm_tiles") else None)
         if target is None:
             raise SystemExit("--build-defines: no measurement build for this kernel")

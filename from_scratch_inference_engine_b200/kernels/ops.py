@@ -347,6 +347,7 @@ _attn_tc = {}
 ATTENTION_TC_PAGES = (8, 16, 32, 64, 128)
 ATTENTION_TC_HEAD_DIMS = (64, 128)
 ATTENTION_TC_ROWS = 256
+ATTENTION_TC_DECODE_HEAD_DIMS = (128,)      # tiles of up to 16 rows: attention_tc_decode
 
 
 def attn_tc(head_dim: int):
@@ -360,7 +361,10 @@ def attn_tc(head_dim: int):
         lib.fsie_attn_tc_pages_map.argtypes = [p, p, ll, i, i]
         lib.fsie_attn_tc.argtypes = [p, i, i, p, i, i, p, i, p, p, i, p, p, p, p, i, p, p,
                                      i, i, i, i, i, i, f, p, i, p, p]
-        for name in ("fsie_attn_tc_map_bytes", "fsie_attn_tc_pages_map", "fsie_attn_tc"):
+        lib.fsie_attn_tc_decode.argtypes = lib.fsie_attn_tc.argtypes
+        lib.fsie_attn_tc_decode_rows.argtypes = []
+        for name in ("fsie_attn_tc_map_bytes", "fsie_attn_tc_pages_map", "fsie_attn_tc",
+                     "fsie_attn_tc_decode", "fsie_attn_tc_decode_rows"):
             getattr(lib, name).restype = i
         _attn_tc[head_dim] = lib
     return _attn_tc[head_dim]
@@ -417,6 +421,43 @@ def attention_tc(pages_map: PagesMap, entry: int, q: torch.Tensor, q_ld: int,
         _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0), _ptr(out), out.stride(0),
         _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, head_dim, window, nsplit,
         float(scale), _ptr(combine_tokens), num_combine, _ptr(error), _stream()), "attention_tc")
+    return out
+
+
+def attention_tc_decode(pages_map: PagesMap, entry: int, q: torch.Tensor, q_ld: int,
+                        block_tables: torch.Tensor, tile_item: torch.Tensor,
+                        tile_row0: torch.Tensor, num_tiles: int, item_qstart: torch.Tensor,
+                        item_qlen: torch.Tensor, item_pos0: torch.Tensor, out: torch.Tensor,
+                        tokens: int, heads: int, kv_heads: int, window: int, scale: float,
+                        error: torch.Tensor, nsplit: int = 1,
+                        part_o: Optional[torch.Tensor] = None,
+                        part_ml: Optional[torch.Tensor] = None,
+                        combine_tokens: Optional[torch.Tensor] = None, num_combine: int = 0
+                        ) -> torch.Tensor:
+    """bfloat16 attention of decoded tokens (tiles of up to 16 query rows, head size 128) with
+    tcgen05.mma: the keys of a tile are the M side."""
+    for name, t in (("block_tables", block_tables), ("tile_item", tile_item),
+                    ("tile_row0", tile_row0), ("item_qstart", item_qstart),
+                    ("item_qlen", item_qlen), ("item_pos0", item_pos0), ("error", error)):
+        _need(t, torch.int32, name)
+    _need(q, torch.bfloat16, "q", contiguous=False)
+    _need(out, torch.bfloat16, "out")
+    head_dim = pages_map.head_dim
+    if head_dim not in ATTENTION_TC_DECODE_HEAD_DIMS:
+        raise KernelError(f"attention_tc_decode takes head size 128, not {head_dim}")
+    if nsplit > 1:
+        _need(part_o, torch.float32, "part_o")
+        _need(part_ml, torch.float32, "part_ml")
+        if part_o.numel() < nsplit * tokens * heads * head_dim or \
+                part_ml.numel() < nsplit * tokens * heads * 2:
+            raise KernelError("attention_tc_decode: split scratch is too small")
+    _check(attn_tc(head_dim).fsie_attn_tc_decode(
+        pages_map.ptr, pages_map.entries, entry, _ptr(q), q_ld, pages_map.page_size,
+        _ptr(block_tables), block_tables.stride(0), _ptr(tile_item), _ptr(tile_row0), num_tiles,
+        _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0), _ptr(out), out.stride(0),
+        _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, head_dim, window, nsplit,
+        float(scale), _ptr(combine_tokens), num_combine, _ptr(error), _stream()),
+        "attention_tc_decode")
     return out
 
 

@@ -15,12 +15,15 @@ from .base import LayerCache, Mixer, build_part, register_part
 
 
 def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
-                     blocks_per_sm: int = 2) -> int:
+                     blocks_per_sm: int = 2, decode_slots: int = 3, decode_fixed: int = 270
+                     ) -> int:
     """Into how many key ranges to split each tile (at most 32, each at least 128 keys).
 
     Tiles of decoded tokens all have the same work, so the time is waves x (fixed cost of a
-    block + keys per range); measured at batch 64 and context 4,096 the fixed cost equals
-    about 270 keys and three blocks fit on an SM.  Tiles of a prompt have uneven work and
+    block + keys per range); measured at batch 64 and context 4,096 the fixed cost of the
+    mma.sync kernel equals about 270 keys and three blocks fit on an SM (the tcgen05 kernel
+    for decoded tokens: 530 keys, two blocks: `decode_fixed`, `decode_slots`).  Tiles of a
+    prompt have uneven work and
     are split only when there are fewer of them than block slots (`blocks_per_sm` per SM;
     the tcgen05 kernel has one, and its partial results cost more than a little idling, so
     it splits only to fill slots that would stay empty)."""
@@ -30,10 +33,10 @@ def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
             return 1
         wanted = slots // blocks if blocks_per_sm == 1 else -(-slots // blocks)
         return max(1, min(wanted, longest // 128, 32))
-    slots = 3 * sms
+    slots = decode_slots * sms
     best, best_cost = 1, None
     for n in range(1, max(1, min(32, longest // 128)) + 1):
-        cost = -(-blocks * n // slots) * (270 + longest / n)
+        cost = -(-blocks * n // slots) * (decode_fixed + longest / n)
         if best_cost is None or cost < best_cost * 0.98:
             best, best_cost = n, cost
     return best
@@ -134,12 +137,31 @@ class GqaAttention(Mixer):
             for row_class, tiles, class_tokens, count, longest in \
                     ctx.attention_row_classes(group_size, class_rows):
                 on_tcgen05 = pages_map is not None and row_class == len(class_rows) - 1
-                nsplit = splits(tiles.count * self.num_kv_heads, longest, row_class == 0,
-                                1 if on_tcgen05 else 2)
+                # decoded tokens: with at least a block per SM before any split the tcgen05 kernel
+                # (a tile's keys as the M side) is ahead of the mma.sync one, below that behind
+                decode_tcgen05 = (pages_map is not None and row_class == 0
+                                  and self.head_dim in ops.ATTENTION_TC_DECODE_HEAD_DIMS
+                                  and tiles.count * self.num_kv_heads
+                                  >= ctx.runtime.decode_tcgen05_min_blocks)
+                if decode_tcgen05:
+                    nsplit = attention_splits(tiles.count * self.num_kv_heads, longest, sms, True,
+                                              decode_slots=2, decode_fixed=530)
+                else:
+                    nsplit = splits(tiles.count * self.num_kv_heads, longest, row_class == 0,
+                                    1 if on_tcgen05 else 2)
                 part_o = part_ml = None
                 if nsplit > 1:
                     part_o = ctx.scratch("attention.part_o", nsplit * tokens * self.q_width)
                     part_ml = ctx.scratch("attention.part_ml", nsplit * tokens * self.num_heads * 2)
+                if decode_tcgen05:
+                    ops.attention_tc_decode(pages_map, cache.entry_index, qkv, qkv.stride(0),
+                                            group.block_tables, tiles.item, tiles.row0,
+                                            tiles.count, ctx.item_qstart, ctx.item_qlen,
+                                            ctx.item_pos0, out, tokens, self.num_heads,
+                                            self.num_kv_heads, self.window, self.scale,
+                                            ctx.error, nsplit, part_o, part_ml, class_tokens,
+                                            count)
+                    continue
                 if on_tcgen05:
                     ops.attention_tc(pages_map, cache.entry_index, qkv, qkv.stride(0),
                                      group.block_tables, tiles.item, tiles.row0, tiles.count,

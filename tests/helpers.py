@@ -53,6 +53,13 @@ TINY = {
                           vocab_size=300, rope_theta=10000.0, rms_norm_eps=1e-6,
                           tie_word_embeddings=False, max_position_embeddings=1024),
               seed=5, std=0.05),
+    # head size 128, group of 3: decoded tokens can take the tcgen05 attention kernel too
+    "F": dict(config=dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2",
+                          num_hidden_layers=2, hidden_size=192, num_attention_heads=6,
+                          num_key_value_heads=2, head_dim=128, intermediate_size=256,
+                          vocab_size=300, rope_theta=100000.0, rms_norm_eps=1e-6,
+                          tie_word_embeddings=False, max_position_embeddings=1024),
+              seed=6, std=0.05),
 }
 
 

@@ -228,7 +228,7 @@ class PagedCase:
         return out.cpu().double()
 
 
-    def run_mma(self, ops, nsplit=1, tma=False, tc=False):
+    def run_mma(self, ops, nsplit=1, tma=False, tc=False, tc_decode=False):
         """The tensor-core kernels: requests sorted into row classes as the engine does."""
         group = self.heads // self.kv_heads
         i32 = lambda v: dev(torch.tensor(v, dtype=torch.int32))
@@ -267,6 +267,17 @@ class PagedCase:
                                  out, tokens, self.heads, self.kv_heads, self.window,
                                  1.0 / math.sqrt(self.hd), error, nsplit, part_o, part_ml,
                                  i32(toks), len(toks))
+                assert error.item() == 0
+                continue
+            if tc_decode and c == 0:
+                error = torch.zeros(1, dtype=torch.int32, device="cuda")
+                ops.attention_tc_decode(ops.PagesMap(pages, "tc"), 0, q, q.stride(0),
+                                        dev(self.tables), i32(tile_item), i32(tile_row0),
+                                        len(tile_item), i32(qstart),
+                                        i32([n for _, n in self.items]),
+                                        i32([p for p, _ in self.items]), out, tokens, self.heads,
+                                        self.kv_heads, self.window, 1.0 / math.sqrt(self.hd),
+                                        error, nsplit, part_o, part_ml, i32(toks), len(toks))
                 assert error.item() == 0
                 continue
             if tma:
@@ -365,6 +376,44 @@ def test_attention_window_edge(ops, kernel, dtype, window):
                      peak=inside)
     got = run_kernel(case, ops, kernel, nsplit=2)
     assert (got - case.want).abs().max().item() < tol(dtype) * case.want.abs().max().item()
+
+
+@pytest.mark.parametrize("heads,kv_heads,page_size", [(28, 4, 16), (40, 8, 32), (16, 1, 8), (3, 3, 128),
+                                                      (12, 2, 64)])
+def test_attention_tc_decode_sizes(ops, heads, kv_heads, page_size):
+    """The tcgen05 kernel for tiles of up to 16 rows (head size 128): decoded tokens over short and
+    long histories, two-token portions, first tokens, beside requests of the other row classes."""
+    group = heads // kv_heads
+    items = [(45, 1), (0, 1), (127, 1), (128, 1), (1300, 1), (63, max(1, 16 // group)), (130, 70), (0, 37)]
+    case = PagedCase(torch.bfloat16, heads, kv_heads, 128, page_size, items=items, seed=heads)
+    for nsplit in (1, 3):
+        got = case.run_mma(ops, nsplit, tc_decode=True)
+        assert (got - case.want).abs().max().item() < tol(torch.bfloat16) * case.want.abs().max().item()
+
+
+@pytest.mark.parametrize("key_at", ["first", "page_edge", "far", "self"])
+def test_attention_tc_decode_finds_one_far_key(ops, key_at):
+    pick = {"first": lambda p, n: 0, "page_edge": lambda p, n: 16 * 7 - 1,
+            "far": lambda p, n: 131, "self": lambda p, n: p + n - 1}[key_at]
+    case = PagedCase(torch.bfloat16, 14, 2, 128, 16, items=[(600, 1), (500, 2)], seed=6, peak=pick)
+    for nsplit in (1, 4):
+        got = case.run_mma(ops, nsplit, tc_decode=True)
+        assert (got - case.want).abs().max().item() < tol(torch.bfloat16) * case.want.abs().max().item()
+
+
+@pytest.mark.parametrize("window", [1, 16, 21, 200])
+def test_attention_tc_decode_window_edge(ops, window):
+    outside = lambda p, n: max(0, p + n - 1 - window)
+    case = PagedCase(torch.bfloat16, 6, 3, 128, 8, items=[(290, 1), (64, 7), (700, 1)], window=window,
+                     seed=7, peak=outside)
+    got = case.run_mma(ops, tc_decode=True)
+    assert torch.isfinite(got).all()
+    assert (got - case.want).abs().max().item() < tol(torch.bfloat16) * case.want.abs().max().item()
+    inside = lambda p, n: max(0, p + n - window)
+    case = PagedCase(torch.bfloat16, 6, 3, 128, 8, items=[(290, 1), (64, 7)], window=window, seed=8,
+                     peak=inside)
+    got = case.run_mma(ops, nsplit=2, tc_decode=True)
+    assert (got - case.want).abs().max().item() < tol(torch.bfloat16) * case.want.abs().max().item()
 
 
 def test_attention_refuses_what_it_cannot_take(ops):

@@ -19,6 +19,7 @@ REQUESTS = {
     "C": {"a": 150, "b": 40, "c": 97, "d": 64, "e": 23},
     "D": {"a": 70, "b": 35, "c": 48},
     "E": {"a": 300, "b": 150, "c": 90, "d": 64},
+    "F": {"a": 290, "b": 150, "c": 129, "d": 64},
 }
 
 
@@ -53,7 +54,8 @@ FAMILIES = {
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("family", list(FAMILIES))
-@pytest.mark.parametrize("name,page_size", [("A", 4), ("B", 8), ("C", 16), ("D", 16), ("E", 16)])
+@pytest.mark.parametrize("name,page_size", [("A", 4), ("B", 8), ("C", 16), ("D", 16), ("E", 16),
+                                            ("F", 32)])
 def test_replay_matches_plain(folders, name, page_size, family, dtype):
     requests = requests_for(name)
     steps = FAMILIES[family](requests, 11)
@@ -159,3 +161,21 @@ def test_replay_with_the_tiled_product_on_every_matrix(folders, name, page_size,
     worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], TOLERANCE["bfloat16"])
     assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
     assert len(calls) >= 4 * len(runner.model.blocks)
+
+
+@pytest.mark.parametrize("family", ["tail", "portions", "mixed"])
+def test_replay_with_the_tcgen05_kernel_for_decoded_tokens(folders, family, monkeypatch):
+    """Decoded tokens and portions of up to 16 rows take the tcgen05 attention kernel only when
+    they fill the GPU; here it is forced onto a handful of requests (head size 128)."""
+    requests = requests_for("F")
+    steps = FAMILIES[family](requests, 7)
+    need = helpers.live_tokens_needed(steps, round_to=16)
+    runner = build_runner(folders["F"], "bfloat16", need, 16, decode_tcgen05_min_blocks=1)
+    from from_scratch_inference_engine_b200.kernels import ops
+    calls, original = [], ops.attention_tc_decode
+    monkeypatch.setattr(ops, "attention_tc_decode",
+                        lambda *a, **k: (calls.append(1), original(*a, **k))[1])
+    rows = helpers.run_trace_in_process(runner, steps)
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders["F"], TOLERANCE["bfloat16"])
+    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+    assert calls
