@@ -137,7 +137,7 @@ class GqaAttention(Mixer):
             for row_class, tiles, class_tokens, count, longest in \
                     ctx.attention_row_classes(group_size, class_rows):
                 on_tcgen05 = pages_map is not None and row_class == len(class_rows) - 1
-                # decoded tokens: with at least a block per SM before any split the tcgen05 kernel
+                # decoded tokens: from about 1.6 blocks per SM before any split the tcgen05 kernel
                 # (a tile's keys as the M side) is ahead of the mma.sync one, below that behind
                 decode_tcgen05 = (pages_map is not None and row_class == 0
                                   and self.head_dim in ops.ATTENTION_TC_DECODE_HEAD_DIMS
