@@ -452,7 +452,7 @@ def main() -> int:
     points = {}
     for batch in [int(b) for b in args.points.split(",") if b]:
         count = max(8, steps // 4)
-        ms, _ = decode_rate(batch, count, 3)
+        ms, _ = decode_rate(batch, count, max(3, warmup))
         points[f"decode_b{batch}"] = batch * 1000.0 / ms
 
     record = {
