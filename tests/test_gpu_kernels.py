@@ -592,9 +592,10 @@ def test_gemm_tiles_one_key_block_stands_out(ops):
 
 # -------------------------------------------------------- product without set-up for small matrices
 @pytest.mark.parametrize("tokens", [1, 5, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(384, 512), (200, 96), (37, 1024), (4608, 3584)])
+@pytest.mark.parametrize("n,k", [(384, 512), (200, 96), (37, 1024), (4608, 3584), (3584, 512), (4001, 64),
+                                 (9000, 96)])
 def test_gemm_skinny(ops, tokens, n, k):
-    """Rows of w in blocks of 16 (a ragged last block), k in chunks of 32 taken in turn by eight
+    """Rows of w in blocks of 16 (a ragged last block), k in chunks of 32 taken in turn by the
     warps (fewer chunks than warps at k = 96), tokens padded to 8 or 16."""
     torch.manual_seed(tokens * 1000 + n)
     x_full = dev(torch.randn(tokens, k + 8), torch.bfloat16)
@@ -613,8 +614,9 @@ def test_gemm_skinny(ops, tokens, n, k):
 def test_gemm_skinny_one_element_stands_out(ops):
     """A single k position of a single row and token carries the result: a lane that pairs the
     wrong 16 bytes of x with its weights shows at once."""
-    tokens, n, k = 7, 64, 256
-    for kk, row, token in ((0, 0, 0), (37, 9, 3), (255, 63, 6), (130, 24, 5)):
+    tokens, k = 7, 256
+    for n, kk, row, token in ((64, 0, 0, 0), (64, 37, 9, 3), (64, 255, 63, 6), (64, 130, 24, 5),
+                              (3584, 77, 24, 2), (3584, 200, 3583, 6), (3584, 1, 1816, 0)):
         x = torch.zeros(tokens, k)
         w = torch.zeros(n, k)
         x[token, kk] = 3.0

@@ -179,3 +179,5 @@ def test_replay_with_the_tcgen05_kernel_for_decoded_tokens(folders, family, monk
     worst, scale, bad = helpers.compare_rows(rows, requests, folders["F"], TOLERANCE["bfloat16"])
     assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
     assert calls
+    if family == "tail":
+        assert runner._graphs, "the decoded tokens did not go through a captured step"
