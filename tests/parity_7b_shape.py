@@ -32,6 +32,9 @@ def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--layers", type=int, default=28)
     parser.add_argument("--dtype", default="float32", choices=["float32", "bfloat16"])
+    parser.add_argument("--decode-tcgen05", action="store_true",
+                        help="bfloat16: decoded tokens take the tcgen05 attention kernel that the engine "
+                             "otherwise keeps for large batches")
     args = parser.parse_args()
     sys.path.insert(0, str(HERE.parent))
     import bench
@@ -66,8 +69,10 @@ def main():
         want[key] = plain.forward(plain_config, Widening(), ids).cpu().numpy()
     scale = max(float(np.abs(w).max()) for w in want.values())
 
-    model = LoadedModel.from_tensors(config, tensors, dtype=args.dtype, max_positions=512)
-    result = {"layers": args.layers, "dtype": args.dtype, "max_abs_plain_logit": scale}
+    options = {"decode_tcgen05_min_blocks": 1} if args.decode_tcgen05 else {}
+    model = LoadedModel.from_tensors(config, tensors, dtype=args.dtype, max_positions=512, **options)
+    result = {"layers": args.layers, "dtype": args.dtype, "max_abs_plain_logit": scale,
+              "decode_tcgen05": bool(args.decode_tcgen05)}
     families = {"whole": helpers.trace_whole(requests),
                 "tail_by_one": helpers.trace_tail_by_one(requests),
                 "portions": helpers.trace_portions(requests, 5),
