@@ -185,13 +185,15 @@ class Engine:
             return None
         return self.sampler.sample_async(logits, [i.seq.params for i in sampling],
                                          [i.seq.seed for i in sampling],
-                                         [len(i.seq.output) + i.seq.pending for i in sampling])
+                                         [len(i.seq.output) + i.seq.pending for i in sampling],
+                                         self.runner.error)
 
-    @staticmethod
-    def _tokens_of(items, picked) -> List[Optional[int]]:
+    def _tokens_of(self, items, picked) -> List[Optional[int]]:
         if picked is None:
             return [None] * len(items)
         chosen = iter(picked.result())
+        if picked.fault:            # a kernel refused an input or gave up a wait: the ids mean nothing
+            self.runner.raise_on_device_error()
         return [next(chosen) if item.samples else None for item in items]
 
     def _settle(self) -> int:

@@ -55,14 +55,19 @@ class Picked:
     """The tokens one sampling call chose: on the device at once (`device`, int32 [rows]), on
     the host after `result()`, which waits for the copy that was started with the call."""
 
-    def __init__(self, device: torch.Tensor, host: np.ndarray, event, rows: int):
+    def __init__(self, device: torch.Tensor, host: np.ndarray, event, rows: int,
+                 watches_fault: bool = False):
         self.device, self._host, self._event, self.rows = device, host, event, rows
+        self._watches_fault = watches_fault
         self._list: Optional[List[int]] = None
+        self.fault = 0          # after result(): the device's error flag as it stood after the kernels
 
     def result(self) -> List[int]:
         if self._list is None:
             self._event.synchronize()
             self._list = self._host[:self.rows].tolist()
+            if self._watches_fault:
+                self.fault = int(self._host[-1])
         return self._list
 
 
@@ -86,17 +91,21 @@ class Sampler:
         return self.sample_async(logits, params, seeds, indices).result()
 
     def _host_buffer(self, rows: int) -> torch.Tensor:
-        if not self._pinned or self._pinned[0].numel() < rows:
+        if not self._pinned or self._pinned[0].numel() - 1 < rows:
             size = max(256, 1 << (rows - 1).bit_length())
-            self._pinned = [torch.empty(size, dtype=torch.int32, pin_memory=True)
+            # one more element: the device's error flag travels with the ids
+            self._pinned = [torch.zeros(size + 1, dtype=torch.int32, pin_memory=True)
                             for _ in range(self.HOST_BUFFERS)]
         self._turn = (self._turn + 1) % self.HOST_BUFFERS
         return self._pinned[self._turn]
 
     def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-                     seeds: Sequence[int], indices: Sequence[int]) -> Picked:
+                     seeds: Sequence[int], indices: Sequence[int],
+                     error: Optional[torch.Tensor] = None) -> Picked:
         """The same without waiting: the kernels and the copy to pinned host memory are queued,
-        the chosen ids stay on the device for a step that feeds them back in."""
+        the chosen ids stay on the device for a step that feeds them back in.  `error` (int32
+        [1], the flag that kernels set when they refuse an input or give up a wait) is copied
+        along, so that whoever reads the ids learns of a fault without a transfer of its own."""
         rows = logits.shape[0]
         if rows != len(params):
             raise ValueError("one SamplingParams per row of logits is needed")
@@ -127,7 +136,9 @@ class Sampler:
             chosen = picks[0]
         pinned = self._host_buffer(rows)
         pinned[:rows].copy_(chosen, non_blocking=True)
+        if error is not None:
+            pinned[-1:].copy_(error, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
-        self.bytes_to_host += 4 * rows
-        return Picked(chosen, pinned.numpy(), event, rows)
+        self.bytes_to_host += 4 * rows + (4 if error is not None else 0)
+        return Picked(chosen, pinned.numpy(), event, rows, error is not None)

@@ -239,3 +239,18 @@ def test_command_line_generates_from_a_random_weights_folder(tmp_path, capsys):
     assert (folder / "config.json").exists() and (folder / "model.safetensors").exists()
     llm = LLM(str(folder), block_size=16, num_blocks=32)
     assert llm.generate_ids([5, 17, 3, 88, 41], GenerationConfig(max_tokens=9, temperature=0.0)) == report["outputs"][0]
+
+
+@pytest.mark.parametrize("pipeline", [False, True])
+def test_engine_raises_when_a_kernel_has_set_the_error_flag(folders, pipeline):
+    """Kernels that refuse an input or give up a wait set a flag on the device; it travels to the
+    host with the sampled ids, and the engine raises instead of handing out tokens.  (The flag is
+    set by hand here: nothing is made to fail on the GPU.)"""
+    from from_scratch_inference_engine_b200 import SamplingParams
+    from from_scratch_inference_engine_b200.engine.runner import DeviceFault
+    engine = engine_for(folders["A"], block_size=4, num_blocks=32, max_batch=2, pipeline=pipeline)
+    engine.add_request(helpers.random_ids(256, 9, 1), SamplingParams(temperature=0.0), 6)
+    assert engine.step() > 0
+    engine.runner.error.fill_(12)
+    with pytest.raises(DeviceFault, match="tile never arrived"):
+        engine.run_until_done()
