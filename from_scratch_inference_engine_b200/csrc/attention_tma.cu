@@ -30,7 +30,7 @@ constexpr int CHUNKS = HD / 8;         // 16-byte chunks per row
 constexpr int HALVES = HD / 64;        // 128-byte column halves of a key row
 constexpr int HALF_BYTES = BN * 128;   // one column half of a 64-key tile
 constexpr int TILE_BYTES = HALVES * HALF_BYTES;
-enum { ERR_ATTN_PRODUCER = 21, ERR_ATTN_CONSUMER = 22 };
+enum { ERR_ATTN_PRODUCER = 41, ERR_ATTN_CONSUMER = 42 };
 
 struct TmaExtra {                      // where a cache entry sits inside its group's page tensor
     int entries, entry, error_slot;    // entries per page, this entry
