@@ -30,6 +30,18 @@ struct SkinnyParams {
     int T, N, K, out_f32;
 };
 
+// The q, k, v product of an attention layer with what follows it on the way to the cache: w
+// holds `heads` query heads, then `kv_heads` key heads, then as many value heads, of head_dim
+// rows each.  Query and key heads are rotated by the angles of their token's position
+// (pairs (i, i + head_dim / 2), cos | sin table as in rope_kv_write), queries go to y, keys
+// and values into their token's slot of the pages (slot_of < 0 or no pages: not stored).
+struct SkinnyRope {
+    const int* positions; const float* cos_sin; int table_len;
+    const int* slot_of; bf16* k_pages; bf16* v_pages; long long page_stride; int page_size;
+    int heads, kv_heads, head_dim;
+    int* error;
+};
+
 __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                             uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -45,18 +57,30 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // TT: token tiles of 8 (1 or 2).  Dynamic shared memory: per warp a ring of SK_AHEAD slots of 1 KB
 // (each lane's 16 bytes of its two rows: a lane reads back only what it asked for itself, so
 // no barrier guards the ring); static: the warps' partial sums.
-template <int TT>
+// ROPE: the block's 16 rows are 8 rows of a head and the 8 rows half a head further on - the
+// two halves of 8 rotation pairs - and the epilogue is the one SkinnyRope describes.
+template <int TT, bool ROPE>
 __global__ void __launch_bounds__(32 * SK_WARPS)
-gemm_skinny_kernel(const SkinnyParams p) {
+gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
     extern __shared__ __align__(16) unsigned char sk_ring[];
     __shared__ float red[SK_WARPS * SK_ROWS * 8 * TT];            // [warp][16 rows][8 * TT]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int row0 = blockIdx.x * SK_ROWS;
     const int chunks = p.K / SK_CHUNK;
+    // rows of w behind rows 0-7 and 8-15 of the block's tile
+    int row0, row8;
+    if (ROPE) {
+        const int per_head = rope.head_dim / 16;                  // blocks per head
+        const int head = blockIdx.x / per_head, d0 = (blockIdx.x - head * per_head) * 8;
+        row0 = head * rope.head_dim + d0;
+        row8 = row0 + rope.head_dim / 2;
+    } else {
+        row0 = blockIdx.x * SK_ROWS;
+        row8 = row0 + 8;
+    }
     // this lane's two rows (clamped at the matrix's end; those results are not stored)
     const bf16* w_lo = p.w + (size_t)min(row0 + g, p.N - 1) * p.K + 8 * t;
-    const bf16* w_hi = p.w + (size_t)min(row0 + g + 8, p.N - 1) * p.K + 8 * t;
+    const bf16* w_hi = p.w + (size_t)min(row8 + g, p.N - 1) * p.K + 8 * t;
     unsigned char* mine = sk_ring + (size_t)warp * SK_AHEAD * 1024 + lane * 16;     // slot s: + s * 1024; second row: + 512
 
     auto ask = [&](int slot, int c) {                             // this lane's 32 bytes of chunk c
@@ -108,6 +132,49 @@ gemm_skinny_kernel(const SkinnyParams p) {
         mine[(size_t)(g + 8) * TP + 1] = acc[n][3];
     }
     __syncthreads();
+    if constexpr (ROPE) {
+        const int half = rope.head_dim / 2;
+        const int per_head = rope.head_dim / 16;
+        const int head = blockIdx.x / per_head, d0 = (blockIdx.x - head * per_head) * 8;
+        for (int e = threadIdx.x; e < 8 * TP; e += blockDim.x) {
+            const int token = e >> 3, r = e & 7;                  // consecutive threads: consecutive pairs of a token
+            if (token >= p.T) continue;
+            float lo = 0.f, hi = 0.f;
+#pragma unroll
+            for (int w = 0; w < SK_WARPS; ++w) {
+                lo += red[((size_t)w * SK_ROWS + r) * TP + token];
+                hi += red[((size_t)w * SK_ROWS + r + 8) * TP + token];
+            }
+            if (p.bias) { lo += __bfloat162float(p.bias[row0 + r]); hi += __bfloat162float(p.bias[row8 + r]); }
+            // the unfused path stores the product as bfloat16 before it rotates: the same rounding here
+            lo = __bfloat162float(__float2bfloat16_rn(lo));
+            hi = __bfloat162float(__float2bfloat16_rn(hi));
+            const int d = d0 + r;
+            if (head < rope.heads + rope.kv_heads) {              // a query or key head: rotate
+                int pos = rope.positions[token];
+                if (pos < 0 || pos >= rope.table_len) { atomicExch(rope.error, 2); pos = 0; }
+                const float* cs = rope.cos_sin + (size_t)pos * rope.head_dim;
+                const float c = cs[d], sn = cs[half + d];
+                const float a = lo * c - hi * sn, b = hi * c + lo * sn;
+                lo = a; hi = b;
+            }
+            bf16* dst;
+            if (head < rope.heads) {
+                dst = reinterpret_cast<bf16*>(p.y) + (size_t)token * p.ldy + head * rope.head_dim;
+            } else {
+                const int slot = rope.slot_of ? rope.slot_of[token] : -1;
+                if (slot < 0) continue;
+                const long long page = slot / rope.page_size;
+                const int offset = slot - (int)page * rope.page_size;
+                const bool is_k = head < rope.heads + rope.kv_heads;
+                const int kvh = head - rope.heads - (is_k ? 0 : rope.kv_heads);
+                dst = (is_k ? rope.k_pages : rope.v_pages) + page * rope.page_stride +
+                      ((size_t)kvh * rope.page_size + offset) * rope.head_dim;
+            }
+            dst[d] = __float2bfloat16_rn(lo);
+            dst[half + d] = __float2bfloat16_rn(hi);
+        }
+    } else {
     for (int e = threadIdx.x; e < SK_ROWS * TP; e += blockDim.x) {
         const int token = e / SK_ROWS, r = e - token * SK_ROWS;   // consecutive threads: consecutive outputs of a token
         const int n = row0 + r;
@@ -119,18 +186,19 @@ gemm_skinny_kernel(const SkinnyParams p) {
         if (p.out_f32) reinterpret_cast<float*>(p.y)[(size_t)token * p.ldy + n] = sum;
         else reinterpret_cast<bf16*>(p.y)[(size_t)token * p.ldy + n] = __float2bfloat16_rn(sum);
     }
+    }
 }
 
-template <int TT>
-static int launch_skinny(const SkinnyParams& p, cudaStream_t stream) {
+template <int TT, bool ROPE>
+static int launch_skinny(const SkinnyParams& p, const SkinnyRope& rope, cudaStream_t stream) {
     constexpr size_t smem = (size_t)SK_WARPS * SK_AHEAD * 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<TT, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return launch_dependent(gemm_skinny_kernel<TT>, dim3((p.N + SK_ROWS - 1) / SK_ROWS), dim3(32 * SK_WARPS), smem, stream, p);
+    return launch_dependent(gemm_skinny_kernel<TT, ROPE>, dim3((p.N + SK_ROWS - 1) / SK_ROWS), dim3(32 * SK_WARPS), smem, stream, p, rope);
 }
 
 }  // namespace fsie
@@ -149,7 +217,32 @@ int fsie_gemm_skinny(const void* w, const void* x, long long ldx, void* y, long 
     SkinnyParams p;
     p.w = (const bf16*)w; p.x = (const bf16*)x; p.ldx = ldx; p.y = y; p.ldy = ldy; p.bias = (const bf16*)bias;
     p.T = T; p.N = N; p.K = K; p.out_f32 = out_f32;
-    return T <= 8 ? launch_skinny<1>(p, stream) : launch_skinny<2>(p, stream);
+    SkinnyRope none = {};
+    return T <= 8 ? launch_skinny<1, false>(p, none, stream) : launch_skinny<2, false>(p, none, stream);
+}
+
+// The q, k, v product fused with the rotation and the cache write (see SkinnyRope): w [(heads +
+// 2 kv_heads) * head_dim, K]; rotated queries to q_out[T, ldq] (bfloat16), keys and values to
+// slot_of[t] of the pages unless that is negative or k_pages is null.  head_dim a multiple of 16;
+// the whole head is rotated (cos_sin has head_dim floats per position: cos | sin).
+int fsie_gemm_skinny_qkv_rope(const void* w, const void* x, long long ldx, void* q_out, long long ldq, const void* bias,
+                              int T, int K, const int* positions, const float* cos_sin, int table_len,
+                              const int* slot_of, void* k_pages, void* v_pages, long long page_stride, int page_size,
+                              int heads, int kv_heads, int head_dim, int* error, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (T > 16 || K <= 0 || K % SK_CHUNK != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(w) & 15) ||
+        (reinterpret_cast<uintptr_t>(x) & 15) || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || head_dim % 16 != 0 ||
+        !positions || !cos_sin || !error || page_size <= 0)
+        return ERR_BAD_ARGUMENT;
+    SkinnyParams p;
+    p.w = (const bf16*)w; p.x = (const bf16*)x; p.ldx = ldx; p.y = q_out; p.ldy = ldq; p.bias = (const bf16*)bias;
+    p.T = T; p.N = (heads + 2 * kv_heads) * head_dim; p.K = K; p.out_f32 = 0;
+    SkinnyRope rope;
+    rope.positions = positions; rope.cos_sin = cos_sin; rope.table_len = table_len;
+    rope.slot_of = k_pages ? slot_of : nullptr; rope.k_pages = (bf16*)k_pages; rope.v_pages = (bf16*)v_pages;
+    rope.page_stride = page_stride; rope.page_size = page_size;
+    rope.heads = heads; rope.kv_heads = kv_heads; rope.head_dim = head_dim; rope.error = error;
+    return T <= 8 ? launch_skinny<1, true>(p, rope, stream) : launch_skinny<2, true>(p, rope, stream);
 }
 
 }  // extern "C"

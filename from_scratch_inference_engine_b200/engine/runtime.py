@@ -70,6 +70,8 @@ class Runtime:
         # the mma.sync kernel by 9 % at 192 pairs on 148 SMs, ahead by 15 % at 256)
         self.decode_tcgen05_min_blocks = (int(1.6 * self.sm_count) if decode_tcgen05_min_blocks is None
                                           else int(decode_tcgen05_min_blocks))
+        # steps of few tokens rotate q, k and write k, v in the q, k, v product's epilogue
+        self.fused_qkv_rope = True
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -162,6 +164,26 @@ class Runtime:
         return (self.products == "own" and ops.gemm_skinny_fits(x.shape[0], x.shape[1])
                 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
                 and weight.dtype is torch.bfloat16 and weight.is_contiguous())
+
+    def qkv_rotated_and_cached(self, x: torch.Tensor, weight: torch.Tensor,
+                               bias: Optional[torch.Tensor], positions: torch.Tensor,
+                               cos_sin: torch.Tensor, slot_of, k_pages, v_pages, page_stride: int,
+                               page_size: int, heads: int, kv_heads: int, head_dim: int,
+                               rotary_dim: int) -> Optional[torch.Tensor]:
+        """The q, k, v product of an attention layer together with the rotation of q and k and
+        the write of k and v into the pages, where one kernel does all three (steps of few
+        tokens against a matrix that the set-up-free product takes, whole heads rotated);
+        else None, and the caller runs the product and `ops.rope_kv_write` one after the other.
+        Returns [tokens, q + k + v width] of which only the query columns are filled."""
+        if not (self.dtype is torch.bfloat16 and self.fused_qkv_rope and rotary_dim == head_dim
+                and head_dim % 16 == 0 and self._few_tokens(x, weight) is None
+                and self._skinny(x, weight)
+                and weight.shape[0] == (heads + 2 * kv_heads) * head_dim):
+            return None
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+        return ops.gemm_skinny_qkv_rope(weight, x, out, bias, positions, cos_sin, slot_of, k_pages,
+                                        v_pages, page_stride, page_size, heads, kv_heads, head_dim,
+                                        self.error)
 
     def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
         """silu(x @ gate.T) * (x @ up.T) for the stacked weight [gate rows; up rows]: one fused

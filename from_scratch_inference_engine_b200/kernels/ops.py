@@ -572,18 +572,65 @@ def gemm_skinny_fits(tokens: int, k: int) -> bool:
     return 0 < tokens <= GEMM_SKINNY_MAX_TOKENS and k % 32 == 0
 
 
-def gemm_skinny(weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor,
-                bias: Optional[torch.Tensor]) -> torch.Tensor:
-    """out[T, N] = x[T, K] @ weight.T (+ bias) for T <= 16: no pipeline to fill, every lane asks
-    for its weights straight from global memory (for matrices so small that set-up would
-    dominate).  out is bfloat16 or float32."""
+def gemm_skinny_lib():
     global _gemm_skinny
     if _gemm_skinny is None:
         lib = build.load_library("gemm_skinny")
         i, ll, p = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p
         lib.fsie_gemm_skinny.argtypes = [p, p, ll, p, ll, p, i, i, i, i, p]
         lib.fsie_gemm_skinny.restype = i
+        lib.fsie_gemm_skinny_qkv_rope.argtypes = [p, p, ll, p, ll, p, i, i, p, p, i, p, p, p, ll, i,
+                                                  i, i, i, p, p]
+        lib.fsie_gemm_skinny_qkv_rope.restype = i
         _gemm_skinny = lib
+    return _gemm_skinny
+
+
+def gemm_skinny_qkv_rope(weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor,
+                         bias: Optional[torch.Tensor], positions: torch.Tensor,
+                         cos_sin: torch.Tensor, slot_of: Optional[torch.Tensor],
+                         k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                         page_stride: int, page_size: int, heads: int, kv_heads: int,
+                         head_dim: int, error: torch.Tensor) -> torch.Tensor:
+    """The q, k, v product of up to 16 tokens with the rotation of q and k and the cache write in
+    its epilogue: rotated queries into out[:, :heads * head_dim] (bfloat16; the key and value
+    columns of `out` are not written), rotated keys and the values into the pages (not when
+    k_pages is None).  The whole head is rotated: cos_sin is [positions, head_dim]."""
+    lib = gemm_skinny_lib()
+    _need(weight, torch.bfloat16, "weight")
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(out, torch.bfloat16, "out", contiguous=False)
+    _need(positions, torch.int32, "positions")
+    _need(cos_sin, torch.float32, "cos_sin")
+    _need(error, torch.int32, "error")
+    tokens, k = x.shape
+    n = (heads + 2 * kv_heads) * head_dim
+    if weight.shape != (n, k) or x.stride(1) != 1 or not gemm_skinny_fits(tokens, k):
+        raise KernelError("gemm_skinny_qkv_rope: x does not fit the weight, or the sizes are beyond the kernel")
+    if head_dim % 16 or cos_sin.shape[-1] != head_dim:
+        raise KernelError("gemm_skinny_qkv_rope: needs a head size in steps of 16, rotated as a whole")
+    if out.shape[0] != tokens or out.shape[1] < heads * head_dim or out.stride(1) != 1:
+        raise KernelError("gemm_skinny_qkv_rope: out does not fit")
+    if bias is not None:
+        _need(bias, torch.bfloat16, "bias")
+    if k_pages is not None:
+        _need(slot_of, torch.int32, "slot_of")
+        if k_pages.dtype is not torch.bfloat16 or v_pages.dtype is not torch.bfloat16:
+            raise KernelError("gemm_skinny_qkv_rope: the cache must be bfloat16")
+    _check(lib.fsie_gemm_skinny_qkv_rope(
+        _ptr(weight), _ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(bias), tokens, k,
+        _ptr(positions), _ptr(cos_sin), cos_sin.shape[0], _ptr(slot_of), _ptr(k_pages),
+        _ptr(v_pages), page_stride, page_size, heads, kv_heads, head_dim, _ptr(error), _stream()),
+        "gemm_skinny_qkv_rope")
+    return out
+
+
+def gemm_skinny(weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor,
+                bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ weight.T (+ bias) for T <= 16: no pipeline to fill, every lane asks
+    for its weights straight from global memory (for matrices so small that set-up would
+    dominate).  out is bfloat16 or float32."""
+    gemm_skinny_lib()
     _need(weight, torch.bfloat16, "weight")
     _need(x, torch.bfloat16, "x", contiguous=False)
     _need(out, None, "out", contiguous=False)

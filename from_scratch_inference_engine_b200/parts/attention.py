@@ -101,13 +101,16 @@ class GqaAttention(Mixer):
         rt = self.runtime
         tokens = y.shape[0]
         group = ctx.groups[cache.group]
-        qkv = rt.linear(y, self.w_qkv, self.b_qkv)
-        ops.rope_kv_write(qkv, ctx.positions, self.position.table,
-                          group.slot_of if cache.writes else None,
-                          cache.k_pages if cache.writes else None,
-                          cache.v_pages if cache.writes else None,
-                          cache.page_stride, group.page_size, self.num_heads, self.num_kv_heads,
-                          self.head_dim, self.position.rotary_dim, ctx.error)
+        rope = (ctx.positions, self.position.table,
+                group.slot_of if cache.writes else None,
+                cache.k_pages if cache.writes else None,
+                cache.v_pages if cache.writes else None,
+                cache.page_stride, group.page_size, self.num_heads, self.num_kv_heads,
+                self.head_dim, self.position.rotary_dim)
+        qkv = rt.qkv_rotated_and_cached(y, self.w_qkv, self.b_qkv, *rope)
+        if qkv is None:
+            qkv = rt.linear(y, self.w_qkv, self.b_qkv)
+            ops.rope_kv_write(qkv, *rope, ctx.error)
         out = torch.empty((tokens, self.q_width), dtype=qkv.dtype, device=qkv.device)
         self._attend(ctx, qkv, group, cache, out)
         return rt.linear(out, self.w_o, None)

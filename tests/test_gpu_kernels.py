@@ -611,6 +611,52 @@ def test_gemm_skinny(ops, tokens, n, k):
     assert (out32.double() - want - bias.double()).abs().max().item() < 2e-3 * want.abs().max().item()
 
 
+@pytest.mark.parametrize("tokens", [1, 7, 16])
+@pytest.mark.parametrize("heads,kv_heads,hd,k,page_size,bias", [
+    (28, 4, 128, 512, 16, True), (6, 2, 48, 96, 8, False), (5, 1, 16, 64, 4, True), (3, 3, 80, 160, 32, True)])
+def test_gemm_skinny_with_rotation_and_cache_write(ops, tokens, heads, kv_heads, hd, k, page_size, bias):
+    """The q, k, v product with the rotation and the cache write in its epilogue gives what the
+    product followed by rope_kv_write gives: rotated queries, rotated keys and values in the slots
+    (one token has no slot: nothing of it may be stored), other slots untouched."""
+    from from_scratch_inference_engine_b200.parts.rope import rotary_table
+    torch.manual_seed(tokens * 100 + heads)
+    n = (heads + 2 * kv_heads) * hd
+    x = dev(torch.randn(tokens, k), torch.bfloat16)
+    w = dev(torch.randn(n, k) / math.sqrt(k), torch.bfloat16)
+    b = dev(torch.randn(n), torch.bfloat16) if bias else None
+    table = dev(torch.from_numpy(rotary_table(10000.0, hd, 300)))
+    positions = dev(torch.randint(0, 300, (tokens,), dtype=torch.int32))
+    num_pages = 9
+    slots = torch.randperm(num_pages * page_size)[:tokens].to(torch.int32)
+    if tokens > 2:
+        slots[1] = -1
+    slots = dev(slots)
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def pages():
+        return torch.full((num_pages, 1, 2, kv_heads, page_size, hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    want_pages, got_pages = pages(), pages()
+    want = torch.empty((tokens, n), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_skinny(w, x, want, b)
+    ops.rope_kv_write(want, positions, table, slots, want_pages[:, 0, 0], want_pages[:, 0, 1],
+                      want_pages.stride(0), page_size, heads, kv_heads, hd, hd, error)
+    got = torch.full((tokens, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_skinny_qkv_rope(w, x, got, b, positions, table, slots, got_pages[:, 0, 0], got_pages[:, 0, 1],
+                             got_pages.stride(0), page_size, heads, kv_heads, hd, error)
+    assert error.item() == 0
+
+    def same(a, b):      # to one rounding of bfloat16 (the two kernels may contract a * c - b * s differently)
+        return (a.float() - b.float()).abs().max().item() <= 2.0 ** -7 * b.float().abs().max().item()
+    assert same(got[:, :heads * hd], want[:, :heads * hd])
+    assert same(got_pages, want_pages)
+    assert torch.equal(got_pages == 7.0, want_pages == 7.0)       # the same slots were written
+    # without pages: queries only
+    got = torch.full((tokens, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_skinny_qkv_rope(w, x, got, b, positions, table, None, None, None, 0, page_size, heads, kv_heads,
+                             hd, error)
+    assert same(got[:, :heads * hd], want[:, :heads * hd])
+
+
 def test_gemm_skinny_one_element_stands_out(ops):
     """A single k position of a single row and token carries the result: a lane that pairs the
     wrong 16 bytes of x with its weights shows at once."""
