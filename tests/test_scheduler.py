@@ -305,3 +305,26 @@ def test_a_plan_that_would_preempt_is_given_up_while_tokens_are_pending():
     s.resolve_step(items, [1 if i.samples else None for i in items])
     assert s.plan() and s.preemptions >= 1    # with nothing pending the youngest is preempted
     assert {s.sequences[a].status, s.sequences[b].status} == {SeqStatus.Running, SeqStatus.Waiting}
+
+
+def test_key_splits_of_the_attention_launch():
+    """How many key ranges a tile is cut into (host arithmetic of parts/attention.py): decoded
+    tokens fill the block slots without falling under 128 keys per range and never split past 32;
+    prompt tiles split only into slots that would stay empty."""
+    from from_scratch_inference_engine_b200.parts.attention import attention_splits
+    sms = 148
+    # decoded tokens, mma.sync kernel (three blocks per SM): 32 pairs at 4,096 keys fill 444 slots
+    n = attention_splits(32, 4096, sms, True)
+    assert 9 <= n <= 13 and 32 * n <= 3 * sms
+    assert attention_splits(4, 4096, sms, True) >= 24           # batch 1
+    assert attention_splits(4, 200, sms, True) == 1              # too short to split
+    assert attention_splits(4, 100000, sms, True) <= 32
+    assert attention_splits(2048, 4096, sms, True) <= 2          # many pairs: waves, not splits
+    # decoded tokens, tcgen05 kernel (two blocks per SM, dearer blocks): one wave unsplit
+    assert attention_splits(256, 4096, sms, True, decode_slots=2, decode_fixed=530) == 1
+    assert attention_splits(148, 4096, sms, True, decode_slots=2, decode_fixed=530) == 2
+    # prompt tiles: as many splits as fill the slots, none when there are tiles enough
+    assert attention_splits(2 * sms, 8192, sms, False) == 1
+    assert attention_splits(sms // 2, 8192, sms, False) == 4
+    assert attention_splits(32, 2048, sms, False, 1) == 4        # one block per SM: 148 // 32
+    assert attention_splits(32, 300, sms, False, 1) == 2         # at least 128 keys per range
