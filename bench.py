@@ -52,11 +52,17 @@ def peaks():
     if path.exists():
         try:
             data = json.loads(path.read_text())
+            found = 0
             for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
-                if key in data:
-                    values[key] = float(data[key])
-            source = "measured"
-        except (OSError, ValueError):
+                value = data.get(key) if isinstance(data, dict) else None
+                if isinstance(value, dict):        # a record with the figure inside
+                    value = next((value[k] for k in ("value", "median", "mean") if k in value), None)
+                if isinstance(value, (int, float)) and value > 0:
+                    values[key] = float(value)
+                    found += 1
+            if found:
+                source = "measured"
+        except (OSError, ValueError, TypeError):
             pass
     return values, source
 
