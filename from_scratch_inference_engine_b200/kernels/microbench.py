@@ -35,10 +35,14 @@ def peaks():
     if path.exists():
         try:
             data = json.loads(path.read_text())
-            values.update({k: float(v) for k, v in data.items()
-                           if k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained")})
-            values["source"] = "measured"
-        except (OSError, ValueError):
+            for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                value = data.get(key) if isinstance(data, dict) else None
+                if isinstance(value, dict):        # a record with the figure inside
+                    value = next((value[k] for k in ("value", "median", "mean") if k in value), None)
+                if isinstance(value, (int, float)) and value > 0:
+                    values[key] = float(value)
+                    values["source"] = "measured"
+        except (OSError, ValueError, TypeError):
             pass
     return values
 
