@@ -55,6 +55,7 @@ class RequestCache:
     length: int = 0
     shared_tokens: int = 0        # leading tokens that came from shared prefix pages
     closed: bool = False
+    fresh_state: bool = True      # the state slot still holds what its previous owner left
     _arrays: Optional[list] = None    # per group (table length, int32 array) for the step's staging
 
     def table_array(self, g: int):
@@ -106,9 +107,11 @@ def group_needs(needs: Sequence[Optional[CacheNeed]]) -> List[Tuple[CacheNeed, L
 
 class CacheManager:
     def __init__(self, needs: Sequence[Optional[CacheNeed]], page_size: int,
-                 num_pages, num_slots: int, enable_prefix_cache: bool = False):
+                 num_pages, num_slots: int, enable_prefix_cache: bool = False,
+                 has_state: bool = False):
         """`needs[e]` is the need of cache entry e (None for an entry without keys).
-        `num_pages` is one count for every group or a list with one count per group."""
+        `num_pages` is one count for every group or a list with one count per group.
+        `has_state` says that some layer keeps per-request state of fixed size in the slots."""
         if page_size <= 0:
             raise ValueError("CacheManager: page_size must be positive")
         grouped = group_needs(needs)
@@ -126,8 +129,11 @@ class CacheManager:
             for index, entry in enumerate(group.entries):
                 self.entry_group[entry] = (gi, index)
         self.live: Dict[object, RequestCache] = {}
-        # sharing a prefix needs every position's keys to be kept: no windowed group
-        self.prefix_enabled = enable_prefix_cache and all(g.need.window == 0 for g in self.groups)
+        # sharing a prefix needs every position's keys to be kept (no windowed group) and
+        # nothing else that the shared tokens would have had to pass through: fixed-size state
+        # has no copy per page, so a request that skipped tokens would start from a wrong state
+        self.prefix_enabled = (enable_prefix_cache and not has_state
+                               and all(g.need.window == 0 for g in self.groups))
         self._prefix: Dict[int, List[_PrefixEntry]] = {}
         # cached entries from least to most recently used, and by their page in group 0 (the
         # pages of an entry are always shared together, so group 0 speaks for all of them);

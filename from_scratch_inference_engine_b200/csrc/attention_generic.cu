@@ -279,7 +279,18 @@ extern "C" {
 
 long long fsie_attn_static_scratch_floats(int tokens, int heads, int head_dim, int nsplit) {
     if (nsplit <= 1) return 0;
-    return (long long)nsplit * tokens * heads * ((long long)head_dim + 2);
+    if (tokens < 0 || heads < 0 || head_dim < 0) return -1;
+    // multiplied factor by factor and cut off as soon as the limit is passed, so that four
+    // large ints cannot wrap around 64 bits and slip under the check
+    const long long limit = (long long)FSIE_STATIC_SCRATCH_FLOATS;
+    const long long factors[4] = {nsplit, tokens, heads, (long long)head_dim + 2};
+    long long need = 1;
+    for (long long f : factors) {
+        if (f > limit) return limit + 1;
+        need *= f;                         // need <= limit and f <= limit: below 2^40
+        if (need > limit) return limit + 1;
+    }
+    return need;
 }
 
 const char* fsie_attn_static_scratch_error(int code) {
@@ -305,6 +316,7 @@ int fsie_attn_generic_static_scratch(
     int head_dim, int window, int nsplit, float scale, int dtype, cudaStream_t stream) {
     if (tokens < 0 || heads <= 0 || head_dim <= 0 || nsplit < 1) return fsie::ERR_BAD_ARGUMENT;
     const long long need = fsie_attn_static_scratch_floats(tokens, heads, head_dim, nsplit);
+    if (need < 0) return fsie::ERR_BAD_ARGUMENT;
     if (need > (long long)FSIE_STATIC_SCRATCH_FLOATS) return FSIE_ERR_SCRATCH_TOO_SMALL;
     float* scratch = nullptr;
     const int rc = fsie::static_scratch_for_current_device(&scratch);

@@ -15,12 +15,19 @@
  *
  *  - It calls no cudaMalloc, cudaFree or any allocating routine.
  *  - The first call on a device looks the array's device address up and sets the kernel's
- *    shared-memory limit; make that first call outside any stream capture.
+ *    shared-memory limit; make that first call outside any stream capture, and from one host
+ *    thread: the looked-up address is kept per device without a lock (two threads racing
+ *    through their first calls would both store the same value, but nothing orders them).
  *  - It needs nsplit * tokens * heads * (head_dim + 2) floats; a launch that needs more than
  *    FSIE_STATIC_SCRATCH_FLOATS is refused with FSIE_ERR_SCRATCH_TOO_SMALL and nothing runs.
- *    fsie_attn_static_scratch_floats() tells the need beforehand.
- *  - Nothing in the array has to start at zero: every (split, token, head) slot a launch
- *    reads is written by that same launch first.  The array keeps the last call's contents.
+ *    fsie_attn_static_scratch_floats() tells the need beforehand (anything above the limit is
+ *    reported as limit + 1: the product is cut off before it could overflow; negative sizes
+ *    give -1 and the launch is refused as a bad argument).
+ *  - Nothing in the array has to start at zero: every (split, token, head) slot that a tile
+ *    covers is written by the launch before its merge reads it.  The array keeps the last
+ *    call's contents, so the tiles must cover every one of the `tokens` rows: with
+ *    nsplit > 1 the merge runs over all `tokens`, and a row that no tile covers is merged
+ *    from whatever an earlier call left there - its row of `out` is undefined.
  *  - All calls share the one array.  Calls that overlap on the GPU (two streams, two
  *    threads, two processes' worth of launches on one context) race on it; keep calls on one
  *    stream or order them yourself.

@@ -108,7 +108,8 @@ class ModelRunner:
                  cuda_graphs: bool = True):
         self.model, self.runtime = model, runtime
         needs = model.cache_needs()
-        self.cache = CacheManager(needs, page_size, num_pages, max_requests, enable_prefix_cache)
+        self.cache = CacheManager(needs, page_size, num_pages, max_requests, enable_prefix_cache,
+                                  has_state=any(n is not None for n in model.state_needs()))
         device, dtype = runtime.device, runtime.dtype
         # pages of group g: [page, entry in group, K or V, kv_head, slot, head_dim]
         self.pages: List[torch.Tensor] = []
@@ -260,8 +261,9 @@ class ModelRunner:
             q_len.append(len(entry.tokens))
             pos0.append(entry.handle.length)
             slots.append(entry.handle.slot)
-            if entry.handle.length == 0:
+            if entry.handle.fresh_state:          # first step since the slot was acquired
                 fresh_slots.append(entry.handle.slot)
+                entry.handle.fresh_state = False
             want_rows += [len(token_ids) + w for w in entry.want]
             token_ids += [0] if entry.source_row >= 0 else list(entry.tokens)
         tables = [(cache.page_size, [e.handle.table_array(g) for e in entries])

@@ -25,9 +25,12 @@ def parse_dtype(name) -> torch.dtype:
 
 
 class Runtime:
-    """Device and precision of one engine.
+    """Device and precision of one engine, and which kernel multiplies which step.
 
-    bfloat16: matrix products by the library (cuBLAS through torch, bf16 operands, 32-bit
+    bfloat16: steps of up to 16 tokens take the engine's few-token products (tcgen05 for the
+    large matrices, a set-up-free mma.sync kernel for the small ones), steps with enough
+    256 x 256 output tiles to fill the GPU take the engine's tiled tcgen05 product, and the
+    steps in between take the library product (cuBLAS through torch, bf16 operands, 32-bit
     accumulation), as the reference engine uses the library for its products
     (src/cuda/device.cu:322-357).  float32: every product by the engine's own FFMA kernel,
     no tensor-core mode.  Everything that is not a plain matrix product is a kernel of
@@ -219,4 +222,20 @@ class Runtime:
                 self._f32_out = False
         if self._f32_out:
             return torch.mm(x, weight.t(), out_dtype=torch.float32)
-        return F.linear(x, weight).float()
+        # this torch cannot give a float32 result from bfloat16 operands: rounding the logits
+        # to bfloat16 on the way would break the rule that logits are 32-bit, so the rows go
+        # through the engine's own products sixteen at a time where those take the matrix,
+        # else through a float32 product over slabs of the matrix (slow, and said so once)
+        part = x[:self.few_token_limit]
+        if x.shape[0] > self.few_token_limit and (
+                self._few_tokens(part, weight) is not None or self._skinny(part, weight)):
+            return torch.cat([self.linear_f32_out(x[r:r + self.few_token_limit], weight)
+                              for r in range(0, x.shape[0], self.few_token_limit)])
+        if not getattr(self, "_warned_f32_out", False):
+            self._warned_f32_out = True
+            import warnings
+            warnings.warn("torch.mm(out_dtype=float32) is not available: float32 logits are "
+                          "computed by a float32 product over slabs of the output head")
+        xf = x.float()
+        return torch.cat([xf @ weight[r:r + 8192].float().t()
+                          for r in range(0, weight.shape[0], 8192)], dim=1)

@@ -88,6 +88,17 @@ class PlanItem:
     source_row: int = -1   # >= 0: the single token is row source_row of the previous step's samples
 
 
+def cache_too_small_for_window(cache: CacheManager) -> str:
+    """Why a windowed group of the cache could never hold one request's window ('' if each can):
+    a query sees its last `window` keys, which may straddle one page more than they fill."""
+    for index, group in enumerate(cache.groups):
+        window = group.need.window
+        if window and group.num_pages < cache.blocks_for(window) + 1:
+            return (f"cache group {index} keeps a window of {window} keys and needs "
+                    f"{cache.blocks_for(window) + 1} pages for one request, it has {group.num_pages}")
+    return ""
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, max_batch: int = 256, max_step_tokens: int = 2048,
                  max_positions: int = 0):
@@ -115,6 +126,9 @@ class Scheduler:
         if total - 1 > share:
             raise ValueError(f"Engine: request needs up to {total - 1} cached tokens, the page "
                              f"pool holds {share} for one request")
+        short = cache_too_small_for_window(self.cache)
+        if short:
+            raise ValueError(f"Engine: {short}")
         if self.max_positions and total - 1 > self.max_positions:
             raise ValueError(f"Engine: request would reach position {total - 1}, the model's "
                              f"limit is {self.max_positions}")
@@ -133,8 +147,11 @@ class Scheduler:
         while self.waiting and len(self.running) < self.max_batch and cache.can_open():
             seq = self.sequences[self.waiting[0]]
             first = min(seq.context_length(), self.max_step_tokens)
-            # pages the first portion needs, seen against what is free before this step
-            if any(cache.blocks_for(first) > free for free in cache.free_pages()):
+            # pages the first portion needs, seen against what is free before this step; a
+            # windowed group gives pages back as the portions pass, so one free page lets the
+            # request start and `plan` cuts its portions to the room there is
+            if any((1 if group.need.window else cache.blocks_for(first)) > free
+                   for group, free in zip(cache.groups, cache.free_pages())):
                 break
             self.waiting.popleft()
             seq.handle = cache.open(seq.id)
@@ -151,6 +168,17 @@ class Scheduler:
         while True:
             items: List[PlanItem] = []
             tokens_left = self.max_step_tokens
+            if cache.prefix_enabled:
+                # before any page of this step is budgeted: a shared page that only the prefix
+                # cache held counted as free until a request took it
+                for sid in self.running:
+                    seq = self.sequences[sid]
+                    handle = seq.handle
+                    if seq.prefilled or handle.length or any(handle.tables):
+                        continue
+                    cap = ((seq.context_length() - 1) // cache.page_size) * cache.page_size
+                    if cap > 0:
+                        cache.acquire_prefix(handle, seq.context_slice(0, cap))
             pages_left = cache.free_pages()
 
             def take(handle, n) -> bool:
@@ -181,11 +209,6 @@ class Scheduler:
                     continue
                 total = seq.context_length()
                 handle = seq.handle
-                if cache.prefix_enabled and handle.length == 0 and not any(handle.tables):
-                    cap = ((total - 1) // cache.page_size) * cache.page_size
-                    if cap > 0:
-                        cache.acquire_prefix(handle, seq.context_slice(0, cap))
-                        pages_left = [min(a, b) for a, b in zip(pages_left, cache.free_pages())]
                 remaining = total - handle.length
                 chunk = min(remaining, tokens_left)
                 # shrink the portion to the pages that are left

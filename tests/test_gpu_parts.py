@@ -196,3 +196,24 @@ def test_run_order_is_data(tmp_path, dtype, order):
     close(torch.cat(rows), want, dtype)
     usual = plain.forward(config, weights, ids)
     assert (usual - want).abs().max().item() > 1e-3          # the order matters
+
+
+@pytest.mark.parametrize("rows", [5, 40])
+@pytest.mark.parametrize("route", ["own kernels", "float32 slabs"])
+def test_logits_stay_32_bit_without_the_library_float32_result(rows, route):
+    """Where torch cannot return a float32 product of bfloat16 operands, the output head must
+    not round its logits to bfloat16 on the way (8 bits of mantissa: ~4e-3 relative)."""
+    runtime = runtime_for("bfloat16")
+    runtime._f32_out = False
+    if route == "float32 slabs":
+        runtime.products = "library"                  # none of the engine's products takes it
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, 72, generator=g).to(torch.bfloat16)
+    w = torch.randn(333, 72, generator=g).to(torch.bfloat16)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        got = runtime.linear_f32_out(x.cuda(), w.cuda().contiguous())
+    assert got.dtype is torch.float32 and got.shape == (rows, 333)
+    want = x.double() @ w.double().t()
+    assert (got.double().cpu() - want).abs().max().item() < 2e-5 * want.abs().max().item()

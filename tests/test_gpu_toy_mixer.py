@@ -15,6 +15,9 @@ import plain_qwen2 as plain
 pytestmark = pytest.mark.gpu
 
 
+HYBRID_HEADS, HYBRID_THETA = 2, 10000.0
+
+
 def define_toy():
     from from_scratch_inference_engine_b200.config import (LayerCall, LayerSpec, ModelSpec,
                                                             PartSpec, register_architecture)
@@ -56,21 +59,30 @@ def define_toy():
         vocab: int
         decay: float
         eps: float
+        attention_layers: int = 0      # this many leading layers mix by attention instead
 
         @classmethod
         def from_dict(cls, d):
-            return cls(d["width"], d["layers"], d["vocab"], d["decay"], d["eps"])
+            return cls(d["width"], d["layers"], d["vocab"], d["decay"], d["eps"],
+                       d.get("attention_layers", 0))
 
         def to_dict(self):
             return {"architectures": ["ToyStateForCausalLM"], "width": self.width,
                     "layers": self.layers, "vocab": self.vocab, "decay": self.decay,
-                    "eps": self.eps}
+                    "eps": self.eps, "attention_layers": self.attention_layers}
 
         def build_spec(self):
             norm = PartSpec("rmsnorm", {"width": self.width, "eps": self.eps})
+            attention = PartSpec("gqa_attention", {
+                "hidden_size": self.width, "num_heads": HYBRID_HEADS, "num_kv_heads": 1,
+                "head_dim": self.width // HYBRID_HEADS, "qkv_bias": False, "window": 0,
+                "position": PartSpec("rotary", {"theta": HYBRID_THETA,
+                                                "rotary_dim": self.width // HYBRID_HEADS,
+                                                "max_position": 0})})
+            toy_mixer = PartSpec("toy_decaying_sum", {"width": self.width, "decay": self.decay})
             layers = tuple(LayerSpec(
                 prefix=f"blocks.{i}.", arrangement="prenorm",
-                mixer=PartSpec("toy_decaying_sum", {"width": self.width, "decay": self.decay}),
+                mixer=attention if i < self.attention_layers else toy_mixer,
                 feed_forward=PartSpec("swiglu", {"hidden_size": self.width,
                                                  "intermediate_size": 2 * self.width}),
                 mixer_norm=norm, feed_forward_norm=norm) for i in range(self.layers))
@@ -96,12 +108,19 @@ def plain_toy(folder, ids):
     for i in range(cfg["layers"]):
         p = f"blocks.{i}."
         y = plain.rms_norm(x, w[p + "mixer_norm.weight"], cfg["eps"])
-        state = torch.zeros(cfg["width"], dtype=torch.float64)
-        mixed = []
-        for t in range(len(ids)):
-            state = cfg["decay"] * state + y[t]
-            mixed.append(state)
-        x = x + plain.linear(torch.stack(mixed), w[p + "mixer.out.weight"])
+        if i < cfg.get("attention_layers", 0):
+            heads, hd, positions = HYBRID_HEADS, cfg["width"] // HYBRID_HEADS, list(range(len(ids)))
+            q = plain.rope(plain.linear(y, w[p + "mixer.q_proj.weight"]), heads, hd, HYBRID_THETA, positions)
+            k = plain.rope(plain.linear(y, w[p + "mixer.k_proj.weight"]), 1, hd, HYBRID_THETA, positions)
+            v = plain.linear(y, w[p + "mixer.v_proj.weight"])
+            x = x + plain.linear(plain.attention(q, k, v, heads, 1, hd), w[p + "mixer.o_proj.weight"])
+        else:
+            state = torch.zeros(cfg["width"], dtype=torch.float64)
+            mixed = []
+            for t in range(len(ids)):
+                state = cfg["decay"] * state + y[t]
+                mixed.append(state)
+            x = x + plain.linear(torch.stack(mixed), w[p + "mixer.out.weight"])
         y = plain.rms_norm(x, w[p + "feed_forward_norm.weight"], cfg["eps"])
         x = x + plain.linear(plain.silu_mul(plain.linear(y, w[p + "feed_forward.gate_proj.weight"]),
                                             plain.linear(y, w[p + "feed_forward.up_proj.weight"])),
@@ -151,3 +170,30 @@ def test_toy_mixer_generates_through_the_scheduler(toy):
         for token in engine.output(rid):
             assert int(plain_toy(toy, seq)[-1].argmax()) == token
             seq.append(token)
+
+
+def test_hybrid_of_attention_and_state_declines_prefix_sharing(tmp_path):
+    """An attention layer's pages could be shared between requests with a common prefix; the
+    state of the layer after it has no copy per page, so a request that skipped the shared
+    tokens would start from a wrong state (and from what the slot's last owner left).  The
+    cache manager therefore shares nothing for such a model, whatever the caller asks."""
+    config_class = define_toy()
+    try:
+        from from_scratch_inference_engine_b200 import (Engine, LoadedModel, SamplingParams,
+                                                        write_random_model)
+        folder = write_random_model(tmp_path / "hybrid", config_class(32, 2, 61, 0.8, 1e-5, 1),
+                                    seed=9, std=0.3)
+        model = LoadedModel.from_pretrained(folder, dtype="float32", max_positions=256)
+        engine = Engine(model, block_size=4, num_blocks=24, max_batch=1, max_step_tokens=8,
+                        enable_prefix_cache=True)
+        assert len(engine.runner.cache.groups) == 1 and not engine.runner.cache.prefix_enabled
+        stem = helpers.random_ids(61, 13, 5)
+        prompts = [stem + [3, 4], stem + [9], stem[:8] + [11, 12, 13]]
+        for prompt in prompts:                  # one slot: each request inherits the last one's
+            seq = list(prompt)
+            for token in engine.generate(prompt, SamplingParams(temperature=0.0), 5):
+                assert int(plain_toy(folder, seq)[-1].argmax()) == token
+                seq.append(token)
+        assert engine.prefix_hits() == 0
+    finally:
+        undefine_toy()

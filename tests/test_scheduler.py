@@ -194,6 +194,64 @@ def test_prefix_cache_on_equals_off_with_hits():
     assert outs[False] == outs[True]
 
 
+def test_prefix_hit_under_page_pressure_never_plans_more_than_is_free():
+    """A cached prefix page that only the cache holds counts as free until a new request
+    takes it: the plan of that step must not give the same page to a decode as well."""
+    s, cache = make(num_pages=8, page_size=4, prefix=True, max_step_tokens=64)
+    a = s.add(list(range(100, 109)), GREEDY, 2, -1, 0)     # 9 tokens: registers 2 full pages
+    run_all(s, cache)
+    assert s.sequences[a].status is SeqStatus.Finished and cache.free_pages() == [8]
+    b = s.add(list(range(200, 207)), GREEDY, 12, -1, 0)    # decodes across page edges
+    run_step(s, cache)
+    c = s.add(list(range(100, 108)) + list(range(300, 313)), GREEDY, 2, -1, 0)   # a's prefix + 13
+    run_all(s, cache)                                     # run_step reserves every planned item
+    assert cache.prefix_hits == 1
+    assert s.sequences[b].status is SeqStatus.Finished and s.sequences[c].status is SeqStatus.Finished
+    cache.clear_prefix_cache()
+    assert cache.free_pages() == [8]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_prefix_cache_under_pressure_random_orders(seed):
+    import random
+    rng = random.Random(seed)
+    s, cache = make(num_pages=12, page_size=4, prefix=True, max_step_tokens=24, max_batch=4)
+    stems = [[rng.randrange(90) for _ in range(12)] for _ in range(2)]
+    ids, outs = [], {}
+    for k in range(14):
+        prompt = stems[rng.randrange(2)][:rng.choice([4, 8, 12])] + \
+            [rng.randrange(90) for _ in range(rng.randrange(1, 9))]
+        ids.append((s.add(prompt, GREEDY, rng.randrange(1, 9), -1, 0), prompt))
+        for _ in range(rng.randrange(3)):
+            if s.has_work():
+                run_step(s, cache)
+    run_all(s, cache)
+    for rid, prompt in ids:
+        assert s.sequences[rid].output == alone(prompt, s.sequences[rid].max_tokens)
+    cache.clear_prefix_cache()
+    assert cache.free_pages() == [12]
+
+
+def test_small_window_pool_admits_with_the_default_token_budget():
+    """A windowed group's pool smaller than the first portion must not keep the request
+    waiting for ever: it starts with the pages there are and its portions are cut to them."""
+    needs = [NEED, CacheNeed(1, 16, window=21)]
+    s, cache = make(num_pages=[64, 6], page_size=8, needs=needs, max_step_tokens=2048)
+    rid = s.add(list(range(70)), GREEDY, 6, -1, 0)
+    log = []
+    run_all(s, cache, log)
+    assert len(s.sequences[rid].output) == 6
+    assert log[0][0][1] == 48                             # six pages of eight tokens
+    assert cache.free_pages() == [64, 6]
+
+
+def test_window_pool_that_can_never_hold_a_window_is_refused():
+    needs = [NEED, CacheNeed(1, 16, window=21)]
+    s, cache = make(num_pages=[64, 3], page_size=8, needs=needs)
+    with pytest.raises(ValueError, match="window of 21"):
+        s.add(list(range(10)), GREEDY, 4, -1, 0)
+
+
 def test_windowed_group_bounds_what_a_request_holds():
     needs = [NEED, CacheNeed(1, 16, window=8)]
     s, cache = make(num_pages=[40, 6], page_size=4, needs=needs, max_step_tokens=8)

@@ -96,3 +96,30 @@ def test_static_scratch_entry_refuses_what_does_not_fit(lib):
     assert code == TOO_SMALL
     assert b"more split scratch" in lib.fsie_attn_static_scratch_error(code)
     assert torch.isnan(got).all()                               # nothing ran
+
+
+def test_static_scratch_entry_at_exactly_its_limit_and_without_allocating(lib):
+    """8 splits x 128 tokens x 16 heads x (62 + 2) floats are exactly the 1,048,576 the
+    array holds.  The device's free memory is read before and after a repeated call: a caller
+    that has no memory left to give must not lose any to this entry point."""
+    from test_gpu_kernels import PagedCase, tol
+    case = PagedCase(torch.float32, 16, 2, 62, 16, items=[(300, 100), (900, 28)], seed=24)
+    assert lib.fsie_attn_static_scratch_floats(128, 16, 62, 8) == SCRATCH_FLOATS
+    code, got, want = call_both(lib, case, 8)              # first call: set-up may happen here
+    assert code == 0, lib.fsie_attn_static_scratch_error(code).decode()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    code, again, _ = call_both(lib, case, 8)
+    free_after, _ = torch.cuda.mem_get_info()
+    # what torch itself reserved for the test's own tensors is not the entry point's doing
+    grown_by_torch = torch.cuda.memory_reserved() - reserved_before
+    assert free_before - free_after <= grown_by_torch
+    bound = tol(torch.float32) * case.want.abs().max().item()
+    for out in (got, again):
+        assert (out - want).abs().max().item() < bound
+        assert (out - case.want).abs().max().item() < bound
+    # one more split does not fit, and absurd sizes are cut off instead of wrapping around
+    assert lib.fsie_attn_static_scratch_floats(128, 16, 62, 9) > SCRATCH_FLOATS
+    assert lib.fsie_attn_static_scratch_floats(2**31 - 1, 2**31 - 1, 2**31 - 3, 2**31 - 1) == SCRATCH_FLOATS + 1
+    assert lib.fsie_attn_static_scratch_floats(-5, 4, 64, 2) == -1
