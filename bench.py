@@ -17,9 +17,11 @@ A step is one decode step of a batch of 8 requests whose contexts end at 4,096 t
   points    decode tokens/s at batch 1 and 64
 
 Between timed steps nothing flushes L2: every step streams 15 GB of weights, far more
-than the 126 MB of L2.  The reference cannot be installed offline (its CMake build
-fetches Eigen, nlohmann/json and GoogleTest from the network), so `--impl reference`
-reports that and exits 0.  This engine runs on one GPU only: --gpus N > 1 exits 2.
+than the 126 MB of L2.  `--impl reference` runs the same shape and workload through the
+unmodified reference engine (its CUDA path compiled from its own sources by
+baseline/build_reference.py, since its CMake build needs the network) and prints the same
+line with "impl": "reference"; where that build is impossible it prints an `unavailable`
+line and exits 0.  This engine runs on one GPU only: --gpus N > 1 exits 2.
 """
 
 from __future__ import annotations
@@ -297,6 +299,57 @@ def long_context_workload(args) -> int:
     return 0
 
 
+def reference_arm(args) -> int:
+    """The same metric and shape through the unmodified reference engine (built from its own
+    sources by baseline/build_reference.py; its CUDA engine, CudaEngine::step, decodes the batch
+    and reads the chosen tokens back every step).  Nothing of this package runs on this arm."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_arm as arm
+    shape = dict(SHAPE_7B)
+    full_layers = shape["num_hidden_layers"]
+    layers = args.layers or full_layers
+    shape["num_hidden_layers"] = layers
+    steps, warmup = args.steps, max(args.warmup, 3)
+    clocks = ClockSampler()
+    clocks.start()
+    figures = arm.run(shape, args.batch, args.context, steps, warmup, args.prefill_tokens)
+    clock_record = clocks.stop()
+    if "unavailable" in figures:
+        print(json.dumps({"impl": "reference", "unavailable": figures["unavailable"]}))
+        return 0
+    value = figures["decode_tokens_per_s"]
+    record = {
+        "metric": "decode tok/s @ batch 8, context 4,096 (Qwen2.5-7B shape)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": figures["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic: random bf16 weights N(0,0.02) widened to fp32 by the reference's "
+                "loader, uniform token ids",
+        "impl": "reference",
+        "config": {"model": "Qwen2.5-7B shape", "global_batch": args.batch,
+                   "seq_len": args.context, "parallelism": "single GPU", "layers": layers,
+                   "layers_of_shape": full_layers, "hidden": shape["hidden_size"],
+                   "heads": shape["num_attention_heads"], "kv_heads": shape["num_key_value_heads"],
+                   "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"],
+                   "vocab": shape["vocab_size"], "prefill_tokens": args.prefill_tokens,
+                   "precision": "fp32 only: the reference has no other",
+                   "timing": "wall clock around CudaEngine::step, which synchronises the device "
+                             "and reads the tokens back every step",
+                   "l2": "not flushed: each step streams 30 GB of weights, L2 is 126 MB"},
+        # the reference engine has one way to step: ids and positions go to the device and the
+        # chosen tokens come back every step, so the figure above already is end to end
+        "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": figures["ms_per_step"],
+                "h2d_bytes_per_step": 16.0 * args.batch, "d2h_bytes_per_step": 8.0 * args.batch},
+        "prefill": {"value": (args.prefill_tokens * 1000.0 / figures["prefill_ms"]
+                              if figures["prefill_ms"] > 0 else None),
+                    "tokens": args.prefill_tokens, "ms": figures["prefill_ms"]},
+        "load_s": figures["load_s"], "fill_s": figures["fill_s"],
+        "clocks": clock_record,
+    }
+    print(json.dumps(record))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -318,16 +371,11 @@ def main() -> int:
     parser.add_argument("--num-blocks", type=int, default=16384)
     args = parser.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference cannot be installed offline: its CMake build fetches "
-                          "Eigen, nlohmann/json and GoogleTest from the network (pip install "
-                          "--no-index fails at FetchContent), and its CUDA path has no Python "
-                          "binding"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
         return 2
+    if args.impl == "reference":
+        return reference_arm(args)
     if args.workload == "serving":
         return serving_workload(args)
     if args.workload == "long":

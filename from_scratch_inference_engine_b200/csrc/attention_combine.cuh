@@ -1,5 +1,5 @@
 // Merge of split key ranges for the bfloat16 attention kernels (attention_mma.cu,
-// attention_tma.cu, attention_tcgen05.cu).  Needs HD (head size) defined before inclusion.
+// attention_tcgen05.cu).  Needs HD (head size) defined before inclusion.
 #pragma once
 
 namespace fsie {

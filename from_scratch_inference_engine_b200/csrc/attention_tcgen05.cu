@@ -68,14 +68,7 @@ constexpr uint32_t COL_S = 0, COL_O = STREAMS * BN;
 enum { ERR_TC_PRODUCER = 31, ERR_TC_MMA = 32, ERR_TC_SOFTMAX = 33, ERR_TC_LAYOUT = 34 };
 
 struct TcExtra { int entries, entry; int* error; };
-#ifdef FSIE_TC_TIMING
-// cycles spent by one softmax warp (with FSIE_TC_TIMING_MMA: by the MMA thread) per phase, summed
-// over all blocks (measurement builds only)
-__device__ unsigned long long fsie_tc_timing[10];
-#define TC_MARK(slot) do { const long long now_ = clock64(); phase_[slot] += (unsigned)(now_ - mark_); mark_ = now_; } while (0)
-#else
 #define TC_MARK(slot) do { } while (0)
-#endif
 
 }  // namespace fsie
 #include "attention_combine.cuh"
@@ -181,9 +174,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     unsigned char* ring = q_s + STREAMS * Q_BYTES;           // [slot][HALVES][128 keys][128 B]
     int& abort_flag = ctl.abort_flag;
 
-#ifdef FSIE_TC_TIMING
-    const long long block_begin_ = clock64();
-#endif
     // Blocks are handed out in the order of blockIdx.x, and the caller lists the tiles with the most
     // keys first: all kv heads of the longest tile start first, so that the last wave is short.
     const int tile = blockIdx.x / p.kv_heads, kvh = blockIdx.x % p.kv_heads, split = blockIdx.z;
@@ -304,21 +294,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         if (lane == 0 && ntiles > 0) {
             const uint32_t idesc_s = idesc_bf16(BM, BN, 0), idesc_o = idesc_bf16(BM, HD, 1);
             bool ok = true;
-#ifdef FSIE_TC_TIMING_MMA
-            unsigned long long t_ring = 0, t_p = 0;
-            const long long t_begin = clock64();
-#endif
             auto ring_wait = [&](int e) {            // the tile of ring entry e has arrived
-#ifdef FSIE_TC_TIMING_MMA
-                const long long t0_ = clock64();
-#endif
                 if (!mbar_wait(&ctl.ring_full[e % SLOTS], (e / SLOTS) & 1)) {
                     atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#ifdef FSIE_TC_TIMING_MMA
-                t_ring += clock64() - t0_;
-#endif
             };
             // Descriptors differ from one MMA to the next only by a constant in their address field
             // (16-byte units): the issuing thread adds it to a base made once.
@@ -328,9 +308,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                 const uint64_t kd = k_base + (uint64_t)(((2 * i) % SLOTS) * (KV_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-#ifdef FSIE_TC_SKIP_QK
-                    break;
-#endif
                     // 16 elements along the head: 32 bytes inside the swizzled row; 64: the next block
                     const uint32_t step = (k >> 2) * (ATOM_BYTES >> 4) + 2 * (k & 3);
                     mma_ss(tmem + COL_S + st * BN, qd + step, kd + step, idesc_s, k > 0);
@@ -345,24 +322,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             for (int st = 0; st < streams && ok; ++st) scores(st, 0);
             for (int i = 0; i < ntiles && ok; ++i) {
                 for (int st = 0; st < streams && ok; ++st) {
-#ifdef FSIE_TC_TIMING_MMA
-                    const long long t0_ = clock64();
-#endif
                     if (!mbar_wait(&ctl.p_ready[st], i & 1)) {
                         atomicExch(x.error, ERR_TC_MMA); atomicExch(&abort_flag, 1); ok = false; break;
                     }
-#ifdef FSIE_TC_TIMING_MMA
-                    t_p += clock64() - t0_;
-#endif
                     if (st == 0) ring_wait(2 * i + 1);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t vd = v_base + (uint64_t)(((2 * i + 1) % SLOTS) * (KV_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < BN / 16; ++k) {         // 16 keys per instruction
-#ifdef FSIE_TC_SKIP_PV
-                        break;
-#endif
                         // 16 keys of P: 8 columns of bfloat16 pairs in the stream's score columns;
                         // 16 keys of V: 16 rows of 128 bytes
                         mma_ts(tmem + COL_O + st * BN, tmem + COL_S + st * BN + k * 8, vd + (uint64_t)(k * (16 * 128 >> 4)),
@@ -377,12 +345,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
                     }
                 }
             }
-#ifdef FSIE_TC_TIMING_MMA
-            atomicAdd(&fsie_tc_timing[0], t_p);
-            atomicAdd(&fsie_tc_timing[1], t_ring);
-            atomicAdd(&fsie_tc_timing[2], (unsigned long long)(clock64() - t_begin) - t_p - t_ring);
-            atomicAdd(&fsie_tc_timing[6], (unsigned long long)ntiles);
-#endif
         }
     } else if ((warp - 2) / 4 < streams) {
         // ------------------------------------------------------------------ softmax, one thread per row
@@ -397,10 +359,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         const float sc = p.scale * 1.4426950408889634f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-#ifdef FSIE_TC_TIMING
-        unsigned phase_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        long long mark_ = clock64();
-#endif
         for (int i = 0; i < ntiles && ok; ++i) {
             // (decisions to give up are taken by whole warps: the tensor-memory accesses below are
             // warp-collective)
@@ -410,11 +368,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             TC_MARK(0);
-#ifdef FSIE_TC_NO_SOFTMAX
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&ctl.p_ready[st]);
-            continue;
-#endif
             const int k0 = kbegin + i * BN;
             // the row's 128 scores in registers: four reads in flight, one wait
             uint32_t sr[BN];
@@ -485,9 +438,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             mbar_arrive(&ctl.p_ready[st]);
             TC_MARK(5);
         }
-#if defined(FSIE_TC_TIMING) && !defined(FSIE_TC_TIMING_MMA)
-        const long long loop_end_ = clock64();
-#endif
         // ---- the last P V, then normalise and store (or hand a partial result to the merge)
         bool have = ok && ntiles > 0;
         if (have && !__all_sync(0xffffffffu, mbar_wait(&ctl.o_done[st], 0))) {
@@ -531,16 +481,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
             p.part_ml[idx * 2] = m_run == -INFINITY ? -INFINITY : m_run * p.scale;
             p.part_ml[idx * 2 + 1] = l_run;
         }
-#if defined(FSIE_TC_TIMING) && !defined(FSIE_TC_TIMING_MMA)
-        if (warp == 2 && lane == 0) {
-            for (int k = 0; k < 6; ++k) atomicAdd(&fsie_tc_timing[k], (unsigned long long)phase_[k]);
-            atomicAdd(&fsie_tc_timing[6], (unsigned long long)ntiles);
-            // everything outside the loop over key tiles: set-up before it, the output after it
-            atomicAdd(&fsie_tc_timing[7], (unsigned long long)(loop_end_ - block_begin_) -
-                                          (unsigned long long)(phase_[0] + phase_[1] + phase_[2] + phase_[3] + phase_[4] + phase_[5]));
-            atomicAdd(&fsie_tc_timing[8], (unsigned long long)(clock64() - loop_end_));
-        }
-#endif
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -576,12 +516,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
 #if HEAD_DIM == 128
 namespace dec {
 
-#ifndef FSIE_TCD_SLOTS
-#define FSIE_TCD_SLOTS 3
-#endif
 constexpr int KEYS = 128;               // keys per tile
 constexpr int ROWS = 16;                // query rows per tile
-constexpr int DSLOTS = FSIE_TCD_SLOTS;  // ring of K / V tiles; with 3 two blocks fit on an SM
+constexpr int DSLOTS = 3;               // ring of K / V tiles; with 3 two blocks fit on an SM
 constexpr int DTHREADS = 64 + 128;
 constexpr int QP_ATOM = ROWS * 128;     // 16 rows x 128 bytes of a K-major operand with N = 16
 constexpr int DQ_BYTES = HALVES * QP_ATOM;
@@ -639,9 +576,6 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnP
     unsigned char* p_s = q_s + DQ_BYTES;                     // [2 halves of the keys][16 rows][128 B]
     unsigned char* ring = p_s + DP_BYTES;                    // [slot][HALVES][128 keys][128 B]
     int& abort_flag = ctl.abort_flag;
-#ifdef FSIE_TC_TIMING
-    const long long block_begin_ = clock64();
-#endif
 
     const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
     const int group = p.heads / p.kv_heads;
@@ -820,11 +754,6 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnP
         for (int r = 0; r < ROWS; ++r)          // rows beyond the tile's count stay zero
             if (r >= nrows) *reinterpret_cast<bf16*>(p_mine + r * 128 + ((p_chunk ^ (r & 7)) << 4)) = __float2bfloat16_rn(0.f);
         bool fail = false, left = false;
-#ifdef FSIE_TC_TIMING
-        unsigned phase_[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        const long long loop_begin_ = clock64();
-        long long mark_ = loop_begin_;
-#endif
         for (int i = 0; i < ntiles; ++i) {
             if (!mbar_wait(&ctl.s_full[i & 1], (i >> 1) & 1)) fail = true;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -916,9 +845,6 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnP
             mbar_arrive(&ctl.p_ready);
             TC_MARK(5);
         }
-#ifdef FSIE_TC_TIMING
-        const long long loop_end_ = clock64();
-#endif
         // ---- the last P V, the row sums, then dimension t of every row
         bool have = !left && !fail && ntiles > 0;
         if (have && !mbar_wait(&ctl.pv_done, (ntiles - 1) & 1)) have = false;
@@ -956,14 +882,6 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnP
                 }
             }
         }
-#ifdef FSIE_TC_TIMING
-        if (warp == 2 && lane == 0) {
-            for (int k = 0; k < 6; ++k) atomicAdd(&fsie_tc_timing[k], (unsigned long long)phase_[k]);
-            atomicAdd(&fsie_tc_timing[6], (unsigned long long)ntiles);
-            atomicAdd(&fsie_tc_timing[7], (unsigned long long)(loop_begin_ - block_begin_));
-            atomicAdd(&fsie_tc_timing[8], (unsigned long long)(clock64() - loop_end_));
-        }
-#endif
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -982,17 +900,6 @@ using namespace fsie;
 
 extern "C" {
 
-#ifdef FSIE_TC_TIMING
-// out[0..5]: cycles per phase - of a softmax warp: wait for S, read S, maximum, wait for P V,
-// exponentials and P, hand-over; with FSIE_TC_TIMING_MMA of the MMA thread: wait for P, wait for
-// the ring, everything else - out[6]: tiles; the counters are reset.
-int fsie_attn_tc_timing(unsigned long long* out) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, fsie_tc_timing, sizeof(fsie_tc_timing));
-    if (e != cudaSuccess) return (int)e;
-    unsigned long long zero[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-    return (int)cudaMemcpyToSymbol(fsie_tc_timing, zero, sizeof(zero));
-}
-#endif
 
 int fsie_attn_tc_head_dim() { return HD; }
 int fsie_attn_tc_rows() { return STREAMS * BM; }
@@ -1019,7 +926,9 @@ int fsie_attn_tc_pages_map(void* map_out, const void* pages, long long total_row
     return 0;
 }
 
-// Tiles of 256 query rows.  Arguments as fsie_attn_tma (attention_tma.cu).
+// Tiles of 256 query rows.  Arguments as fsie_attn_mma (attention_mma.cu) without a row class,
+// with the pages given as a TMA descriptor (`pages_map`, made by fsie_attn_tc_pages_map over
+// `entries` cache entries per page, of which this launch reads `entry`) and the error flag.
 int fsie_attn_tc(const void* pages_map, int entries, int entry, const void* q, int q_ld, int page_size,
                  const int* block_tables, int bt_stride, const int* tile_item, const int* tile_row0, int tiles,
                  const int* item_qstart, const int* item_qlen, const int* item_pos0, void* out, int out_ld,

@@ -34,8 +34,6 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     "core": ("elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "sampling.cu"),
     # tensor-core attention, one build per head size: defines=("-DHEAD_DIM=128",)
     "attn_mma": ("attention_mma.cu",),
-    # the same attention fed by TMA (head sizes in steps of 64), one build per head size
-    "attn_tma": ("attention_tma.cu",),
     # attention for prompt portions with scores and outputs in tensor memory (head size 64 or 128)
     "attn_tc": ("attention_tcgen05.cu",),
     # tcgen05 / TMA matrix product for steps of few tokens
@@ -46,7 +44,7 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     "gemm_skinny": ("gemm_skinny.cu",),
 }
 # specialisations compiled by build_all() beside the default form of every library
-DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)], "attn_tma": [("-DHEAD_DIM=128",)],
+DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)],
                            "attn_tc": [("-DHEAD_DIM=128",)]}
 
 _loaded: Dict[Tuple[str, Tuple[str, ...]], ctypes.CDLL] = {}

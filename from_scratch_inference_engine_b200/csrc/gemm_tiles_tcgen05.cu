@@ -37,18 +37,11 @@ namespace fsie {
 
 constexpr int HALF = 128;                    // rows per block: of x (MMA M = 2 x 128) and of w (N = 2 x 128)
 constexpr int TILE = 256;                    // tile rows and accumulator columns
-#ifndef FSIE_GT_ATOMS
-#define FSIE_GT_ATOMS 2
-#endif
 constexpr int ATOM_K = 64;                   // k elements of one TMA box: 128 bytes, one swizzle row
-constexpr int ATOMS = FSIE_GT_ATOMS;         // boxes along k per stage and operand
+constexpr int ATOMS = 2;                     // boxes along k per stage and operand
 constexpr int BK = ATOM_K * ATOMS;           // k elements per stage
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 6 / ATOMS;
-#ifndef FSIE_GT_PREFETCH
-#define FSIE_GT_PREFETCH 0
-#endif
-constexpr int PREFETCH = FSIE_GT_PREFETCH;   // k-blocks of w asked into L2 ahead of the ring (0: none; it measured slower)
 constexpr uint32_t BOX_BYTES = HALF * ATOM_K * 2;        // 16 KB
 constexpr uint32_t STAGE_BYTES = 2 * ATOMS * BOX_BYTES;  // this block's rows of x, then its rows of w
 constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 4 * 2 * (32 * 128);   // ring + two output boxes per epilogue warp
@@ -86,10 +79,6 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_addr(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar) & FIRST_BLOCK_MASK) : "memory");
-}
-// Asks for a box to be brought from HBM into L2, without a destination in shared memory.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 // Arrival on the barrier at this offset in the first block of the pair.
 __device__ __forceinline__ void mbar_arrive_first_block(uint64_t* bar) {
@@ -141,9 +130,6 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 
 // Stores 32 consecutive outputs of one row, columns n .. n + 31 as far as they lie below N.
 __device__ __forceinline__ void store_row_chunk(const TileGemmParams& p, int row, int n, const float* v, bool vector_ok) {
-#ifdef FSIE_GT_NO_STORE
-    if (v[0] != 123.25f || v[7] != -77.f) return;
-#endif
     if (row >= p.M) return;
     if (p.out_f32) {
         float* dst = reinterpret_cast<float*>(p.y) + (size_t)row * p.ldy + n;
@@ -218,34 +204,22 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             const int n0 = (tile / p.m_tiles) * TILE_COLS;
             return EPI == EPI_SWIGLU ? (rank == 0 ? n0 : p.up_row0 + n0) : n0 + rank * HALF;
         };
-        // w comes from HBM (x stays in L2): its boxes are asked for PREFETCH k-blocks before the
-        // ring has room for them, so the ring only has to cover the latency of L2
-        auto prefetch_w = [&](int ahead) {
-            const int tile = pair + (ahead / kblocks) * pairs;
-            if (tile < total_tiles) tma_prefetch_2d(&map_w, (ahead % kblocks) * BK, w_row_of(tile));
-        };
-        for (int j = 0; j < PREFETCH; ++j) prefetch_w(j);
         for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
             const int m0 = (tile % p.m_tiles) * TILE + rank * HALF;
             const int w_row = w_row_of(tile);
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
                 const int s = it % STAGES;
-                if (PREFETCH > 0) prefetch_w(it + PREFETCH);
                 if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) {
                     atomicExch(p.error, ERR_TMA_WAIT); atomicExch(&abort_flag, 1);
                 }
                 if (*(volatile int*)&abort_flag) { ok = false; break; }
                 unsigned char* stage = smem + s * STAGE_BYTES;
-#ifdef FSIE_GT_NO_LOAD
-                if (rank == 0) mbar_arrive(&full_bar[s]);
-#else
                 if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);       // both blocks' boxes
 #pragma unroll
                 for (int a = 0; a < ATOMS; ++a) {
                     tma_load_2d_pair(stage + a * BOX_BYTES, &map_x, kb * BK + a * ATOM_K, m0, &full_bar[s]);
                     tma_load_2d_pair(stage + (ATOMS + a) * BOX_BYTES, &map_w, kb * BK + a * ATOM_K, w_row, &full_bar[s]);
                 }
-#endif
                 issued = it + 1;
             }
         }
@@ -283,9 +257,6 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     const uint64_t a = umma_desc(stage + at * BOX_BYTES), b = umma_desc(stage + (ATOMS + at) * BOX_BYTES);
 #pragma unroll
                     for (int k = 0; k < ATOM_K / UMMA_K; ++k) {
-#ifdef FSIE_GT_NO_MMA
-                        break;
-#endif
                         // 16 elements further along k: 32 bytes inside the swizzled row (address field in 16-byte units)
                         umma_bf16_pair(tmem + buf * TILE, a + 2 * k, b + 2 * k, idesc, (kb > 0 || at > 0 || k > 0) ? 1u : 0u);
                     }

@@ -304,7 +304,5 @@ class ModelRunner:
                     36: "tcgen05 decode attention: a tile or the softmax never arrived",
                     37: "tcgen05 decode attention: scores or outputs never completed",
                     38: "tcgen05 decode attention: shared memory does not start on a 1,024-byte "
-                        "boundary",
-                    41: "TMA-fed attention: the copy engine's stage never became free",
-                    42: "TMA-fed attention: a tile never arrived"}
+                        "boundary"}
             raise DeviceFault(what.get(code, f"device error flag {code}"))

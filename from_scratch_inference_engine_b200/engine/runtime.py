@@ -80,7 +80,7 @@ class Runtime:
 
     def pages_map(self, pages: torch.Tensor):
         """TMA descriptor of a cache group's page tensor (made once per tensor), or None when
-        the TMA-fed attention kernels do not take its head size or page size."""
+        the tcgen05 attention kernels do not take its head size or page size."""
         key = ("pages_map", pages.data_ptr())
         if key not in self._tables:
             head_dim, page_size = pages.shape[-1], pages.shape[-2]

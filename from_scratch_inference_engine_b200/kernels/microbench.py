@@ -124,11 +124,10 @@ def run_attention(args, timer, decode: bool):
     part_ml = torch.empty(max(1, nsplit * tokens * heads * 2), device="cuda")
     scale = 1.0 / math.sqrt(hd)
 
-    use_tma = args.variant == "tma" and row_class >= 0
     use_tc = args.variant == "tc" and row_class == 2
     use_tcd = args.variant == "tc" and row_class == 0 and hd in ops.ATTENTION_TC_DECODE_HEAD_DIMS
-    if use_tma or use_tc or use_tcd:
-        pages_map = ops.PagesMap(pages, "tc" if use_tc or use_tcd else "tma")
+    if use_tc or use_tcd:
+        pages_map = ops.PagesMap(pages, "tc")
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def launch():
@@ -140,10 +139,6 @@ def run_attention(args, timer, decode: bool):
             ops.attention_tc(pages_map, 0, q, q.stride(0), tables, tile_item, tile_row0,
                              tile_item.numel(), qstart, qlen, pos0, out, tokens, heads, kv_heads,
                              0, scale, error, nsplit, part_o, part_ml, None, 0)
-        elif use_tma:
-            ops.attention_tma(row_class, pages_map, 0, q, q.stride(0), tables, tile_item, tile_row0,
-                              tile_item.numel(), qstart, qlen, pos0, out, tokens, heads, kv_heads,
-                              0, scale, error, nsplit, part_o, part_ml, None, 0)
         elif row_class >= 0:
             ops.attention_mma(row_class, q, q.stride(0), pages[:, 0, 0], pages[:, 0, 1],
                               pages.stride(0), page, tables, tile_item, tile_row0,
@@ -156,32 +151,16 @@ def run_attention(args, timer, decode: bool):
                                   part_o, part_ml)
     ms = timer(launch)
     extra = {}
-    if (use_tc or use_tcd) and any("FSIE_TC_TIMING" in d for d in args.build_defines):
-        # cycles per key tile that one warp spent in each phase, summed over all blocks by the kernel
-        import ctypes
-        lib = ops.attn_tc(hd)
-        counters = (ctypes.c_ulonglong * 10)()
-        torch.cuda.synchronize()
-        lib.fsie_attn_tc_timing.argtypes = [ctypes.c_void_p]
-        lib.fsie_attn_tc_timing(counters)
-        names = (["wait_p", "wait_ring", "issue"] if any("TIMING_MMA" in d for d in args.build_defines)
-                 else ["wait_s", "read_s", "max", "wait_pv", "exp_p", "hand_over"])
-        extra["cycles_per_tile"] = {n: round(counters[k] / max(1, counters[6])) for k, n in enumerate(names)}
-        blocks = tile_item.numel() * kv_heads * nsplit
-        launches = args.warmup + args.iters
-        extra["cycles_per_block_before_the_loop"] = round(counters[7] / max(1, blocks * launches))
-        extra["cycles_per_block_after_the_loop"] = round(counters[8] / max(1, blocks * launches))
-        extra["tiles_per_block"] = round(counters[6] / max(1, blocks * launches), 2)
     elem = 2 if dtype is torch.bfloat16 else 4
     kv_bytes = args.batch * args.context * 2 * kv_heads * hd * elem
     io_bytes = kv_bytes + 2 * tokens * heads * hd * elem
     # causal: query t of a portion sees past + t + 1 keys
     pairs = args.batch * (new * past + new * (new + 1) / 2)
     flops = 4.0 * heads * hd * pairs
-    if use_tma or use_tc or use_tcd:
+    if use_tc or use_tcd:
         extra["error"] = int(error.item())
     extra.update({"nsplit": nsplit, "tiles": tile_item.numel(),
-                  "variant": ("tc" if use_tc else "tc_decode" if use_tcd else "tma" if use_tma else "mma")
+                  "variant": ("tc" if use_tc else "tc_decode" if use_tcd else "mma")
                   if row_class >= 0 else "generic"})
     return ms, io_bytes, flops, extra
 
@@ -281,7 +260,7 @@ def run(args):
               "frac_hbm": round(gbs / peak["hbm_gbs"], 3),
               "frac_bf16": round(tflops / peak["bf16_tflops"], 3), "peaks": peak["source"],
               "sizes": {k: v for k, v in vars(args).items()
-                        if k not in ("kernel", "dtype", "warmup", "iters", "no_flush", "build_defines")}}
+                        if k not in ("kernel", "dtype", "warmup", "iters", "no_flush")}}
     record.update(extra)
     print(json.dumps(record))
 
@@ -304,32 +283,14 @@ def main(argv=None) -> int:
     parser.add_argument("--n", type=int, default=37888)
     parser.add_argument("--k", type=int, default=3584)
     parser.add_argument("--nsplit", type=int, default=0, help="0 = the engine's choice")
-    parser.add_argument("--variant", default="mma", choices=["mma", "tma", "tc"],
-                        help="bfloat16 attention: mma.sync with cp.async loads, with TMA loads, "
-                             "or tcgen05 (prompt portions)")
+    parser.add_argument("--variant", default="mma", choices=["mma", "tc"],
+                        help="bfloat16 attention: mma.sync with cp.async loads, or tcgen05")
     parser.add_argument("--top-k", type=int, default=0)
     parser.add_argument("--top-p", type=float, default=1.0)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--no-flush", action="store_true")
-    parser.add_argument("--build-defines", default="", help="extra -D flags for the kernel library under "
-                        "test: a measurement build, e.g. '-DFSIE_TC_TIMING' (cycles per phase of the tcgen05 "
-                        "attention's softmax warps; with -DFSIE_TC_TIMING_MMA of its MMA thread) or "
-                        "'-DFSIE_GT_NO_MMA' / '-DFSIE_GT_NO_LOAD' / '-DFSIE_GT_NO_EPILOGUE' (the tiled product "
-                        "with a stage of its pipeline left out; results are then wrong on purpose)")
     args = parser.parse_args(argv)
-    args.build_defines = tuple(args.build_defines.split())
-    if args.build_defines:
-        # the measurement build replaces the library of the kernel under test for this process
-        from ..csrc import build
-        target = {"attention_prefill": "attn_tc",
-                  "attention_decode": "attn_tc" if args.variant == "tc" else "attn_mma"}.get(
-            args.kernel, "gemm_tiles" if args.kernel.startswith("gemm_tiles") else None)
-        if target is None:
-            raise SystemExit("--build-defines: no measurement build for this kernel")
-        plain_load = build.load_library
-        build.load_library = lambda name, defines=(): plain_load(
-            name, tuple(defines) + (args.build_defines if name == target else ()))
     run(args)
     return 0
 

@@ -321,28 +321,6 @@ def attention_mma(row_class: int, q: torch.Tensor, q_ld: int, k_pages: torch.Ten
     return out
 
 
-_attn_tma = {}
-ATTENTION_TMA_PAGES = (8, 16, 32, 64)
-
-
-def attn_tma(head_dim: int):
-    """The TMA-fed attention library for one head size (a multiple of 64)."""
-    if head_dim not in _attn_tma:
-        if head_dim % 64 or not 64 <= head_dim <= 256:
-            raise KernelError(f"TMA-fed attention takes head sizes 64..256 in steps of 64, "
-                              f"not {head_dim}")
-        lib = build.load_library("attn_tma", (f"-DHEAD_DIM={head_dim}",))
-        i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
-        lib.fsie_attn_tma_map_bytes.argtypes = []
-        lib.fsie_attn_tma_pages_map.argtypes = [p, p, ll, i, i]
-        lib.fsie_attn_tma.argtypes = [i, p, i, i, p, i, i, p, i, p, p, i, p, p, p, p, i, p, p,
-                                      i, i, i, i, i, i, f, p, i, p, p]
-        for name in ("fsie_attn_tma_map_bytes", "fsie_attn_tma_pages_map", "fsie_attn_tma"):
-            getattr(lib, name).restype = i
-        _attn_tma[head_dim] = lib
-    return _attn_tma[head_dim]
-
-
 _attn_tc = {}
 ATTENTION_TC_PAGES = (8, 16, 32, 64, 128)
 ATTENTION_TC_HEAD_DIMS = (64, 128)
@@ -372,21 +350,19 @@ def attn_tc(head_dim: int):
 
 class PagesMap:
     """TMA descriptor of one cache group's pages [pages, entries, 2, kv_heads, slots, head_dim]
-    (boxes of one page x 64 columns, 128-byte swizzle), as the TMA-fed attention kernels read it."""
+    (boxes of one page x 64 columns, 128-byte swizzle), as the tcgen05 attention kernels read it."""
 
-    def __init__(self, pages: torch.Tensor, kind: str = "tma"):
+    def __init__(self, pages: torch.Tensor, kind: str = "tc"):
         _need(pages, torch.bfloat16, "pages")
         num_pages, entries, two, kv_heads, page_size, head_dim = pages.shape
         if two != 2:
             raise KernelError("pages must be [pages, entries, 2, kv_heads, slots, head_dim]")
         self.pages, self.entries, self.page_size, self.head_dim = pages, entries, page_size, head_dim
         rows = num_pages * entries * 2 * kv_heads * page_size
-        if kind == "tc":
-            lib = attn_tc(head_dim)
-            size, encode = lib.fsie_attn_tc_map_bytes(), lib.fsie_attn_tc_pages_map
-        else:
-            lib = attn_tma(head_dim)
-            size, encode = lib.fsie_attn_tma_map_bytes(), lib.fsie_attn_tma_pages_map
+        if kind != "tc":
+            raise KernelError(f"PagesMap: unknown kind '{kind}'")
+        lib = attn_tc(head_dim)
+        size, encode = lib.fsie_attn_tc_map_bytes(), lib.fsie_attn_tc_pages_map
         self.buffer = ctypes.create_string_buffer(size + 64)
         offset = (-ctypes.addressof(self.buffer)) % 64
         self.ptr = ctypes.c_void_p(ctypes.addressof(self.buffer) + offset)
@@ -458,37 +434,6 @@ def attention_tc_decode(pages_map: PagesMap, entry: int, q: torch.Tensor, q_ld: 
         _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, head_dim, window, nsplit,
         float(scale), _ptr(combine_tokens), num_combine, _ptr(error), _stream()),
         "attention_tc_decode")
-    return out
-
-
-def attention_tma(row_class: int, pages_map: PagesMap, entry: int, q: torch.Tensor, q_ld: int,
-                  block_tables: torch.Tensor, tile_item: torch.Tensor, tile_row0: torch.Tensor,
-                  num_tiles: int, item_qstart: torch.Tensor, item_qlen: torch.Tensor,
-                  item_pos0: torch.Tensor, out: torch.Tensor, tokens: int, heads: int,
-                  kv_heads: int, window: int, scale: float, error: torch.Tensor, nsplit: int = 1,
-                  part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                  combine_tokens: Optional[torch.Tensor] = None, num_combine: int = 0
-                  ) -> torch.Tensor:
-    """bfloat16 attention of one row class with keys and values fetched by TMA."""
-    for name, t in (("block_tables", block_tables), ("tile_item", tile_item),
-                    ("tile_row0", tile_row0), ("item_qstart", item_qstart),
-                    ("item_qlen", item_qlen), ("item_pos0", item_pos0), ("error", error)):
-        _need(t, torch.int32, name)
-    _need(q, torch.bfloat16, "q", contiguous=False)
-    _need(out, torch.bfloat16, "out")
-    head_dim = pages_map.head_dim
-    if nsplit > 1:
-        _need(part_o, torch.float32, "part_o")
-        _need(part_ml, torch.float32, "part_ml")
-        if part_o.numel() < nsplit * tokens * heads * head_dim or \
-                part_ml.numel() < nsplit * tokens * heads * 2:
-            raise KernelError("attention_tma: split scratch is too small")
-    _check(attn_tma(head_dim).fsie_attn_tma(
-        row_class, pages_map.ptr, pages_map.entries, entry, _ptr(q), q_ld, pages_map.page_size,
-        _ptr(block_tables), block_tables.stride(0), _ptr(tile_item), _ptr(tile_row0), num_tiles,
-        _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0), _ptr(out), out.stride(0),
-        _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, head_dim, window, nsplit,
-        float(scale), _ptr(combine_tokens), num_combine, _ptr(error), _stream()), "attention_tma")
     return out
 
 

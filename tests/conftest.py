@@ -20,3 +20,13 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Largest relative difference between engine and plain logits that the replay tests saw,
+    per compute dtype and configuration: the bfloat16 bounds of the tests are set from these."""
+    import helpers
+    if helpers.OBSERVED:
+        terminalreporter.write_line("largest engine-plain logit difference relative to max(1, |logit|):")
+        for label in sorted(helpers.OBSERVED):
+            terminalreporter.write_line(f"  {label}: {helpers.OBSERVED[label]:.3e}")

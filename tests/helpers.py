@@ -158,6 +158,47 @@ def trace_mixed(requests: Dict[str, List[int]], seed: int = 0, max_live: int = 4
     return steps
 
 
+def trace_mixed_with_recompute(requests: Dict[str, List[int]], seed: int = 0, max_live: int = 4,
+                               decode_tail: int = 6):
+    """The mixed family with preemption as the step function sees it: now and then a live
+    request is released in the middle (everything it holds is given back) and fed again
+    from position 0 under another name, into pages that others have used meanwhile.
+    Returns (steps, requests with the names of the second runs added)."""
+    rng = random.Random(seed)
+    pending = list(requests.items())
+    names = dict(requests)
+    live: Dict[str, int] = {}
+    released = set()
+    steps = []
+    while pending or live:
+        while pending and len(live) < max_live and (not live or rng.random() < 0.7):
+            key, _ = pending.pop(0)
+            live[key] = 0
+        entries, ended = [], []
+        for key in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue
+            ids, at = names[key], live[key]
+            left = len(ids) - at
+            n = 1 if left <= decode_tail else min(rng.choice([2, 3, 5, 8, 13, 17]), left - decode_tail)
+            entries.append({"id": key, "tokens": ids[at:at + n], "want": list(range(n))})
+            live[key] = at + n
+            origin = key.split("~")[0]
+            if live[key] == len(ids):
+                ended.append(key)
+                del live[key]
+            elif origin not in released and live[key] >= 9 and rng.random() < 0.3:
+                # preempted: released after this step, recomputed later from its first token
+                released.add(origin)
+                ended.append(key)
+                del live[key]
+                names[origin + "~again"] = ids
+                pending.insert(0, (origin + "~again", ids))
+        if entries:
+            steps.append({"step": len(steps), "entries": entries, "end": ended})
+    return steps, names
+
+
 def live_tokens_needed(steps: List[dict], round_to: int = 64) -> int:
     """Largest sum over live requests of their token counts, each rounded up to `round_to`."""
     held: Dict[str, int] = {}
@@ -207,18 +248,26 @@ def run_trace_in_process(runner, steps: List[dict]):
     return collect_rows(steps, outputs)
 
 
-def compare_rows(rows, requests, model_dir, rel: float):
-    """Largest |engine - plain| over all rows against rel * max(1, max |plain|)."""
-    worst, scale = 0.0, 1.0
+OBSERVED: Dict[str, float] = {}      # label -> largest relative difference seen (for reports)
+
+
+def compare_rows(rows, requests, model_dir, rel: float, label: str = ""):
+    """Every row's largest |engine - plain| against rel * max(1, max |plain| of that row).
+    Returns (largest difference, largest |plain|, rows beyond the bound); the largest
+    difference relative to its row's bound base is kept in OBSERVED[label]."""
+    worst, scale, relative = 0.0, 1.0, 0.0
     mismatched = []
     for (key, pos), row in sorted(rows.items()):
         want = plain_logits(model_dir, requests[key])[pos]
-        scale = max(scale, float(np.abs(want).max()))
+        base = max(1.0, float(np.abs(want).max()))
+        scale = max(scale, base)
         diff = float(np.abs(row.astype(np.float64) - want).max())
-        if diff > worst:
-            worst = diff
-        if diff > rel * max(1.0, float(np.abs(want).max())):
+        worst = max(worst, diff)
+        relative = max(relative, diff / base)
+        if diff > rel * base:
             mismatched.append((key, pos, diff))
+    if label:
+        OBSERVED[label] = max(OBSERVED.get(label, 0.0), relative)
     return worst, scale, mismatched
 
 

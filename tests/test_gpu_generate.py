@@ -49,8 +49,8 @@ def test_greedy_generation_through_llm(folders, name, block_size, dtype):
                                       1e-5 if dtype == "float32" else 2e-2)
         if dtype == "float32":
             assert agreed == 8
-    assert llm.engine.runner.cache.free_pages()[0] + 0 >= 0
     llm.engine.runner.cache.check()
+    assert llm.engine.runner.cache.free_pages() == [64]
 
 
 def test_model_forward_entry_point(folders):
@@ -88,17 +88,31 @@ def test_two_concurrent_requests_equal_each_alone(folders):
     assert engine.stats()["tokens_prefilled"] == 34
 
 
-def test_pages_run_out_preemption_recomputes_to_the_same_tokens(folders):
+def same_or_near_tie(folder, prompts, outputs, want, dtype):
+    """float32: the tokens are the expected ones.  bfloat16: another batch may round otherwise
+    (other key splits, another product kernel), so each request's tokens must agree with the
+    plain implementation up to a first difference that is a near tie of the plain logits."""
+    if dtype == "float32":
+        assert outputs == want
+        return
+    for prompt, out, expected in zip(prompts, outputs, want):
+        assert len(out) == len(expected)
+        assert_greedy_agrees(folder, prompt, out, 2e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pages_run_out_preemption_recomputes_to_the_same_tokens(folders, dtype):
     from from_scratch_inference_engine_b200 import SamplingParams
     greedy = SamplingParams(temperature=0.0)
-    prompts = [helpers.random_ids(256, 3, s) for s in (5, 6)]
-    alone = [engine_for(folders["A"]).generate(p, greedy, 12) for p in prompts]
-    engine = engine_for(folders["A"], num_blocks=4)          # 16 tokens of cache in all
+    prompts = [helpers.random_ids(384, 5, s) for s in (5, 6)]
+    alone = [engine_for(folders["B"], dtype, block_size=8).generate(p, greedy, 12) for p in prompts]
+    engine = engine_for(folders["B"], dtype, block_size=8, num_blocks=3)     # 24 tokens of cache in all
     ids = [engine.add_request(p, greedy, 12) for p in prompts]
     engine.run_until_done()
     assert engine.preemptions() > 0
-    assert [engine.output(i) for i in ids] == alone
-    assert engine.runner.cache.free_pages() == [4]
+    same_or_near_tie(folders["B"], prompts, [engine.output(i) for i in ids], alone, dtype)
+    assert engine.runner.cache.free_pages() == [3]
+    engine.runner.cache.check()
 
 
 def test_temperature_sampling_does_not_depend_on_batching_or_preemption(folders):
@@ -134,18 +148,19 @@ def test_eos_stops_and_is_kept(folders):
     assert out == free_run[:free_run.index(eos) + 1]
 
 
-def test_prefix_cache_on_equals_off_with_hits(folders):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefix_cache_on_equals_off_with_hits(folders, dtype):
     from from_scratch_inference_engine_b200 import SamplingParams
     greedy = SamplingParams(temperature=0.0)
-    shared = helpers.random_ids(256, 26, 9)
-    tails = [helpers.random_ids(256, 5, s) for s in (1, 2, 3)]
+    shared = helpers.random_ids(384, 26, 9)
+    tails = [helpers.random_ids(384, 5, s) for s in (1, 2, 3)]
     outs = {}
     for on in (False, True):
-        engine = engine_for(folders["A"], enable_prefix_cache=on)
+        engine = engine_for(folders["B"], dtype, block_size=8, enable_prefix_cache=on)
         outs[on] = [engine.generate(shared + tail, greedy, 6) for tail in tails]
         assert (engine.prefix_hits() > 0) == on
         engine.runner.cache.check()
-    assert outs[True] == outs[False]
+    same_or_near_tie(folders["B"], [shared + t for t in tails], outs[True], outs[False], dtype)
 
 
 def test_windowed_model_generates_within_a_small_window_pool(folders):
@@ -168,7 +183,8 @@ def test_requests_beyond_the_pool_are_refused(folders):
         engine.add_request([1, 256], None, 2)
 
 
-def test_overlapped_steps_give_the_same_tokens_as_one_step_at_a_time(folders):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_steps_give_the_same_tokens_as_one_step_at_a_time(folders, dtype):
     """The engine launches a step before it has read the tokens of the step before it (their
     ids enter the batch on the device).  Same outputs as without the overlap, with requests
     that stop at an end-of-sequence token (one token run for nothing and dropped), stop at
@@ -181,14 +197,17 @@ def test_overlapped_steps_give_the_same_tokens_as_one_step_at_a_time(folders):
               SamplingParams(temperature=0.0), SamplingParams(temperature=1.2, top_k=30, seed=6),
               SamplingParams(temperature=0.0), SamplingParams(temperature=0.0),
               SamplingParams(temperature=0.7, top_p=0.8, seed=7)]
+    if dtype == "bfloat16":
+        # a draw near a step of the distribution would tell nothing about the overlap: greedy only
+        params = [SamplingParams(temperature=0.0)] * len(params)
     lengths = [9, 14, 1, 11, 20, 7, 13]
-    free_run = engine_for(folders["B"], block_size=8, pipeline=False).generate(prompts[4], params[4], 20)
+    free_run = engine_for(folders["B"], dtype, block_size=8, pipeline=False).generate(prompts[4], params[4], 20)
     eos = {4: free_run[6]}                       # request 4 stops where that token first appears
     stopped = free_run[:free_run.index(free_run[6]) + 1]
     results = {}
     for pipeline in (False, True):
         for blocks in (64, 9):                   # roomy; 72 tokens of cache: forces preemption
-            engine = engine_for(folders["B"], block_size=8, num_blocks=blocks, max_batch=4,
+            engine = engine_for(folders["B"], dtype, block_size=8, num_blocks=blocks, max_batch=4,
                                 enable_prefix_cache=True, pipeline=pipeline)
             ids = [engine.add_request(p, q, n, eos_id=eos.get(i, -1))
                    for i, (p, q, n) in enumerate(zip(prompts, params, lengths))]
@@ -200,9 +219,19 @@ def test_overlapped_steps_give_the_same_tokens_as_one_step_at_a_time(folders):
                 assert engine.preemptions() > 0
             engine.runner.raise_on_device_error()
     first = results[False, 64]
-    assert first[4] == stopped and len(stopped) < 20
-    assert [len(o) for o in first] == [9, 14, 1, 11, len(stopped), 7, 13]
-    assert all(other == first for other in results.values())
+    if dtype == "float32":
+        assert first[4] == stopped and len(stopped) < 20
+        assert [len(o) for o in first] == [9, 14, 1, 11, len(stopped), 7, 13]
+        assert all(other == first for other in results.values())
+        return
+    for outputs in results.values():
+        for index, (prompt, out) in enumerate(zip(prompts, outputs)):
+            if index == 4:        # stops at its end-of-sequence token, wherever that comes
+                assert out[-1] == eos[4] or len(out) == 20
+                assert eos[4] not in out[:-1]
+            else:
+                assert len(out) == lengths[index]
+            assert_greedy_agrees(folders["B"], prompt, out, 2e-2)
 
 
 def test_warm_up_captures_the_decode_graphs_and_changes_no_token(folders):

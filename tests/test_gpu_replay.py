@@ -9,9 +9,18 @@ from helpers import TINY
 
 pytestmark = pytest.mark.gpu
 
-# float32: the engine's 32-bit sums against the plain 64-bit ones; bfloat16: activations
-# rounded to 8 bits of mantissa at every product, relative to the largest logit.
-TOLERANCE = {"float32": 1e-4, "bfloat16": 4e-2}
+# float32: the engine's 32-bit sums against the plain 64-bit ones.  bfloat16: activations are
+# rounded to 8 bits of mantissa at every product; how far that moves the logits depends on the
+# model (depth, widths, the size of its weights), so each configuration has its own bound:
+# about 2.5 times the largest difference seen over all families and kernel choices (the terminal
+# summary of a GPU run prints what it saw), relative to max(1, the row's largest |logit|).
+FLOAT32_BOUND = 1e-4
+BFLOAT16_BOUND = {"A": 4e-2, "B": 4e-2, "C": 4e-2, "D": 4e-2, "E": 4e-2, "F": 4e-2}
+
+
+def bound(dtype, name):
+    return FLOAT32_BOUND if dtype == "float32" else BFLOAT16_BOUND[name]
+
 
 REQUESTS = {
     "A": {"a": 100, "b": 37, "c": 64, "d": 81, "e": 5, "f": 49},
@@ -45,10 +54,12 @@ def build_runner(folder, dtype, max_tokens, page_size, **runtime_options):
 
 
 FAMILIES = {
-    "whole": lambda r, seed: helpers.trace_whole(r),
-    "tail": lambda r, seed: helpers.trace_tail_by_one(r),
-    "portions": lambda r, seed: helpers.trace_portions(r, seed),
-    "mixed": lambda r, seed: helpers.trace_mixed(r, seed),
+    "whole": lambda r, seed: (helpers.trace_whole(r), r),
+    "tail": lambda r, seed: (helpers.trace_tail_by_one(r), r),
+    "portions": lambda r, seed: (helpers.trace_portions(r, seed), r),
+    "mixed": lambda r, seed: (helpers.trace_mixed(r, seed), r),
+    # released in the middle and fed again from position 0 (preemption with recompute)
+    "recompute": helpers.trace_mixed_with_recompute,
 }
 
 
@@ -57,14 +68,16 @@ FAMILIES = {
 @pytest.mark.parametrize("name,page_size", [("A", 4), ("B", 8), ("C", 16), ("D", 16), ("E", 16),
                                             ("F", 32)])
 def test_replay_matches_plain(folders, name, page_size, family, dtype):
-    requests = requests_for(name)
-    steps = FAMILIES[family](requests, 11)
+    steps, requests = FAMILIES[family](requests_for(name), 11)
     # the pool holds exactly what the live requests need, so pages are used again
     need = helpers.live_tokens_needed(steps, round_to=page_size)
     runner = build_runner(folders[name], dtype, need, page_size)
     rows = helpers.run_trace_in_process(runner, steps)
-    assert len(rows) == sum(len(v) for v in requests.values())
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], TOLERANCE[dtype])
+    assert len(rows) == sum(len(e["tokens"]) for step in steps for e in step["entries"])
+    if family != "recompute":
+        assert len(rows) == sum(len(v) for v in requests.values())
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], bound(dtype, name),
+                                             f"{dtype} {name}")
     assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
     assert all(pool.num_free == pool.num_pages for pool in runner.cache.pools)
 
@@ -76,7 +89,7 @@ def test_first_tokens_of_a_sequence(folders, dtype):
     for steps in (helpers.trace_whole(requests), helpers.trace_tail_by_one(requests, tail=2)):
         runner = build_runner(folders["A"], dtype, 64, 4)
         rows = helpers.run_trace_in_process(runner, steps)
-        _, _, bad = helpers.compare_rows(rows, requests, folders["A"], TOLERANCE[dtype])
+        _, _, bad = helpers.compare_rows(rows, requests, folders["A"], bound(dtype, "A"), f"{dtype} A")
         assert not bad
 
 
@@ -88,7 +101,7 @@ def test_long_decoding(folders, dtype):
     steps = helpers.trace_tail_by_one(requests, tail=200)
     runner = build_runner(folders["B"], dtype, 256, 8)
     rows = helpers.run_trace_in_process(runner, steps)
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders["B"], TOLERANCE[dtype])
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders["B"], bound(dtype, "B"), f"{dtype} B")
     assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
 
 
@@ -112,7 +125,7 @@ def test_captured_decode_steps_equal_uncaptured_ones(folders, dtype):
         for key, row in captured.items():
             assert np.abs(row - direct[key]).max() < 2e-5, key
     for rows in (captured, direct):
-        worst, scale, bad = helpers.compare_rows(rows, requests, folders["B"], TOLERANCE[dtype])
+        worst, scale, bad = helpers.compare_rows(rows, requests, folders["B"], bound(dtype, "B"), f"{dtype} B")
         assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
 
 
@@ -134,13 +147,12 @@ def test_cutting_does_not_change_float32_beyond_rounding(folders):
 def test_replay_with_the_few_token_product_on_every_matrix(folders, name, page_size, family):
     """The tcgen05 product that steps of up to 16 tokens use is reserved for large matrices;
     here it is forced onto the tiny models' matrices so that replay covers it too."""
-    requests = requests_for(name)
-    steps = FAMILIES[family](requests, 11)
+    steps, requests = FAMILIES[family](requests_for(name), 11)
     need = helpers.live_tokens_needed(steps, round_to=page_size)
     runner = build_runner(folders[name], "bfloat16", need, page_size, few_token_min_elements=0)
     assert runner.runtime._few_token_weights
     rows = helpers.run_trace_in_process(runner, steps)
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], TOLERANCE["bfloat16"])
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], bound("bfloat16", name), f"bfloat16 {name}")
     assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
 
 
@@ -149,8 +161,7 @@ def test_replay_with_the_few_token_product_on_every_matrix(folders, name, page_s
 def test_replay_with_the_tiled_product_on_every_matrix(folders, name, page_size, family, monkeypatch):
     """Steps of more than 16 tokens take the tiled tcgen05 product (bias and SwiGLU in its
     epilogue) for every matrix, however few tiles that makes at these sizes."""
-    requests = requests_for(name)
-    steps = FAMILIES[family](requests, 5)
+    steps, requests = FAMILIES[family](requests_for(name), 5)
     need = helpers.live_tokens_needed(steps, round_to=page_size)
     runner = build_runner(folders[name], "bfloat16", need, page_size, tiled_min_tiles=1)
     assert runner.runtime._tiled_weights
@@ -158,7 +169,7 @@ def test_replay_with_the_tiled_product_on_every_matrix(folders, name, page_size,
     calls, original = [], ops.gemm_tiles
     monkeypatch.setattr(ops, "gemm_tiles", lambda *a, **k: (calls.append(1), original(*a, **k))[1])
     rows = helpers.run_trace_in_process(runner, steps)
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], TOLERANCE["bfloat16"])
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], bound("bfloat16", name), f"bfloat16 {name}")
     assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
     assert len(calls) >= 4 * len(runner.model.blocks)
 
@@ -167,8 +178,7 @@ def test_replay_with_the_tiled_product_on_every_matrix(folders, name, page_size,
 def test_replay_with_the_tcgen05_kernel_for_decoded_tokens(folders, family, monkeypatch):
     """Decoded tokens and portions of up to 16 rows take the tcgen05 attention kernel only when
     they fill the GPU; here it is forced onto a handful of requests (head size 128)."""
-    requests = requests_for("F")
-    steps = FAMILIES[family](requests, 7)
+    steps, requests = FAMILIES[family](requests_for("F"), 7)
     need = helpers.live_tokens_needed(steps, round_to=16)
     runner = build_runner(folders["F"], "bfloat16", need, 16, decode_tcgen05_min_blocks=1)
     from from_scratch_inference_engine_b200.kernels import ops
@@ -176,7 +186,7 @@ def test_replay_with_the_tcgen05_kernel_for_decoded_tokens(folders, family, monk
     monkeypatch.setattr(ops, "attention_tc_decode",
                         lambda *a, **k: (calls.append(1), original(*a, **k))[1])
     rows = helpers.run_trace_in_process(runner, steps)
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders["F"], TOLERANCE["bfloat16"])
+    worst, scale, bad = helpers.compare_rows(rows, requests, folders["F"], bound("bfloat16", "F"), "bfloat16 F")
     assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
     assert calls
     if family == "tail":

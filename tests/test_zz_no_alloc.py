@@ -73,7 +73,7 @@ def call_both(lib, case, nsplit):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_static_scratch_entry_matches_the_ordinary_one_twice_in_a_row(lib, dtype):
-    from test_gpu_kernels import PagedCase, tol
+    from test_gpu_kernels import PagedCase, assert_rows_close
     first = PagedCase(dtype, 14, 2, 64, 16, items=[(700, 1), (0, 3), (301, 1), (33, 2)], seed=21)
     second = PagedCase(dtype, 14, 2, 64, 16, items=[(90, 2), (512, 1), (5, 1)], seed=22)
     for case, nsplit in ((first, 6), (second, 3), (second, 1)):
@@ -82,9 +82,8 @@ def test_static_scratch_entry_matches_the_ordinary_one_twice_in_a_row(lib, dtype
         code, got, want = call_both(lib, case, nsplit)
         assert code == 0, lib.fsie_attn_static_scratch_error(code).decode()
         assert torch.isfinite(got).all()
-        bound = tol(dtype) * case.want.abs().max().item()
-        assert (got - want).abs().max().item() < bound          # against the ordinary entry
-        assert (got - case.want).abs().max().item() < bound     # and against the plain answer
+        assert_rows_close(got, want, case, dtype)               # against the ordinary entry
+        assert_rows_close(got, case.want, case, dtype)          # and against the plain answer
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit(lib):
@@ -102,7 +101,7 @@ def test_static_scratch_entry_at_exactly_its_limit_and_without_allocating(lib):
     """8 splits x 128 tokens x 16 heads x (62 + 2) floats are exactly the 1,048,576 the
     array holds.  The device's free memory is read before and after a repeated call: a caller
     that has no memory left to give must not lose any to this entry point."""
-    from test_gpu_kernels import PagedCase, tol
+    from test_gpu_kernels import PagedCase, assert_rows_close
     case = PagedCase(torch.float32, 16, 2, 62, 16, items=[(300, 100), (900, 28)], seed=24)
     assert lib.fsie_attn_static_scratch_floats(128, 16, 62, 8) == SCRATCH_FLOATS
     code, got, want = call_both(lib, case, 8)              # first call: set-up may happen here
@@ -115,10 +114,9 @@ def test_static_scratch_entry_at_exactly_its_limit_and_without_allocating(lib):
     # what torch itself reserved for the test's own tensors is not the entry point's doing
     grown_by_torch = torch.cuda.memory_reserved() - reserved_before
     assert free_before - free_after <= grown_by_torch
-    bound = tol(torch.float32) * case.want.abs().max().item()
     for out in (got, again):
-        assert (out - want).abs().max().item() < bound
-        assert (out - case.want).abs().max().item() < bound
+        assert_rows_close(out, want, case, torch.float32)
+        assert_rows_close(out, case.want, case, torch.float32)
     # one more split does not fit, and absurd sizes are cut off instead of wrapping around
     assert lib.fsie_attn_static_scratch_floats(128, 16, 62, 9) > SCRATCH_FLOATS
     assert lib.fsie_attn_static_scratch_floats(2**31 - 1, 2**31 - 1, 2**31 - 3, 2**31 - 1) == SCRATCH_FLOATS + 1
