@@ -11,10 +11,15 @@ A step is one decode step of a batch of 8 requests whose contexts end at 4,096 t
   e2e       the same through the Python entry point (`Engine.step`): every step copies
             its inputs from pinned host memory and reads the chosen tokens back
   prefill   one 2,048-token prompt through the step function: tokens/s, ms and the
-            fraction of the measured bf16 matrix peak
+            fraction of the measured bf16 matrix peak; `points`: four such prompts in one
+            step, and one prompt in portions of 512 tokens
   roofline  bytes the decode step must read (every weight once + the live requests'
             keys and values) / its time, against the measured copy bandwidth
-  points    decode tokens/s at batch 1 and 64
+  points    decode tokens/s at batch 1 and 64 (32 timed steps or more)
+  decode_by_context  the headline batch with contexts ending at 2,048 / 3,072 / 4,096 tokens
+  fp32      the true 32-bit path of the same model (own FFMA products, float32 cache): decode
+            tokens/s with its HBM fraction (28 GB of weights per step) and the prefill of one
+            prompt against the nominal FFMA peak
 
 Between timed steps nothing flushes L2: every step streams 15 GB of weights, far more
 than the 126 MB of L2.  `--impl reference` runs the same shape and workload through the
@@ -45,6 +50,9 @@ SHAPE_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidd
                 tie_word_embeddings=False, max_position_embeddings=32768,
                 use_sliding_window=False)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# FFMA peak of the float32 path (no tensor-core mode): 148 SMs x 128 lanes x 2 flop x 1.965 GHz,
+# nominal; the measured-peaks file has no float32 figure
+FP32_FFMA_TFLOPS = 74.4
 
 
 def peaks():
@@ -362,6 +370,12 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has")
     parser.add_argument("--prefill-tokens", type=int, default=2048)
     parser.add_argument("--points", default="1,64", help="extra decode batch sizes ('' = none)")
+    parser.add_argument("--contexts", default="2048,3072,4096",
+                        help="contexts at which decoding at --batch is also timed ('' = none)")
+    parser.add_argument("--dtype", default="bf16", choices=["bf16", "bfloat16", "fp32", "float32"],
+                        help="compute dtype of the whole run (the default run adds a short fp32 section)")
+    parser.add_argument("--fp32-steps", type=int, default=8,
+                        help="decode steps timed on the float32 path after the bf16 run (0 = skip)")
     parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long"],
                         help="decode: the default measurement; serving: continuous batching of 256 "
                              "requests at the 1.5B shape; long: the 14B shape, decode at batch 32 with "
@@ -397,7 +411,9 @@ def main() -> int:
     steps, warmup = args.steps, max(args.warmup, 3)
     page = 16
     rng = np.random.default_rng(0)
-    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16",
+    compute = "bfloat16" if args.dtype in ("bf16", "bfloat16") else "float32"
+    bytes_per = 2 if compute == "bfloat16" else 4
+    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype=compute,
                                     max_positions=args.context + 64)
     device = model.runtime.device
 
@@ -422,11 +438,12 @@ def main() -> int:
             handles.append(handle)
         return handles
 
-    def decode_rate(batch, count, warm):
-        """Device-timed decode: `count` steps of `batch` single tokens with device argmax."""
-        start_len = args.context - (count + warm)
-        pages = batch * (-(-args.context // page) + 1)
-        runner = ModelRunner(model.model, model.runtime, page_size=page, num_pages=pages,
+    def decode_rate(use_model, batch, count, warm, context_end):
+        """Device-timed decode: `count` steps of `batch` single tokens with device argmax, the
+        last of which brings the contexts to `context_end` tokens.  (ms per step, launches)"""
+        start_len = context_end - (count + warm)
+        pages = batch * (-(-context_end // page) + 1)
+        runner = ModelRunner(use_model.model, use_model.runtime, page_size=page, num_pages=pages,
                              max_requests=batch)
         handles = fill(runner, batch, start_len)
         tokens = rng.integers(0, config.vocab_size, size=(count + warm, batch))
@@ -446,9 +463,49 @@ def main() -> int:
         torch.cuda.empty_cache()
         return ms, launches
 
+    def step_bytes(batch, context_mid, element_bytes):
+        """What a decode step has to read: every weight once and the live requests' keys and values."""
+        return (weight_bytes(config, layers) + batch * context_mid * kv_bytes_per_token(config, layers)) \
+            * element_bytes / 2
+
+    def prefill_figures(use_model, tokens, repeat=3):
+        """One prompt whole, four prompts in one step, and one prompt in portions of 512 tokens."""
+        runner = ModelRunner(use_model.model, use_model.runtime, page_size=page,
+                             num_pages=4 * (tokens // page + 1), max_requests=4,
+                             max_step_tokens=4 * tokens)
+        prompts = [rng.integers(0, config.vocab_size, size=tokens).tolist() for _ in range(4)]
+
+        def whole(index):
+            handle = runner.cache.open(("p", index))
+            runner.step([StepEntry(handle, prompts[index % 4], [tokens - 1])])
+            runner.cache.close(handle)
+
+        def four(index):
+            handles = [runner.cache.open(("f", index, r)) for r in range(4)]
+            runner.step([StepEntry(h, prompts[r], [tokens - 1]) for r, h in enumerate(handles)])
+            for handle in handles:
+                runner.cache.close(handle)
+
+        def portions(index):
+            handle = runner.cache.open(("c", index))
+            for at in range(0, tokens, 512):
+                last = at + 512 >= tokens
+                runner.step([StepEntry(handle, prompts[index % 4][at:at + 512],
+                                       [len(prompts[index % 4][at:at + 512]) - 1] if last else [])])
+            runner.cache.close(handle)
+        out = {}
+        for name, fn, count in (("whole", whole, tokens), ("x4", four, 4 * tokens),
+                                ("portions_512", portions, tokens)):
+            fn(0)
+            out[name] = (min(timed(fn, 1) for _ in range(repeat)), count)
+        runner.raise_on_device_error()
+        del runner
+        torch.cuda.empty_cache()
+        return out
+
     clocks = ClockSampler()
     clocks.start()
-    ms_step, launches = decode_rate(args.batch, steps, warmup)
+    ms_step, launches = decode_rate(model, args.batch, steps, warmup, args.context)
     clock_record = clocks.stop()
     value = args.batch * 1000.0 / ms_step
 
@@ -476,44 +533,64 @@ def main() -> int:
     del engine
     torch.cuda.empty_cache()
 
-    # ---- prefill of one prompt
+    # ---- prefill: one prompt whole (the headline), four in one step, one in portions of 512
     tokens = args.prefill_tokens
-    runner = ModelRunner(model.model, model.runtime, page_size=page,
-                         num_pages=4 * (tokens // page + 1), max_requests=4)
-    prompts = [rng.integers(0, config.vocab_size, size=tokens).tolist() for _ in range(4)]
-
-    def prefill(index):
-        handle = runner.cache.open(("p", index))
-        runner.step([StepEntry(handle, prompts[index % 4], [tokens - 1])])
-        runner.cache.close(handle)
-    prefill(0)
-    ms_prefill = min(timed(prefill, 1) for _ in range(3))
+    matrix_peak = peak["bf16_tflops"] * 1e12 if compute == "bfloat16" else FP32_FFMA_TFLOPS * 1e12
     flops = prefill_flops(config, layers, tokens)
-    prefill_record = {"value": tokens * 1000.0 / ms_prefill, "tokens": tokens,
-                      "ms": ms_prefill,
-                      "frac": flops / (ms_prefill * 1e-3) / (peak["bf16_tflops"] * 1e12)}
-    del runner
-    torch.cuda.empty_cache()
+    figures = prefill_figures(model, tokens, repeat=3 if compute == "bfloat16" else 1)
+    ms_prefill = figures["whole"][0]
+    prefill_record = {"value": tokens * 1000.0 / ms_prefill, "tokens": tokens, "ms": ms_prefill,
+                      "frac": flops / (ms_prefill * 1e-3) / matrix_peak,
+                      "points": {name: {"tokens_per_s": count * 1000.0 / ms, "ms": ms}
+                                 for name, (ms, count) in figures.items() if name != "whole"}}
 
     # ---- roofline of the decode step
-    context_mid = args.context - (steps + 1) / 2
-    step_bytes = weight_bytes(config, layers) + args.batch * context_mid * \
-        kv_bytes_per_token(config, layers)
-    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    achieved = step_bytes(args.batch, args.context - (steps + 1) / 2, bytes_per) / (ms_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peak["hbm_gbs"], "peaks": peak_source}
 
-    points = {}
+    # ---- further decode points: other batch sizes at the same context, and this batch size at
+    # contexts of 2,048 and 3,072 tokens (the headline's contexts end at --context)
+    points, by_context = {}, {}
+    count = max(32, steps) if compute == "bfloat16" else max(8, steps // 4)
     for batch in [int(b) for b in args.points.split(",") if b]:
-        count = max(8, steps // 4)
-        ms, _ = decode_rate(batch, count, max(3, warmup))
+        ms, _ = decode_rate(model, batch, count, max(3, warmup), args.context)
         points[f"decode_b{batch}"] = batch * 1000.0 / ms
+    for context_end in [int(c) for c in args.contexts.split(",") if c]:
+        if context_end == args.context:
+            ms = ms_step
+        else:
+            ms, _ = decode_rate(model, args.batch, count, max(3, warmup), context_end)
+        got = step_bytes(args.batch, context_end - (count + 1) / 2, bytes_per) / (ms * 1e-3) / 1e9
+        by_context[str(context_end)] = {"tokens_per_s": args.batch * 1000.0 / ms,
+                                        "hbm_frac": got / peak["hbm_gbs"]}
+    if by_context:
+        by_context["mean_tokens_per_s"] = statistics.fmean(v["tokens_per_s"] for v in by_context.values())
+
+    # ---- the float32 path (own FFMA products, float32 cache): a few steps, one prompt
+    fp32_record = None
+    if compute == "bfloat16" and args.fp32_steps > 0:
+        del model
+        torch.cuda.empty_cache()
+        model32 = LoadedModel.from_random(config, seed=0, std=0.02, dtype="float32",
+                                          max_positions=args.context + 64)
+        ms32, _ = decode_rate(model32, args.batch, args.fp32_steps, 3, args.context)
+        got32 = step_bytes(args.batch, args.context - (args.fp32_steps + 1) / 2, 4) / (ms32 * 1e-3) / 1e9
+        fig32 = prefill_figures(model32, tokens, repeat=1)
+        fp32_record = {"decode_tokens_per_s": args.batch * 1000.0 / ms32, "ms_per_step": ms32,
+                       "steps": args.fp32_steps, "hbm_gbs": got32, "hbm_frac": got32 / peak["hbm_gbs"],
+                       "prefill_ms": fig32["whole"][0],
+                       "prefill_tokens_per_s": tokens * 1000.0 / fig32["whole"][0],
+                       "prefill_frac_of_ffma_peak": flops / (fig32["whole"][0] * 1e-3) / (FP32_FFMA_TFLOPS * 1e12),
+                       "ffma_peak_tflops": FP32_FFMA_TFLOPS}
+        del model32
+        torch.cuda.empty_cache()
 
     record = {
-        "metric": "decode tok/s @ batch 8, context 4,096 (Qwen2.5-7B shape)",
+        "metric": f"decode tok/s @ batch {args.batch}, context {args.context:,} (Qwen2.5-7B shape)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16",
+        "vs_baseline": None, "dtype": "bf16" if compute == "bfloat16" else "fp32",
         "data": "synthetic: random bf16 weights N(0,0.02), uniform random token ids",
         "impl": "engine",
         "config": {"model": "Qwen2.5-7B shape", "global_batch": args.batch,
@@ -530,8 +607,11 @@ def main() -> int:
         "prefill": prefill_record,
         "roofline": roofline,
         "points": points,
+        "decode_by_context": by_context,
         "clocks": clock_record,
     }
+    if fp32_record is not None:
+        record["fp32"] = fp32_record
     print(json.dumps(record))
     return 0
 

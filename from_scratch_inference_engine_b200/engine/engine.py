@@ -66,17 +66,9 @@ class LoadedModel:
         biases, gains 1 + N(0, std), rounded to bfloat16 first so that both compute dtypes see
         the same numbers.  For benchmarks at sizes whose checkpoint would take minutes to
         write and read back."""
-        spec = config.build_spec()
-        generator = torch.Generator(device=device).manual_seed(seed)
-        tensors = {}
-        for item in DecoderModel(spec).tensor_specs():
-            if item.optional:
-                continue
-            values = torch.randn(item.shape, generator=generator, device=device,
-                                 dtype=torch.float32) * std
-            if item.init == "gain":
-                values += 1.0
-            tensors[item.name] = values.to(torch.bfloat16)
+        from ..parts.model import tensor_specs
+        from ..weights.random_init import random_tensors_on_device
+        tensors = random_tensors_on_device(tensor_specs(config.build_spec()), seed, std, device)
         return cls.from_tensors(config, tensors, dtype, device, max_positions)
 
     def forward(self, ids: Sequence[int]) -> torch.Tensor:
@@ -86,7 +78,7 @@ class LoadedModel:
             raise ValueError(f"forward: {len(ids)} tokens exceed the position table "
                              f"({self.runtime.max_positions})")
         runner = ModelRunner(self.model, self.runtime, page_size=16, num_pages=pages,
-                             max_requests=1)
+                             max_requests=1, max_step_tokens=max(1, len(ids)))
         handle = runner.cache.open(0)
         logits = runner.step([StepEntry(handle, list(ids), list(range(len(ids))))])
         runner.raise_on_device_error()
@@ -100,7 +92,8 @@ class Engine:
         self.model = model
         self.runner = ModelRunner(model.model, model.runtime, page_size=block_size,
                                   num_pages=num_blocks, max_requests=max_batch,
-                                  enable_prefix_cache=enable_prefix_cache)
+                                  enable_prefix_cache=enable_prefix_cache,
+                                  max_step_tokens=max_step_tokens)
         self.scheduler = Scheduler(self.runner.cache, max_batch, max_step_tokens,
                                    self.runner.max_positions)
         self.sampler = Sampler(model.runtime.device)
@@ -123,8 +116,11 @@ class Engine:
         return self.scheduler.add(prompt, params, max_tokens, eos_id, seed)
 
     def warm_up(self, max_context: int = 0) -> int:
-        """Capture the decode graphs for contexts of up to `max_context` tokens (default: what
-        one request may hold) before serving starts; returns their number."""
+        """Before serving starts: run one step of the largest size (its working memory then
+        stays with the allocator) and capture the decode graphs for contexts of up to
+        `max_context` tokens (default: what one request may hold); returns their number."""
+        if not self.has_work():
+            self.runner.reserve_step_memory()
         limit = max_context or min(self.runner.cache.max_tokens_per_request(), self.runner.max_positions)
         return self.runner.capture_decode_graphs(limit, self.scheduler.max_batch)
 

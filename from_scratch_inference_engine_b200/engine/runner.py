@@ -105,8 +105,14 @@ class _DecodeGraph:
 class ModelRunner:
     def __init__(self, model: DecoderModel, runtime: Runtime, page_size: int = 16,
                  num_pages=2048, max_requests: int = 256, enable_prefix_cache: bool = False,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, max_step_tokens: int = 8192):
+        """`max_step_tokens` and `max_requests` cap what one step may bring (tokens; requests):
+        a step beyond them is refused before anything runs, so that the working memory of a
+        step is bounded by what `reserve_step_memory` has seen."""
+        if max_step_tokens <= 0 or max_requests <= 0:
+            raise ValueError("max_step_tokens and max_requests must be positive")
         self.model, self.runtime = model, runtime
+        self.max_step_tokens, self.max_step_items = int(max_step_tokens), int(max_requests)
         needs = model.cache_needs()
         self.cache = CacheManager(needs, page_size, num_pages, max_requests, enable_prefix_cache,
                                   has_state=any(n is not None for n in model.state_needs()))
@@ -149,6 +155,13 @@ class ModelRunner:
     def _validate(self, entries: Sequence[StepEntry]) -> None:
         if not entries:
             raise ValueError("step: empty batch")
+        if len(entries) > self.max_step_items:
+            raise ValueError(f"step: {len(entries)} requests in one step, the runner was built "
+                             f"for {self.max_step_items}")
+        total = sum(len(entry.tokens) for entry in entries)
+        if total > self.max_step_tokens:
+            raise ValueError(f"step: {total} tokens in one step, the runner was built for "
+                             f"{self.max_step_tokens}")
         seen = set()
         for entry in entries:
             if entry.handle.closed:
@@ -192,6 +205,23 @@ class ModelRunner:
         host = np.asarray([d for d, _ in pairs] + [r for _, r in pairs], dtype=np.int32)
         from ..kernels import ops
         ops.place_tokens(ctx.token_ids, self._ring.stage(host, self.runtime.device), device_tokens)
+
+    def reserve_step_memory(self, tokens: int = 0) -> int:
+        """Run one step of `tokens` tokens (default: the cap) of a scratch request, so that the
+        allocator holds the working memory of the largest step before serving starts and no
+        later step has to ask the driver for memory; the request's pages and slot are given
+        back.  Skipped (returns 0) when the pool cannot hold that many tokens right now."""
+        tokens = min(tokens or self.max_step_tokens, self.max_step_tokens, self.max_positions)
+        cache = self.cache
+        if not cache.can_open() or any(cache.blocks_for(tokens) > free for free in cache.free_pages()):
+            return 0
+        handle = cache.open(("reserve_step_memory", id(self)))
+        try:
+            self.step([StepEntry(handle, [0] * tokens, [tokens - 1])])
+            torch.cuda.current_stream().synchronize()
+        finally:
+            cache.close(handle)
+        return tokens
 
     def capture_decode_graphs(self, max_context: int, max_batch: int = 0) -> int:
         """Capture ahead of time the decode steps that requests of up to `max_context` tokens

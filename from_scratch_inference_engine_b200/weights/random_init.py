@@ -72,6 +72,33 @@ def random_tensors(specs: Iterable[TensorSpec], seed: int, std: float = 0.02,
     return out
 
 
+def random_tensors_on_device(specs: Iterable[TensorSpec], seed: int, std: float = 0.02,
+                             device="cuda:0", dtype: torch.dtype = torch.bfloat16
+                             ) -> Dict[str, torch.Tensor]:
+    """The same recipe (matrices and biases N(0, std), gains 1 + N(0, std), rounded to `dtype`)
+    drawn by the device's own generator, for sizes at which hashing billions of counters on the
+    host would take minutes: benchmarks and tests at real layer sizes.  Reproducible on one
+    kind of device for one seed, but not the bits of `random_tensors`."""
+    generator = torch.Generator(device=device).manual_seed(seed)
+    out: Dict[str, torch.Tensor] = {}
+    for spec in specs:
+        if spec.optional or spec.name in out:
+            continue
+        if spec.role == "table":
+            raise ValueError(f"no random recipe for integer table {spec.name}")
+        if spec.init in ("zeros", "ones"):
+            values = torch.full(spec.shape, float(spec.init == "ones"), device=device)
+        elif spec.init in ("gain", "normal"):
+            values = torch.randn(spec.shape, generator=generator, device=device,
+                                 dtype=torch.float32) * std
+            if spec.init == "gain":
+                values += 1.0
+        else:
+            raise ValueError(f"unknown init '{spec.init}' for {spec.name}")
+        out[spec.name] = values.to(dtype)
+    return out
+
+
 def write_random_model(model_dir, config, seed: int, std: float = 0.02,
                        dtype: torch.dtype = torch.bfloat16) -> Path:
     """Write config.json and model.safetensors for `config` with weights drawn from `seed`."""

@@ -74,14 +74,16 @@ def random_ids(vocab: int, n: int, seed: int) -> List[int]:
     return [rng.randrange(vocab) for _ in range(n)]
 
 
-_plain_cache: Dict[Tuple[str, Tuple[int, ...]], np.ndarray] = {}
+_plain_cache: Dict[Tuple[str, Tuple[int, ...], object], np.ndarray] = {}
 
 
-def plain_logits(model_dir: Path, ids: List[int]) -> np.ndarray:
-    """float64 logits [len(ids), vocab] of the plain implementation (memoised)."""
-    key = (str(model_dir), tuple(ids))
+def plain_logits(model_dir: Path, ids: List[int], store=None) -> np.ndarray:
+    """float64 logits [len(ids), vocab] of the plain implementation (memoised); with
+    store=torch.bfloat16, of the plain implementation that writes every operation's result
+    in bfloat16 as the engine's bfloat16 path does."""
+    key = (str(model_dir), tuple(ids), store)
     if key not in _plain_cache:
-        _plain_cache[key] = plain.logits_of(model_dir, ids).numpy()
+        _plain_cache[key] = plain.logits_of(model_dir, ids, store=store).numpy()
     return _plain_cache[key]
 
 
@@ -251,14 +253,15 @@ def run_trace_in_process(runner, steps: List[dict]):
 OBSERVED: Dict[str, float] = {}      # label -> largest relative difference seen (for reports)
 
 
-def compare_rows(rows, requests, model_dir, rel: float, label: str = ""):
+def compare_rows(rows, requests, model_dir, rel: float, label: str = "", store=None):
     """Every row's largest |engine - plain| against rel * max(1, max |plain| of that row).
     Returns (largest difference, largest |plain|, rows beyond the bound); the largest
-    difference relative to its row's bound base is kept in OBSERVED[label]."""
+    difference relative to its row's bound base is kept in OBSERVED[label].  `store`: see
+    `plain_logits`."""
     worst, scale, relative = 0.0, 1.0, 0.0
     mismatched = []
     for (key, pos), row in sorted(rows.items()):
-        want = plain_logits(model_dir, requests[key])[pos]
+        want = plain_logits(model_dir, requests[key], store)[pos]
         base = max(1.0, float(np.abs(want).max()))
         scale = max(scale, base)
         diff = float(np.abs(row.astype(np.float64) - want).max())

@@ -131,30 +131,42 @@ def silu_mul(gate, up):
 
 
 # ------------------------------------------------------------------------------- model
+def stored_as(dtype):
+    """What a value becomes when it is stored in `dtype` between two operations and read back
+    (None: nothing happens to it).  Not in the reference, which stores float32 everywhere:
+    with torch.bfloat16 the formulas below model an engine that keeps the residual stream
+    and all sums in high precision but writes every operation's result in bfloat16."""
+    if dtype is None:
+        return lambda t: t
+    return lambda t: t.to(dtype).to(t.dtype)
+
+
 def decoder_layer(config, weights, l, x, positions, shared_kv=None):
     """One pre-norm layer on a whole sequence, src/model/model.cpp:107-141.  Returns the new
     residual stream and this layer's (k, v).  With `shared_kv` the layer attends over those
     keys and values instead of its own (a run order in which a layer reads another layer's
-    cache; not in the reference)."""
+    cache; not in the reference).  config["store"] (optional, see `stored_as`) is applied to
+    every operation's result except the residual sum."""
     c, w = config, weights
+    st = stored_as(c.get("store"))
     p = f"model.layers.{l}."
-    normed = rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
+    normed = st(rms_norm(x, w[p + "input_layernorm.weight"], c["eps"]))
 
     def project(name):
         bias = w[p + f"self_attn.{name}_proj.bias"] if c["bias"] else None
-        return linear(normed, w[p + f"self_attn.{name}_proj.weight"], bias)
-    q = rope(project("q"), c["heads"], c["head_dim"], c["theta"], positions)
+        return st(linear(normed, w[p + f"self_attn.{name}_proj.weight"], bias))
+    q = st(rope(project("q"), c["heads"], c["head_dim"], c["theta"], positions))
     if shared_kv is None:
-        k = rope(project("k"), c["kv_heads"], c["head_dim"], c["theta"], positions)
+        k = st(rope(project("k"), c["kv_heads"], c["head_dim"], c["theta"], positions))
         v = project("v")
     else:
         k, v = shared_kv
-    attn = attention(q, k, v, c["heads"], c["kv_heads"], c["head_dim"], 0, c["windows"][l])
-    x = x + linear(attn, w[p + "self_attn.o_proj.weight"])
-    normed2 = rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
-    act = silu_mul(linear(normed2, w[p + "mlp.gate_proj.weight"]),
-                   linear(normed2, w[p + "mlp.up_proj.weight"]))
-    return x + linear(act, w[p + "mlp.down_proj.weight"]), (k, v)
+    attn = st(attention(q, k, v, c["heads"], c["kv_heads"], c["head_dim"], 0, c["windows"][l]))
+    x = x + st(linear(attn, w[p + "self_attn.o_proj.weight"]))
+    normed2 = st(rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"]))
+    act = st(silu_mul(st(linear(normed2, w[p + "mlp.gate_proj.weight"])),
+                      st(linear(normed2, w[p + "mlp.up_proj.weight"]))))
+    return x + st(linear(act, w[p + "mlp.down_proj.weight"])), (k, v)
 
 
 def forward(config, weights, ids, schedule=None):
@@ -171,7 +183,7 @@ def forward(config, weights, ids, schedule=None):
         x, kv = decoder_layer(c, w, l, x, positions, None if writes else stored[entry])
         if writes:
             stored[entry] = kv
-    normed = rms_norm(x, w["model.norm.weight"], c["eps"])
+    normed = stored_as(c.get("store"))(rms_norm(x, w["model.norm.weight"], c["eps"]))
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return linear(normed, head)
 
@@ -180,8 +192,9 @@ def load(model_dir, dtype=torch.float64):
     return read_config(model_dir), read_safetensors(Path(model_dir) / "model.safetensors", dtype)
 
 
-def logits_of(model_dir, ids, dtype=torch.float64):
+def logits_of(model_dir, ids, dtype=torch.float64, store=None):
     config, weights = load(model_dir, dtype)
+    config["store"] = store
     return forward(config, weights, ids)
 
 

@@ -105,13 +105,14 @@ def test_pages_run_out_preemption_recomputes_to_the_same_tokens(folders, dtype):
     from from_scratch_inference_engine_b200 import SamplingParams
     greedy = SamplingParams(temperature=0.0)
     prompts = [helpers.random_ids(384, 5, s) for s in (5, 6)]
-    alone = [engine_for(folders["B"], dtype, block_size=8).generate(p, greedy, 12) for p in prompts]
-    engine = engine_for(folders["B"], dtype, block_size=8, num_blocks=3)     # 24 tokens of cache in all
-    ids = [engine.add_request(p, greedy, 12) for p in prompts]
+    alone = [engine_for(folders["B"], dtype, block_size=8).generate(p, greedy, 14) for p in prompts]
+    # 32 tokens of cache in all: each request needs a third page when both hold two
+    engine = engine_for(folders["B"], dtype, block_size=8, num_blocks=4)
+    ids = [engine.add_request(p, greedy, 14) for p in prompts]
     engine.run_until_done()
     assert engine.preemptions() > 0
     same_or_near_tie(folders["B"], prompts, [engine.output(i) for i in ids], alone, dtype)
-    assert engine.runner.cache.free_pages() == [3]
+    assert engine.runner.cache.free_pages() == [4]
     engine.runner.cache.check()
 
 

@@ -9,17 +9,32 @@ from helpers import TINY
 
 pytestmark = pytest.mark.gpu
 
-# float32: the engine's 32-bit sums against the plain 64-bit ones.  bfloat16: activations are
-# rounded to 8 bits of mantissa at every product; how far that moves the logits depends on the
-# model (depth, widths, the size of its weights), so each configuration has its own bound:
-# about 2.5 times the largest difference seen over all families and kernel choices (the terminal
-# summary of a GPU run prints what it saw), relative to max(1, the row's largest |logit|).
+# float32: the engine's 32-bit sums against the plain 64-bit ones.  bfloat16: every operation's
+# result is stored with 8 bits of mantissa, which moves the logits of these models by up to
+# 1.5e-2 of the largest logit - more than many faults would.  So the bfloat16 engine is held
+# to the plain implementation *with the same storage rounding* (plain_qwen2.stored_as): what
+# is left is the order of the sums and the rounding of the attention weights, and each
+# configuration's bound is about 2.5 times the largest difference seen over all families and
+# kernel choices (the terminal summary of a GPU run prints what it saw).  All bounds are
+# relative to max(1, the row's largest |logit|).  Against the exact plain logits the bfloat16
+# engine must still stay within BFLOAT16_LOOSE.
 FLOAT32_BOUND = 1e-4
 BFLOAT16_BOUND = {"A": 4e-2, "B": 4e-2, "C": 4e-2, "D": 4e-2, "E": 4e-2, "F": 4e-2}
+BFLOAT16_LOOSE = 4e-2
 
 
-def bound(dtype, name):
-    return FLOAT32_BOUND if dtype == "float32" else BFLOAT16_BOUND[name]
+def assert_rows_match_plain(rows, requests, folder, dtype, name):
+    if dtype == "float32":
+        worst, scale, bad = helpers.compare_rows(rows, requests, folder, FLOAT32_BOUND,
+                                                 f"float32 {name}")
+    else:
+        worst, scale, bad = helpers.compare_rows(rows, requests, folder, BFLOAT16_LOOSE,
+                                                 f"bfloat16 {name} against exact plain")
+        assert not bad, f"{len(bad)} rows beyond the loose bound, first {bad[:3]}, worst {worst:.3e}"
+        worst, scale, bad = helpers.compare_rows(rows, requests, folder, BFLOAT16_BOUND[name],
+                                                 f"bfloat16 {name} against plain stored in bfloat16",
+                                                 store=torch.bfloat16)
+    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
 
 
 REQUESTS = {
@@ -76,9 +91,7 @@ def test_replay_matches_plain(folders, name, page_size, family, dtype):
     assert len(rows) == sum(len(e["tokens"]) for step in steps for e in step["entries"])
     if family != "recompute":
         assert len(rows) == sum(len(v) for v in requests.values())
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], bound(dtype, name),
-                                             f"{dtype} {name}")
-    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+    assert_rows_match_plain(rows, requests, folders[name], dtype, name)
     assert all(pool.num_free == pool.num_pages for pool in runner.cache.pools)
 
 
@@ -89,8 +102,7 @@ def test_first_tokens_of_a_sequence(folders, dtype):
     for steps in (helpers.trace_whole(requests), helpers.trace_tail_by_one(requests, tail=2)):
         runner = build_runner(folders["A"], dtype, 64, 4)
         rows = helpers.run_trace_in_process(runner, steps)
-        _, _, bad = helpers.compare_rows(rows, requests, folders["A"], bound(dtype, "A"), f"{dtype} A")
-        assert not bad
+        assert_rows_match_plain(rows, requests, folders["A"], dtype, "A")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -101,8 +113,7 @@ def test_long_decoding(folders, dtype):
     steps = helpers.trace_tail_by_one(requests, tail=200)
     runner = build_runner(folders["B"], dtype, 256, 8)
     rows = helpers.run_trace_in_process(runner, steps)
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders["B"], bound(dtype, "B"), f"{dtype} B")
-    assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
+    assert_rows_match_plain(rows, requests, folders["B"], dtype, "B")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -125,8 +136,7 @@ def test_captured_decode_steps_equal_uncaptured_ones(folders, dtype):
         for key, row in captured.items():
             assert np.abs(row - direct[key]).max() < 2e-5, key
     for rows in (captured, direct):
-        worst, scale, bad = helpers.compare_rows(rows, requests, folders["B"], bound(dtype, "B"), f"{dtype} B")
-        assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
+        assert_rows_match_plain(rows, requests, folders["B"], dtype, "B")
 
 
 def test_cutting_does_not_change_float32_beyond_rounding(folders):
@@ -152,8 +162,7 @@ def test_replay_with_the_few_token_product_on_every_matrix(folders, name, page_s
     runner = build_runner(folders[name], "bfloat16", need, page_size, few_token_min_elements=0)
     assert runner.runtime._few_token_weights
     rows = helpers.run_trace_in_process(runner, steps)
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], bound("bfloat16", name), f"bfloat16 {name}")
-    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+    assert_rows_match_plain(rows, requests, folders[name], "bfloat16", name)
 
 
 @pytest.mark.parametrize("family", ["whole", "portions", "mixed"])
@@ -169,8 +178,7 @@ def test_replay_with_the_tiled_product_on_every_matrix(folders, name, page_size,
     calls, original = [], ops.gemm_tiles
     monkeypatch.setattr(ops, "gemm_tiles", lambda *a, **k: (calls.append(1), original(*a, **k))[1])
     rows = helpers.run_trace_in_process(runner, steps)
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders[name], bound("bfloat16", name), f"bfloat16 {name}")
-    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+    assert_rows_match_plain(rows, requests, folders[name], "bfloat16", name)
     assert len(calls) >= 4 * len(runner.model.blocks)
 
 
@@ -186,8 +194,7 @@ def test_replay_with_the_tcgen05_kernel_for_decoded_tokens(folders, family, monk
     monkeypatch.setattr(ops, "attention_tc_decode",
                         lambda *a, **k: (calls.append(1), original(*a, **k))[1])
     rows = helpers.run_trace_in_process(runner, steps)
-    worst, scale, bad = helpers.compare_rows(rows, requests, folders["F"], bound("bfloat16", "F"), "bfloat16 F")
-    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+    assert_rows_match_plain(rows, requests, folders["F"], "bfloat16", "F")
     assert calls
     if family == "tail":
         assert runner._graphs, "the decoded tokens did not go through a captured step"

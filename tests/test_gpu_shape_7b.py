@@ -31,9 +31,13 @@ SHAPE = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_
              tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False)
 LENGTHS = {"a": 150, "b": 72, "c": 48, "d": 33}
 # relative to max(1, largest |plain logit| of the row).  float32: the reference's own bar between
-# its modes (tests/cpp/test_cuda_model.cpp:57, 66).  bfloat16: about 2.5 times what 2 layers show
-# (the terminal summary prints it); rounding accumulates with depth, 28 layers were seen at 4.5e-2.
+# its modes (tests/cpp/test_cuda_model.cpp:57, 66).  bfloat16: against the plain implementation
+# that stores every operation's result in bfloat16 as the engine does (what is left is the
+# order of the sums and the rounding of the attention weights; about 2.5 times what was seen,
+# the terminal summary prints it), and loosely against the exact plain logits, from which
+# storage rounding alone moves 2 layers by 1.8e-2 and 28 layers by 4.5e-2.
 BOUND = {"float32": 1e-4, "bfloat16": 4e-2 if LAYERS <= 4 else 1.2e-1}
+BOUND_STORED = 4e-2
 PAGE = 16
 
 
@@ -42,16 +46,10 @@ def shape_model():
     """(configuration, tensors on the GPU, requests, plain float64 logits per request)."""
     from from_scratch_inference_engine_b200.config import config_from_dict
     from from_scratch_inference_engine_b200.parts import tensor_specs
+    from from_scratch_inference_engine_b200.weights.random_init import random_tensors_on_device
     config = config_from_dict(dict(SHAPE))
-    generator = torch.Generator(device="cuda").manual_seed(0)
-    tensors = {}
-    for spec in tensor_specs(config.build_spec()):
-        if spec.optional:
-            continue
-        values = torch.randn(spec.shape, generator=generator, device="cuda") * 0.02
-        if spec.init == "gain":
-            values += 1.0
-        tensors[spec.name] = values.to(torch.bfloat16)
+    tensors = random_tensors_on_device(tensor_specs(config.build_spec()), seed=0, std=0.02,
+                                       device="cuda")
     requests = {key: helpers.random_ids(config.vocab_size, n, seed)
                 for seed, (key, n) in enumerate(LENGTHS.items())}
 
@@ -64,7 +62,10 @@ def shape_model():
     plain_config = plain.read_config_dict(dict(SHAPE))
     want = {key: plain.forward(plain_config, Widening(), ids).cpu().numpy()
             for key, ids in requests.items()}
-    yield config, tensors, requests, want
+    plain_config["store"] = torch.bfloat16
+    stored = {key: plain.forward(plain_config, Widening(), ids).cpu().numpy()
+              for key, ids in requests.items()}
+    yield config, tensors, requests, want, stored
     tensors.clear()
     torch.cuda.empty_cache()
 
@@ -89,7 +90,7 @@ MODES = {
 def test_replay_at_the_7b_layer_sizes(shape_model, mode):
     from from_scratch_inference_engine_b200.engine import LoadedModel, ModelRunner
     from from_scratch_inference_engine_b200.kernels import ops
-    config, tensors, requests, want = shape_model
+    config, tensors, requests, want, stored = shape_model
     dtype, options = MODES[mode]
     model = LoadedModel.from_tensors(config, tensors, dtype=dtype, max_positions=512, **options)
     calls = {"gemm_tiles": 0, "attention_tc_decode": 0}
@@ -111,7 +112,7 @@ def test_replay_at_the_7b_layer_sizes(shape_model, mode):
                                  max_requests=4)
             rows = helpers.run_trace_in_process(runner, steps)
             assert len(rows) == sum(len(e["tokens"]) for s in steps for e in s["entries"])
-            worst, bad, disagree = 0.0, [], 0
+            worst, worst_stored, bad, disagree = 0.0, 0.0, [], 0
             for (key, pos), row in rows.items():
                 target = want[key.split("~")[0]][pos]
                 base = max(1.0, float(np.abs(target).max()))
@@ -120,9 +121,17 @@ def test_replay_at_the_7b_layer_sizes(shape_model, mode):
                 if diff > BOUND[dtype]:
                     bad.append((key, pos, diff))
                 disagree += int(row.argmax()) != int(target.argmax())
+                if dtype == "bfloat16":
+                    diff = float(np.abs(row - stored[key.split("~")[0]][pos]).max()) / base
+                    worst_stored = max(worst_stored, diff)
+                    if diff > BOUND_STORED:
+                        bad.append((key, pos, diff, "against plain stored in bfloat16"))
             report[family] = worst
             helpers.OBSERVED[f"7B sizes, {LAYERS} layers, {mode}, {family}"] = worst
-            assert not bad, f"{family}: {len(bad)} rows beyond {BOUND[dtype]:.0e}, first {bad[:3]}"
+            if dtype == "bfloat16":
+                helpers.OBSERVED[f"7B sizes, {LAYERS} layers, {mode}, {family}, against plain "
+                                 f"stored in bfloat16"] = worst_stored
+            assert not bad, f"{family}: {len(bad)} rows beyond their bound, first {bad[:3]}"
             if dtype == "float32":
                 assert disagree == 0, f"{family}: argmax differs at {disagree} positions"
             assert all(pool.num_free == pool.num_pages for pool in runner.cache.pools)

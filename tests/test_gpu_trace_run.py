@@ -16,10 +16,10 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def replay(folder, dtype, steps, out_dir, max_tokens):
+def replay(folder, dtype, steps, out_dir, max_tokens, *options):
     text = "".join(json.dumps(step) + "\n" for step in steps)
     done = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype",
-                           dtype, "--out", str(out_dir), "--max-tokens", str(max_tokens)],
+                           dtype, "--out", str(out_dir), "--max-tokens", str(max_tokens), *options],
                           input=text, capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stderr[-2000:]
     assert [l for l in done.stdout.splitlines() if l.startswith("done ")] == \
@@ -54,6 +54,32 @@ def test_trace_run_mixed_trace(tmp_path, dtype):
     worst, scale, bad = helpers.compare_rows(rows, requests, folder,
                                              1e-4 if dtype == "float32" else 4e-2)
     assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
+
+
+def test_trace_run_with_other_pages_and_fewer_live_requests(tmp_path):
+    """--page-size and --max-live: pages of 8 tokens, four requests live at most, and a
+    request released in the middle that runs again from its first token."""
+    folder = helpers.make_model_dir(tmp_path, "D")
+    vocab = TINY["D"]["config"]["vocab_size"]
+    requests = {key: helpers.random_ids(vocab, n, i)
+                for i, (key, n) in enumerate({"a": 70, "b": 35, "c": 48, "d": 20, "e": 9}.items())}
+    steps, names = helpers.trace_mixed_with_recompute(requests, seed=4, max_live=4)
+    need = helpers.live_tokens_needed(steps, round_to=64)
+    out = tmp_path / "out"
+    replay(folder, "float32", steps, out, need, "--page-size", "8", "--max-live", "4")
+    outputs = {step["step"]: np.fromfile(out / f"{step['step']}.f32", dtype="<f4").reshape(-1, vocab)
+               for step in steps}
+    rows = helpers.collect_rows(steps, outputs)
+    worst, scale, bad = helpers.compare_rows(rows, names, folder, 1e-4)
+    assert not bad, f"worst {worst:.3e} at scale {scale:.3f}: {bad[:3]}"
+    # a fifth live request is refused
+    crowd = [{"step": 0, "end": [], "entries": [{"id": str(k), "tokens": [1, 2], "want": []}
+                                                 for k in range(5)]}]
+    done = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype",
+                           "float32", "--out", str(tmp_path / "o2"), "--max-tokens", "512",
+                           "--max-live", "4"], input=json.dumps(crowd[0]) + "\n",
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode != 0
 
 
 def test_trace_run_reports_bad_input(tmp_path):
