@@ -81,6 +81,8 @@ class Sampler:
         self._scratch = None
         self._pinned: List[torch.Tensor] = []
         self._turn = 0
+        from ..engine.context import PinnedRing
+        self._ring = PinnedRing()    # staging of the sampling parameters
         self.bytes_to_device = 0     # sampling parameters copied in (benchmarks read these)
         self.bytes_to_host = 0       # chosen ids copied out
 
@@ -119,18 +121,20 @@ class Sampler:
                                             device=self.device)
             ops.argmax(logits, picks[0], self._scratch)
         if any_random:
+            # one staged copy from pinned memory for all parameters: a copy from pageable memory
+            # would wait for the stream and with it for the step that is still running
             host = np.empty((5, rows), dtype=np.float32)
+            top_k = host[3].view(np.int32)
             for r, p in enumerate(params):
                 host[0, r] = p.temperature if not p.greedy else 0.0
                 host[1, r] = min(p.top_p, 1.0)
                 host[2, r] = uniform_draw(seeds[r], indices[r])
-                host[3, r] = 0.0
+                top_k[r] = max(0, int(p.top_k))
                 host[4, r] = 1.0 if p.greedy else 0.0
-            dev = torch.from_numpy(host).to(self.device)
-            self.bytes_to_device += host.nbytes + 4 * rows
-            top_k = torch.tensor([max(0, int(p.top_k)) for p in params], dtype=torch.int32,
-                                 device=self.device)
-            ops.sample(logits, dev[0], top_k, dev[1], dev[2], picks[1])
+            staged = self._ring.stage(host.reshape(-1).view(np.int32), self.device).view(5, rows)
+            dev = staged.view(torch.float32)
+            self.bytes_to_device += host.nbytes
+            ops.sample(logits, dev[0], staged[3], dev[1], dev[2], picks[1])
             chosen = torch.where(dev[4] > 0, picks[0], picks[1]) if any_greedy else picks[1]
         else:
             chosen = picks[0]

@@ -71,6 +71,16 @@ def read_safetensors(path, dtype=torch.float64):
 
 
 # ------------------------------------------------------------------------------- parts
+def stored_as(dtype):
+    """What a value becomes when it is stored in `dtype` between two operations and read back
+    (None: nothing happens to it).  Not in the reference, which stores float32 everywhere:
+    with torch.bfloat16 the formulas below model an engine that keeps the residual stream
+    and all sums in high precision but writes every operation's result in bfloat16."""
+    if dtype is None:
+        return lambda t: t
+    return lambda t: t.to(dtype).to(t.dtype)
+
+
 def embedding(weight, ids):
     """Row copy, src/model/nn.cpp:90-108."""
     return weight[torch.as_tensor(ids, dtype=torch.long, device=weight.device)]
@@ -103,9 +113,12 @@ def rope(x, n_heads, head_dim, theta, positions):
     return torch.cat([x1 * c - x2 * sn, x2 * c + x1 * sn], dim=-1).reshape(s, n_heads * head_dim)
 
 
-def attention(q, k, v, n_heads, n_kv_heads, head_dim, query_offset=0, window=0):
+def attention(q, k, v, n_heads, n_kv_heads, head_dim, query_offset=0, window=0, store=None):
     """Causal grouped-query attention, two-pass softmax, head h uses kv head h // group,
-    keys 0..query_offset+i inclusive, src/model/nn.cpp:151-226."""
+    keys 0..query_offset+i inclusive, src/model/nn.cpp:151-226.  `store` (not in the
+    reference; see `stored_as`): the unnormalised weights exp(score - max) are stored in that
+    type before they multiply the values, while their sum is taken from the exact ones - what
+    a tensor-core kernel does whose weights are a bfloat16 operand."""
     q_len, total = q.shape[0], k.shape[0]
     group = n_heads // n_kv_heads
     scale = 1.0 / math.sqrt(head_dim)
@@ -120,8 +133,12 @@ def attention(q, k, v, n_heads, n_kv_heads, head_dim, query_offset=0, window=0):
             qv = q[i, h * head_dim:(h + 1) * head_dim]
             scores = (kh[first:last + 1] @ qv) * scale
             p = torch.exp(scores - scores.max())
-            p = p / p.sum()
-            out[i, h * head_dim:(h + 1) * head_dim] = p @ vh[first:last + 1]
+            if store is None:
+                p = p / p.sum()
+                out[i, h * head_dim:(h + 1) * head_dim] = p @ vh[first:last + 1]
+            else:
+                out[i, h * head_dim:(h + 1) * head_dim] = \
+                    (stored_as(store)(p) @ vh[first:last + 1]) / p.sum()
     return out
 
 
@@ -131,16 +148,6 @@ def silu_mul(gate, up):
 
 
 # ------------------------------------------------------------------------------- model
-def stored_as(dtype):
-    """What a value becomes when it is stored in `dtype` between two operations and read back
-    (None: nothing happens to it).  Not in the reference, which stores float32 everywhere:
-    with torch.bfloat16 the formulas below model an engine that keeps the residual stream
-    and all sums in high precision but writes every operation's result in bfloat16."""
-    if dtype is None:
-        return lambda t: t
-    return lambda t: t.to(dtype).to(t.dtype)
-
-
 def decoder_layer(config, weights, l, x, positions, shared_kv=None):
     """One pre-norm layer on a whole sequence, src/model/model.cpp:107-141.  Returns the new
     residual stream and this layer's (k, v).  With `shared_kv` the layer attends over those
@@ -161,7 +168,8 @@ def decoder_layer(config, weights, l, x, positions, shared_kv=None):
         v = project("v")
     else:
         k, v = shared_kv
-    attn = st(attention(q, k, v, c["heads"], c["kv_heads"], c["head_dim"], 0, c["windows"][l]))
+    attn = st(attention(q, k, v, c["heads"], c["kv_heads"], c["head_dim"], 0, c["windows"][l],
+                        c.get("store")))
     x = x + st(linear(attn, w[p + "self_attn.o_proj.weight"]))
     normed2 = st(rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"]))
     act = st(silu_mul(st(linear(normed2, w[p + "mlp.gate_proj.weight"])),

@@ -10,17 +10,20 @@ from helpers import TINY
 pytestmark = pytest.mark.gpu
 
 # float32: the engine's 32-bit sums against the plain 64-bit ones.  bfloat16: every operation's
-# result is stored with 8 bits of mantissa, which moves the logits of these models by up to
-# 1.5e-2 of the largest logit - more than many faults would.  So the bfloat16 engine is held
-# to the plain implementation *with the same storage rounding* (plain_qwen2.stored_as): what
-# is left is the order of the sums and the rounding of the attention weights, and each
-# configuration's bound is about 2.5 times the largest difference seen over all families and
-# kernel choices (the terminal summary of a GPU run prints what it saw).  All bounds are
-# relative to max(1, the row's largest |logit|).  Against the exact plain logits the bfloat16
-# engine must still stay within BFLOAT16_LOOSE.
+# result is stored with 8 bits of mantissa, and how far that moves the logits depends on the
+# model (depth, widths, size of the weights), so each configuration has its own bound: 2.5 times
+# the largest difference seen over all families and kernel choices on a B200 (the terminal
+# summary of a GPU run prints what it saw: A 2.5e-3, B 1.5e-2, C 1.2e-2, D 1.5e-2, E 1.5e-2,
+# F 8.8e-3).  All bounds are relative to max(1, the row's largest |logit|).
+# The bfloat16 engine is also compared with the plain implementation that stores results in
+# bfloat16 where the engine does (plain_qwen2.stored_as, and the attention weights).  On a
+# whole sequence of config A the two then agree to 2e-7: the model of the rounding points is
+# right.  It does not give a sharper bound in general: once a context spans more than one
+# tile of keys the engine rounds its attention weights against a running maximum, values
+# differ by a fraction of a bfloat16 step, every later rounding falls independently, and the
+# difference is as large as against the exact logits.  The same bound holds for both.
 FLOAT32_BOUND = 1e-4
-BFLOAT16_BOUND = {"A": 4e-2, "B": 4e-2, "C": 4e-2, "D": 4e-2, "E": 4e-2, "F": 4e-2}
-BFLOAT16_LOOSE = 4e-2
+BFLOAT16_BOUND = {"A": 6.4e-3, "B": 3.8e-2, "C": 3.0e-2, "D": 3.9e-2, "E": 3.9e-2, "F": 2.2e-2}
 
 
 def assert_rows_match_plain(rows, requests, folder, dtype, name):
@@ -28,9 +31,9 @@ def assert_rows_match_plain(rows, requests, folder, dtype, name):
         worst, scale, bad = helpers.compare_rows(rows, requests, folder, FLOAT32_BOUND,
                                                  f"float32 {name}")
     else:
-        worst, scale, bad = helpers.compare_rows(rows, requests, folder, BFLOAT16_LOOSE,
+        worst, scale, bad = helpers.compare_rows(rows, requests, folder, BFLOAT16_BOUND[name],
                                                  f"bfloat16 {name} against exact plain")
-        assert not bad, f"{len(bad)} rows beyond the loose bound, first {bad[:3]}, worst {worst:.3e}"
+        assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
         worst, scale, bad = helpers.compare_rows(rows, requests, folder, BFLOAT16_BOUND[name],
                                                  f"bfloat16 {name} against plain stored in bfloat16",
                                                  store=torch.bfloat16)

@@ -31,13 +31,12 @@ SHAPE = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_
              tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False)
 LENGTHS = {"a": 150, "b": 72, "c": 48, "d": 33}
 # relative to max(1, largest |plain logit| of the row).  float32: the reference's own bar between
-# its modes (tests/cpp/test_cuda_model.cpp:57, 66).  bfloat16: against the plain implementation
-# that stores every operation's result in bfloat16 as the engine does (what is left is the
-# order of the sums and the rounding of the attention weights; about 2.5 times what was seen,
-# the terminal summary prints it), and loosely against the exact plain logits, from which
-# storage rounding alone moves 2 layers by 1.8e-2 and 28 layers by 4.5e-2.
-BOUND = {"float32": 1e-4, "bfloat16": 4e-2 if LAYERS <= 4 else 1.2e-1}
-BOUND_STORED = 4e-2
+# its modes (tests/cpp/test_cuda_model.cpp:57, 66); 7.9e-6 was seen.  bfloat16: 2.5 times what was
+# seen on a B200 (the terminal summary prints it): 1.8e-2 at 2 layers against the exact plain
+# logits, 1.2e-2 against the plain implementation that stores every result in bfloat16 as the
+# engine does; rounding accumulates with depth, 28 layers were seen at 4.5e-2.
+BOUND = {"float32": 1e-4, "bfloat16": 4.4e-2 if LAYERS <= 2 else 1.2e-1}
+BOUND_STORED = 3.0e-2 if LAYERS <= 2 else 1.2e-1
 PAGE = 16
 
 
