@@ -248,8 +248,9 @@ def run(args):
             ms = timer(lambda: torch.nn.functional.linear(x, w))
         else:
             x, w = rand(m, k), rand(n, k)
-            ms = timer(lambda: ops.gemm_f32(x, w, None))
+            ms = timer(lambda: ops.gemm_f32(x, w, None, kind=args.f32_kind, rows_per_warp=args.f32_rows_per_warp))
             elem = 4
+            extra = {"frac_ffma": round(2.0 * m * n * k / (ms * 1e-3) / 74.4e12, 3), "f32_kind": args.f32_kind}
         nbytes, flops = (m * k + n * k + m * n) * elem, 2.0 * m * n * k
     else:
         raise SystemExit(f"unknown kernel {args.kernel}")
@@ -260,7 +261,7 @@ def run(args):
               "frac_hbm": round(gbs / peak["hbm_gbs"], 3),
               "frac_bf16": round(tflops / peak["bf16_tflops"], 3), "peaks": peak["source"],
               "sizes": {k: v for k, v in vars(args).items()
-                        if k not in ("kernel", "dtype", "warmup", "iters", "no_flush")}}
+                        if k not in ("kernel", "dtype", "warmup", "iters", "no_flush", "f32_kind", "f32_rows_per_warp")}}
     record.update(extra)
     print(json.dumps(record))
 
@@ -285,6 +286,10 @@ def main(argv=None) -> int:
     parser.add_argument("--nsplit", type=int, default=0, help="0 = the engine's choice")
     parser.add_argument("--variant", default="mma", choices=["mma", "tc"],
                         help="bfloat16 attention: mma.sync with cp.async loads, or tcgen05")
+    parser.add_argument("--f32-kind", default="auto", choices=["auto", "rows", "tiles", "plain"],
+                        help="gemm_f32: which of the float32 kernels (frac_ffma is of the nominal "
+                             "74.4 TFLOP/s: 148 SMs x 128 lanes x 2 x 1.965 GHz)")
+    parser.add_argument("--f32-rows-per-warp", type=int, default=0, choices=[0, 1, 2, 4])
     parser.add_argument("--top-k", type=int, default=0)
     parser.add_argument("--top-p", type=float, default=1.0)
     parser.add_argument("--warmup", type=int, default=3)

@@ -84,7 +84,9 @@ def core():
         lib.fsie_rope_kv_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p]
         lib.fsie_swiglu.argtypes = [p, p, ll, i, i, p]
         lib.fsie_place_tokens.argtypes = [p, p, p, p, i, p]
-        lib.fsie_gemm_f32.argtypes = [p, p, p, p, i, i, i, i, i, p]
+        lib.fsie_gemm_f32.argtypes = [p, p, p, p, i, i, i, i, i, i, i, p]
+        lib.fsie_gemm_f32_rows_limit.argtypes = []
+        lib.fsie_gemm_f32_rows_limit.restype = i
         lib.fsie_attn_generic.argtypes = [p, i, p, p, ll, i, p, i, p, p, i, p, p, p, p, i, p, p,
                                           i, i, i, i, i, i, f, i, p]
         lib.fsie_attn_generic_rows.argtypes = []
@@ -205,9 +207,21 @@ def place_tokens(ids: torch.Tensor, dst_and_row: torch.Tensor, chosen: torch.Ten
 
 
 # --------------------------------------------------------------------- float32 product
+GEMM_F32_KINDS = {"auto": 0, "rows": 1, "tiles": 2, "plain": 3}
+
+
+def gemm_f32_rows_limit() -> int:
+    """Rows of x up to which the float32 product takes its few-rows kernel."""
+    return int(core().fsie_gemm_f32_rows_limit())
+
+
 def gemm_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
-             out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out = x @ weight.T (+ bias), all float32, plain FFMA (no tensor-core mode)."""
+             out: Optional[torch.Tensor] = None, kind: str = "auto",
+             rows_per_warp: int = 0) -> torch.Tensor:
+    """out = x @ weight.T (+ bias), all float32, plain FFMA (no tensor-core mode).  `kind`
+    names one of the three kernels (few rows, tiles, plain) instead of the choice by size;
+    `rows_per_warp` (1, 2, 4) fixes how many rows of the weight a warp of the few-rows kernel
+    owns instead of the choice by size."""
     _need(x, torch.float32, "x", contiguous=False)
     _need(weight, torch.float32, "weight")
     if x.dim() != 2 or x.stride(1) != 1:
@@ -220,9 +234,13 @@ def gemm_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]
         _need(bias, torch.float32, "bias")
     if out is None:
         out = torch.empty((m, n), dtype=torch.float32, device=x.device)
-    _need(out, torch.float32, "out")
+    _need(out, torch.float32, "out", contiguous=False)
+    if out.shape != (m, n) or out.stride(1) != 1:
+        raise KernelError("gemm_f32: out must be [rows of x, rows of weight] with unit inner stride")
     _check(core().fsie_gemm_f32(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), m, n, k,
-                                x.stride(0), n, _stream()), "gemm_f32")
+                                x.stride(0), out.stride(0), GEMM_F32_KINDS[kind], int(rows_per_warp),
+                                _stream()),
+           "gemm_f32")
     return out
 
 

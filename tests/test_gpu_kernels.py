@@ -139,19 +139,47 @@ def test_swiglu(ops, dtype):
 
 
 # ---------------------------------------------------------------------- float32 product
-@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (37, 101, 203), (64, 64, 16), (130, 70, 1000)])
-def test_gemm_f32(ops, m, n, k):
+GEMM_F32_SIZES = [(1, 7, 5), (37, 101, 203), (64, 64, 16), (130, 70, 1000), (1, 96, 512),
+                  (8, 4608, 3584), (16, 3584, 1000), (13, 77, 132), (40, 300, 644), (64, 1024, 2048),
+                  (200, 130, 260), (129, 257, 516), (2048, 512, 384)]
+
+
+@pytest.mark.parametrize("kind", ["auto", "rows", "tiles", "plain"])
+@pytest.mark.parametrize("m,n,k", GEMM_F32_SIZES)
+def test_gemm_f32(ops, m, n, k, kind):
+    """The three float32 kernels (few rows, tiles, plain) and the choice among them, each
+    against the 64-bit product, with and without bias, at sizes that are no multiples of
+    their tiles."""
+    from from_scratch_inference_engine_b200.kernels.ops import KernelError
     torch.manual_seed(4)
     x, w, b = torch.randn(m, k), torch.randn(n, k), torch.randn(n)
     want = x.double() @ w.double().T + b.double()
-    got = ops.gemm_f32(dev(x), dev(w), dev(b))
-    assert (got.cpu().double() - want).abs().max().item() < 1e-5 * math.sqrt(k) * 4
-    got = ops.gemm_f32(dev(x), dev(w), None)
-    assert (got.cpu().double() - (want - b.double())).abs().max().item() < 1e-5 * math.sqrt(k) * 4
-    # a row's result does not depend on the other rows of the launch
-    alone = ops.gemm_f32(dev(x[m // 2:m // 2 + 1]), dev(w), dev(b))
-    both = ops.gemm_f32(dev(x), dev(w), dev(b))
-    assert torch.equal(alone[0], both[m // 2])
+    takes = {"auto": True, "plain": True, "tiles": k % 4 == 0,
+             "rows": k % 4 == 0 and m <= ops.gemm_f32_rows_limit()}[kind]
+    if not takes:
+        with pytest.raises(KernelError):
+            ops.gemm_f32(dev(x), dev(w), dev(b), kind=kind)
+        return
+    bound = 1e-5 * math.sqrt(k) * 4
+    got = ops.gemm_f32(dev(x), dev(w), dev(b), kind=kind)
+    assert (got.cpu().double() - want).abs().max().item() < bound
+    got = ops.gemm_f32(dev(x), dev(w), None, kind=kind)
+    assert (got.cpu().double() - (want - b.double())).abs().max().item() < bound
+    # a row's result does not depend on the other rows of the launch (same kernel)
+    alone = ops.gemm_f32(dev(x[m // 2:m // 2 + 1]), dev(w), dev(b), kind=kind)
+    both = ops.gemm_f32(dev(x), dev(w), dev(b), kind=kind)
+    if kind != "auto" or (m <= ops.gemm_f32_rows_limit()) or k % 4:
+        assert torch.equal(alone[0], both[m // 2])
+    else:       # the single row took the few-rows kernel, the batch the tiles: another order of the sums
+        assert (alone[0] - both[m // 2]).abs().max().item() < bound
+    # x as a view with a row stride (rows of a wider matrix), output into a wider matrix
+    if k % 4 == 0 and kind != "plain":
+        wide = torch.randn(m, k + 8)
+        out = torch.full((m, n + 3), float("nan"), device="cuda")
+        ops.gemm_f32(dev(wide)[:, 4:4 + k], dev(w), dev(b), out=out[:, :n], kind=kind)
+        again = wide[:, 4:4 + k].double() @ w.double().T + b.double()
+        assert (out[:, :n].cpu().double() - again).abs().max().item() < bound
+        assert torch.isnan(out[:, n:]).all()
 
 
 # --------------------------------------------------------------------------- attention
