@@ -279,6 +279,21 @@ class CacheManager:
             self.prefix_hits += 1
         return matched
 
+    def release_prefix(self, handle: RequestCache) -> None:
+        """Undo `acquire_prefix` for a request that has run nothing since: the shared pages are
+        given back (they stay cached) and the request holds nothing again."""
+        if handle.length != handle.shared_tokens:
+            raise RuntimeError(f"request {handle.request_id!r} has run tokens of its own")
+        if handle.shared_tokens:
+            self.prefix_hits -= 1
+        for g, table in enumerate(handle.tables):
+            for page in table:
+                if page >= 0:
+                    self._free(g, page)
+            table.clear()
+        handle._arrays = None
+        handle.length = handle.shared_tokens = 0
+
     def register_prefix(self, handle: RequestCache, tokens: Sequence[int]) -> None:
         """Remember the request's full pages covering `tokens` for later requests
         (src/kvcache/block_manager.cpp:175-204); the cache holds its own reference."""

@@ -174,6 +174,23 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const int kblocks = (p.K + BK - 1) / BK;
     const int total_tiles = p.m_tiles * p.n_tiles;
+    // Order of the tiles: bands of up to RASTER_M tiles of rows, inside a band the rows run
+    // fastest.  The pairs of blocks work on consecutive tiles at the same time, so a wave of
+    // them covers a roughly square patch of y and fetches as few rows of x and w as 74 tiles
+    // can need - with more than 2,048 rows of x, walking all rows for each column of tiles
+    // would read the whole of x once per two or three columns (for the down product that is
+    // more than L2 holds, and the product becomes bound by HBM instead of the tensor cores).
+    constexpr int RASTER_M = 8;
+    auto tile_m = [&](int tile) {
+        const int band = tile / (RASTER_M * p.n_tiles), first = band * RASTER_M;
+        const int height = min(RASTER_M, p.m_tiles - first);
+        return first + (tile - band * RASTER_M * p.n_tiles) % height;
+    };
+    auto tile_n = [&](int tile) {
+        const int band = tile / (RASTER_M * p.n_tiles), first = band * RASTER_M;
+        const int height = min(RASTER_M, p.m_tiles - first);
+        return (tile - band * RASTER_M * p.n_tiles) / height;
+    };
     constexpr int TILE_COLS = EPI == EPI_SWIGLU ? TILE / 2 : TILE;      // output columns per tile
 
     if (threadIdx.x == 0) {
@@ -201,11 +218,11 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         int it = 0, issued = 0;
         bool ok = true;
         auto w_row_of = [&](int tile) {
-            const int n0 = (tile / p.m_tiles) * TILE_COLS;
+            const int n0 = tile_n(tile) * TILE_COLS;
             return EPI == EPI_SWIGLU ? (rank == 0 ? n0 : p.up_row0 + n0) : n0 + rank * HALF;
         };
         for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
-            const int m0 = (tile % p.m_tiles) * TILE + rank * HALF;
+            const int m0 = tile_m(tile) * TILE + rank * HALF;
             const int w_row = w_row_of(tile);
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
                 const int s = it % STAGES;
@@ -277,8 +294,8 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         int local_tile = 0, groups = 0;
         for (int tile = pair; tile < total_tiles; tile += pairs, ++local_tile) {
             const int buf = local_tile & 1;
-            const int row0 = (tile % p.m_tiles) * TILE + rank * HALF + quarter * 32;
-            const int n0 = (tile / p.m_tiles) * TILE_COLS;
+            const int row0 = tile_m(tile) * TILE + rank * HALF + quarter * 32;
+            const int n0 = tile_n(tile) * TILE_COLS;
             if (*(volatile int*)&abort_flag) break;
             if (!mbar_wait(&acc_full[buf], (local_tile >> 1) & 1)) {
                 atomicExch(p.error, ERR_EPILOGUE_WAIT); atomicExch(&abort_flag, 1); break;

@@ -168,17 +168,6 @@ class Scheduler:
         while True:
             items: List[PlanItem] = []
             tokens_left = self.max_step_tokens
-            if cache.prefix_enabled:
-                # before any page of this step is budgeted: a shared page that only the prefix
-                # cache held counted as free until a request took it
-                for sid in self.running:
-                    seq = self.sequences[sid]
-                    handle = seq.handle
-                    if seq.prefilled or handle.length or any(handle.tables):
-                        continue
-                    cap = ((seq.context_length() - 1) // cache.page_size) * cache.page_size
-                    if cap > 0:
-                        cache.acquire_prefix(handle, seq.context_slice(0, cap))
             pages_left = cache.free_pages()
 
             def take(handle, n) -> bool:
@@ -209,6 +198,23 @@ class Scheduler:
                     continue
                 total = seq.context_length()
                 handle = seq.handle
+                if cache.prefix_enabled and handle.length == 0 and not any(handle.tables):
+                    # Shared pages are looked for only now that the request gets its first tokens:
+                    # the longer it waits, the more of its prefix others have registered.  A
+                    # shared page that only the prefix cache held counted as free until this
+                    # moment, so what the acquisition pins comes out of this step's budget - and
+                    # if earlier items of the step were already promised those pages, the
+                    # acquisition is undone and the request waits for the next step.
+                    cap = ((total - 1) // cache.page_size) * cache.page_size
+                    if cap > 0:
+                        before = cache.free_pages()
+                        cache.acquire_prefix(handle, seq.context_slice(0, cap))
+                        left = [have - (b - a) for have, b, a
+                                in zip(pages_left, before, cache.free_pages())]
+                        if any(v < 0 for v in left):
+                            cache.release_prefix(handle)
+                            continue
+                        pages_left = left
                 remaining = total - handle.length
                 chunk = min(remaining, tokens_left)
                 # shrink the portion to the pages that are left

@@ -614,6 +614,22 @@ def test_gemm_tiles_swiglu_epilogue(ops, rows, inter, k, blocks):
     assert (out.double() - want).abs().max().item() < 2.5e-2 * want.abs().max().item()
 
 
+@pytest.mark.parametrize("rows,blocks", [(2600, 148), (2600, 6), (4200, 10), (2049, 148)])
+def test_gemm_tiles_bands_of_row_tiles(ops, rows, blocks):
+    """More than eight tiles of rows: the tiles are walked in bands of eight row tiles, the
+    last band lower than the others.  Every output must be written once and be the right one."""
+    torch.manual_seed(rows)
+    n, k = 520, 136
+    x = dev(torch.randn(rows, k), torch.bfloat16)
+    w = dev(torch.randn(n, k) / math.sqrt(k), torch.bfloat16)
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full((rows, n), float("nan"), dtype=torch.float32, device="cuda")
+    ops.gemm_tiles(ops.TiledWeight(w), x, out, None, error, blocks)
+    want = x.double() @ w.double().T
+    assert error.item() == 0 and torch.isfinite(out).all()
+    assert (out.double() - want).abs().max().item() < 2e-3 * want.abs().max().item()
+
+
 def test_gemm_tiles_one_key_block_stands_out(ops):
     """One k-block of one row tile carries the whole result: a stage that is read too early,
     too late or for the wrong tile shows as a gross error, not as noise."""

@@ -252,6 +252,47 @@ def test_window_pool_that_can_never_hold_a_window_is_refused():
         s.add(list(range(10)), GREEDY, 4, -1, 0)
 
 
+def test_shared_pages_are_looked_for_when_a_request_starts_not_when_it_is_admitted():
+    """A short request has left the first two pages of a long common prefix in the cache.
+    Three requests behind that prefix are admitted together; the second and third start only
+    after the first has registered all of it, and must then share all six pages - not the
+    two that were there when they were admitted."""
+    # 19 tokens per step: exactly what the first of the three still has to run
+    s, cache = make(num_pages=64, page_size=4, prefix=True, max_step_tokens=19, max_batch=8)
+    stem = list(range(500, 524))                              # six pages
+    early = s.add(stem[:9], GREEDY, 2, -1, 0)
+    run_all(s, cache)
+    ids = [s.add(stem + [900 + k, 7, 7], GREEDY, 3, -1, 0) for k in range(3)]
+    shared = {}
+    while s.has_work():
+        run_step(s, cache)
+        for rid in ids:
+            handle = s.sequences[rid].handle
+            if handle is not None and handle.length:
+                shared.setdefault(rid, handle.shared_tokens)
+    assert shared == {ids[0]: 8, ids[1]: 24, ids[2]: 24}
+    assert all(s.sequences[r].output == alone(stem + [900 + k, 7, 7], 3) for k, r in enumerate(ids))
+
+
+def test_release_prefix_undoes_an_acquisition():
+    s, cache = make(num_pages=8, page_size=4, prefix=True)
+    first = s.add(list(range(40, 49)), GREEDY, 2, -1, 0)
+    run_all(s, cache)
+    assert cache.free_pages() == [8]                          # two cached pages count as free
+    handle = cache.open("x")
+    assert cache.acquire_prefix(handle, list(range(40, 48))) == 8
+    assert cache.free_pages() == [6] and cache.prefix_hits == 1
+    cache.release_prefix(handle)
+    assert cache.free_pages() == [8] and cache.prefix_hits == 0
+    assert handle.length == 0 and handle.tables == [[]]
+    cache.check()
+    cache.reserve(handle, 5)
+    cache.commit(handle, 5)
+    with pytest.raises(RuntimeError, match="tokens of its own"):
+        cache.release_prefix(handle)
+    cache.close(handle)
+
+
 def test_windowed_group_bounds_what_a_request_holds():
     needs = [NEED, CacheNeed(1, 16, window=8)]
     s, cache = make(num_pages=[40, 6], page_size=4, needs=needs, max_step_tokens=8)
