@@ -34,8 +34,8 @@ LENGTHS = {"a": 150, "b": 72, "c": 48, "d": 33}
 # its modes (tests/cpp/test_cuda_model.cpp:57, 66); 7.9e-6 was seen.  bfloat16: 2.5 times what was
 # seen on a B200 (the terminal summary prints it): 1.8e-2 at 2 layers against the exact plain
 # logits, 1.2e-2 against the plain implementation that stores every result in bfloat16 as the
-# engine does; rounding accumulates with depth, 28 layers were seen at 4.5e-2.
-BOUND = {"float32": 1e-4, "bfloat16": 4.4e-2 if LAYERS <= 2 else 1.2e-1}
+# engine does; rounding accumulates with depth: 28 layers were seen at 7.3e-2 and 4.8e-2 (float32: 3.3e-5).
+BOUND = {"float32": 1e-4, "bfloat16": 4.4e-2 if LAYERS <= 2 else 1.8e-1}
 BOUND_STORED = 3.0e-2 if LAYERS <= 2 else 1.2e-1
 PAGE = 16
 
@@ -141,5 +141,8 @@ def test_replay_at_the_7b_layer_sizes(shape_model, mode):
     if mode == "bfloat16-tcgen05-forced":
         assert calls["gemm_tiles"] > 0 and calls["attention_tc_decode"] > 0
     if dtype == "float32":
-        # cutting the work differently moves nothing beyond rounding
-        assert max(report.values()) - min(report.values()) < 2e-5
+        # Cutting the work differently moves nothing beyond rounding.  Steps of up to 64 tokens and
+        # longer ones take float32 product kernels that add in different orders (a tree over 32
+        # lanes; one chain over k): at 2 layers every family showed the same 7.9e-6, at 28 layers
+        # the families of long steps 3.3e-5 and those of short steps 7.8e-6.
+        assert max(report.values()) - min(report.values()) < 5e-5
