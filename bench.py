@@ -374,6 +374,9 @@ def main() -> int:
                         help="contexts at which decoding at --batch is also timed ('' = none)")
     parser.add_argument("--dtype", default="bf16", choices=["bf16", "bfloat16", "fp32", "float32"],
                         help="compute dtype of the whole run (the default run adds a short fp32 section)")
+    parser.add_argument("--few-token-limit", type=int, default=0,
+                        help="steps of up to this many tokens take the engine's few-token tcgen05 product "
+                             "(0 = the engine's choice, 16; up to 64 for measuring that choice)")
     parser.add_argument("--fp32-steps", type=int, default=8,
                         help="decode steps timed on the float32 path after the bf16 run (0 = skip)")
     parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long"],
@@ -413,8 +416,9 @@ def main() -> int:
     rng = np.random.default_rng(0)
     compute = "bfloat16" if args.dtype in ("bf16", "bfloat16") else "float32"
     bytes_per = 2 if compute == "bfloat16" else 4
+    options = {"few_token_limit": args.few_token_limit} if args.few_token_limit else {}
     model = LoadedModel.from_random(config, seed=0, std=0.02, dtype=compute,
-                                    max_positions=args.context + 64)
+                                    max_positions=args.context + 64, **options)
     device = model.runtime.device
 
     def timed(fn, count):

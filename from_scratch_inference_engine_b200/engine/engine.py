@@ -61,7 +61,7 @@ class LoadedModel:
 
     @classmethod
     def from_random(cls, config, seed: int = 0, std: float = 0.02, dtype="bfloat16",
-                    device="cuda:0", max_positions: int = 0) -> "LoadedModel":
+                    device="cuda:0", max_positions: int = 0, **runtime_options) -> "LoadedModel":
         """Random weights drawn on the device (no folder is written): N(0, std) matrices and
         biases, gains 1 + N(0, std), rounded to bfloat16 first so that both compute dtypes see
         the same numbers.  For benchmarks at sizes whose checkpoint would take minutes to
@@ -69,7 +69,7 @@ class LoadedModel:
         from ..parts.model import tensor_specs
         from ..weights.random_init import random_tensors_on_device
         tensors = random_tensors_on_device(tensor_specs(config.build_spec()), seed, std, device)
-        return cls.from_tensors(config, tensors, dtype, device, max_positions)
+        return cls.from_tensors(config, tensors, dtype, device, max_positions, **runtime_options)
 
     def forward(self, ids: Sequence[int]) -> torch.Tensor:
         """Logits [len(ids), vocab] of one whole sequence (bindings/module.cpp:70-76)."""

@@ -40,7 +40,7 @@ class Runtime:
     def __init__(self, device="cuda:0", dtype=torch.bfloat16, max_positions: int = 0,
                  few_token_min_elements: int = 32 * 1024 * 1024, products: str = "own",
                  tiled_min_tiles: Optional[int] = None,
-                 decode_tcgen05_min_blocks: Optional[int] = None):
+                 decode_tcgen05_min_blocks: Optional[int] = None, few_token_limit: int = 16):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this engine has no CPU path")
         self.device = torch.device(device)
@@ -53,8 +53,12 @@ class Runtime:
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
         # weights prepared for the tcgen05 product of steps with few tokens, by storage address
         self._few_token_weights: Dict[int, ops.DecodeWeight] = {}
-        self.few_token_limit = 16          # steps of up to this many tokens take that product
-        self.few_token_limit_fused = 16    # ... the same for the product with the fused SwiGLU
+        if not 1 <= few_token_limit <= ops.GEMM_DECODE_MAX_TOKENS:
+            raise ValueError(f"few_token_limit must lie in 1..{ops.GEMM_DECODE_MAX_TOKENS}")
+        # steps of up to this many tokens take that product (16: beyond it the library measured
+        # faster; up to 64 is possible and is what measurements of that choice set)
+        self.few_token_limit = int(few_token_limit)
+        self.few_token_limit_fused = int(few_token_limit)    # ... the same with the fused SwiGLU
         self.few_token_min_elements = few_token_min_elements   # ... for matrices at least this large
         # "own": steps of many tokens take the tiled tcgen05 product (fused bias / SwiGLU) where
         # its tiles fill the GPU; "library": they take the library product

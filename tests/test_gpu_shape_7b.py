@@ -141,7 +141,7 @@ def test_replay_at_the_7b_layer_sizes(shape_model, mode):
     if mode == "bfloat16-tcgen05-forced":
         assert calls["gemm_tiles"] > 0 and calls["attention_tc_decode"] > 0
     if dtype == "float32":
-        # Cutting the work differently moves nothing beyond rounding.  Steps of up to 64 tokens and
+        # Cutting the work differently moves nothing beyond rounding.  Steps of up to 48 tokens and
         # longer ones take float32 product kernels that add in different orders (a tree over 32
         # lanes; one chain over k): at 2 layers every family showed the same 7.9e-6, at 28 layers
         # the families of long steps 3.3e-5 and those of short steps 7.8e-6.
