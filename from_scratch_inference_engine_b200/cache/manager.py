@@ -137,11 +137,13 @@ class CacheManager:
         self._prefix: Dict[int, List[_PrefixEntry]] = {}
         # cached entries from least to most recently used, and by their page in group 0 (the
         # pages of an entry are always shared together, so group 0 speaks for all of them);
-        # _evictable counts the entries nobody but the cache holds, kept up to date on every
-        # reference change so that free_pages() costs nothing per step
+        # _idle holds the entries nobody but the cache holds, in the order in which their last
+        # holder let go of them, kept up to date on every reference change: free_pages() costs
+        # nothing per step and an eviction takes the first of them without walking past the
+        # entries that live requests still hold
         self._lru: "OrderedDict[int, _PrefixEntry]" = OrderedDict()
         self._cached_page: Dict[int, _PrefixEntry] = {}
-        self._evictable = 0
+        self._idle: "OrderedDict[int, _PrefixEntry]" = OrderedDict()
         self._tick = 0
         self.prefix_hits = 0
 
@@ -190,17 +192,18 @@ class CacheManager:
 
     def free_pages(self) -> List[int]:
         """Free pages per group, counting cached prefix pages nobody else holds."""
-        return [pool.num_free + self._evictable for pool in self.pools]
+        return [pool.num_free + len(self._idle) for pool in self.pools]
 
     def _incref(self, g: int, page: int) -> None:
         if g == 0 and page in self._cached_page and self.pools[0].ref_count(page) == 1:
-            self._evictable -= 1              # a request shares it again
+            del self._idle[id(self._cached_page[page])]       # a request shares it again
         self.pools[g].incref(page)
 
     def _free(self, g: int, page: int) -> None:
         self.pools[g].free(page)
         if g == 0 and page in self._cached_page and self.pools[0].ref_count(page) == 1:
-            self._evictable += 1              # only the cache holds it now
+            entry = self._cached_page[page]
+            self._idle[id(entry)] = entry     # only the cache holds it now
 
     def can_reserve(self, handle: RequestCache, n_new: int,
                     budget: Optional[List[int]] = None) -> bool:
@@ -329,18 +332,19 @@ class CacheManager:
             del self._prefix[h]
         del self._lru[id(entry)]
         del self._cached_page[entry.pages[0]]
-        if self.pools[0].ref_count(entry.pages[0]) == 1:
-            self._evictable -= 1
+        self._idle.pop(id(entry), None)
         for g, page in enumerate(entry.pages):
             self.pools[g].free(page)
 
     def _evict_one(self) -> bool:
-        """Drop the least recently used entry that only the cache holds."""
-        for entry in self._lru.values():
-            if self.pools[0].ref_count(entry.pages[0]) == 1:
-                self._drop_entry(entry)
-                return True
-        return False
+        """Drop the entry that only the cache holds and that has been idle longest (the
+        reference evicts by the tick of the last use among such entries,
+        src/kvcache/block_manager.cpp:206-212; an entry's last holder lets go of it after its
+        last use, so the order is nearly the same and costs no search)."""
+        if not self._idle:
+            return False
+        self._drop_entry(next(iter(self._idle.values())))
+        return True
 
     def clear_prefix_cache(self) -> None:
         for entry in list(self._lru.values()):
@@ -363,7 +367,7 @@ class CacheManager:
                 if count != pool.ref_count(page):
                     raise AssertionError(f"group {g} page {page}: {count} holders but "
                                          f"reference count {pool.ref_count(page)}")
-        evictable = sum(1 for e in self._lru.values() if self.pools[0].ref_count(e.pages[0]) == 1)
-        if evictable != self._evictable or len(self._lru) != sum(map(len, self._prefix.values())):
-            raise AssertionError(f"prefix cache accounting: {self._evictable} evictable counted, "
-                                 f"{evictable} found")
+        idle = {id(e) for e in self._lru.values() if self.pools[0].ref_count(e.pages[0]) == 1}
+        if idle != set(self._idle) or len(self._lru) != sum(map(len, self._prefix.values())):
+            raise AssertionError(f"prefix cache accounting: {len(self._idle)} idle entries listed, "
+                                 f"{len(idle)} found")
