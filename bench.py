@@ -528,6 +528,12 @@ def main() -> int:
         engine.step()
     ring, sampler = engine.runner._ring, engine.sampler
     h2d0, d2h0 = ring.bytes_staged + sampler.bytes_to_device, sampler.bytes_to_host
+    # The engine overlaps its steps: one is always in flight.  The clock starts after the step
+    # that the warm-up left in flight has completed, and stops when the last of the K steps
+    # launched inside the region has completed: exactly K steps, each with its copy of inputs
+    # from pinned memory and its read of the chosen tokens, the first of them launched onto an
+    # idle GPU.  The slower of the host's clock and the device's events counts.
+    torch.cuda.synchronize()
     wall = time.perf_counter()
     ms_e2e = timed(lambda index: engine.step(), steps)
     wall = (time.perf_counter() - wall) * 1000.0 / steps
