@@ -82,7 +82,7 @@ class LoadedModel:
         handle = runner.cache.open(0)
         logits = runner.step([StepEntry(handle, list(ids), list(range(len(ids))))])
         runner.raise_on_device_error()
-        return logits
+        return logits.clone()          # a step's logits live in working memory that the next step reuses
 
 
 class Engine:

@@ -48,6 +48,7 @@ class Runtime:
         self.max_positions = int(max_positions)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._tables: Dict[object, torch.Tensor] = {}
+        self._buffers: Dict[object, torch.Tensor] = {}
         self._f32_out: Optional[bool] = None
         # device-side error flag that kernels set when they refuse an input or give up a wait
         self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -81,6 +82,25 @@ class Runtime:
         self.fused_qkv_rope = True
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+    def buffer(self, tag: Optional[str], rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """[rows, cols] of working memory for one operation's result.
+
+        With a `tag` the memory is kept and handed out again to whoever asks under the same tag
+        (grown when more is needed): a step's operations run one after the other on one stream,
+        so a result may live in the same place as the result of the same operation of the
+        layer before it, and nothing is asked of the allocator per operation.  The caller
+        guarantees that the earlier result under the tag is dead when it asks again.  Without a
+        tag, and while a CUDA graph is being captured (whose memory must be the graph's own),
+        the memory is fresh."""
+        if tag is None or torch.cuda.is_current_stream_capturing():
+            return torch.empty((rows, cols), dtype=dtype, device=self.device)
+        key = (tag, dtype)
+        have = self._buffers.get(key)
+        if have is None or have.numel() < rows * cols:
+            have = torch.empty(max(rows * cols, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = have
+        return have[:rows * cols].view(rows, cols)
 
     def pages_map(self, pages: torch.Tensor):
         """TMA descriptor of a cache group's page tensor (made once per tensor), or None when
@@ -130,8 +150,8 @@ class Runtime:
             prepared = self._tiled_weights[weight.data_ptr()] = ops.TiledWeight(prepared[0], swiglu)
         return prepared
 
-    def _tiled_product(self, prepared, x, bias, out_dtype) -> torch.Tensor:
-        out = torch.empty((x.shape[0], prepared.n), dtype=out_dtype, device=x.device)
+    def _tiled_product(self, prepared, x, bias, out_dtype, tag=None) -> torch.Tensor:
+        out = self.buffer(tag, x.shape[0], prepared.n, out_dtype)
         return ops.gemm_tiles(prepared, x, out, bias, self.error, self.sm_count)
 
     def _few_tokens(self, x: torch.Tensor, weight: torch.Tensor) -> Optional["ops.DecodeWeight"]:
@@ -143,27 +163,32 @@ class Runtime:
         limit = self.few_token_limit_fused if prepared.swiglu else self.few_token_limit
         return prepared if x.shape[0] <= limit else None
 
-    def _few_token_product(self, prepared, x, bias, out_dtype) -> torch.Tensor:
-        out = torch.empty((x.shape[0], prepared.n), dtype=out_dtype, device=x.device)
+    def _few_token_product(self, prepared, x, bias, out_dtype, tag=None) -> torch.Tensor:
+        out = self.buffer(tag, x.shape[0], prepared.n, out_dtype)
         tiles = -(-prepared.n // (64 if prepared.swiglu else 128))
         splits = ops.gemm_decode_splits(tiles, prepared.k, self.sm_count)
         return ops.gemm_decode(prepared, x, out, bias, self.error, splits)
 
     def linear(self, x: torch.Tensor, weight: torch.Tensor,
-               bias: Optional[torch.Tensor]) -> torch.Tensor:
-        """x @ weight.T (+ bias) in the compute dtype."""
+               bias: Optional[torch.Tensor], tag: Optional[str] = None) -> torch.Tensor:
+        """x @ weight.T (+ bias) in the compute dtype.  `tag`: see `buffer` (the result may then
+        live where the last result under that tag lived)."""
         if self.dtype is torch.float32:
-            return ops.gemm_f32(x, weight, bias)
+            return ops.gemm_f32(x, weight, bias, self.buffer(tag, x.shape[0], weight.shape[0], torch.float32))
         prepared = self._few_tokens(x, weight)
         if prepared is not None and not prepared.swiglu:
-            return self._few_token_product(prepared, x, bias, torch.bfloat16)
+            return self._few_token_product(prepared, x, bias, torch.bfloat16, tag)
         tiled = self._tiled(x, weight)
         if tiled is not None and not tiled.swiglu:
-            return self._tiled_product(tiled, x, bias, torch.bfloat16)
+            return self._tiled_product(tiled, x, bias, torch.bfloat16, tag)
         if self._skinny(x, weight):
-            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
-            return ops.gemm_skinny(weight, x, out, bias)
-        return F.linear(x, weight, bias)
+            return ops.gemm_skinny(weight, x, self.buffer(tag, x.shape[0], weight.shape[0], torch.bfloat16), bias)
+        if tag is None or x.dtype is not torch.bfloat16:
+            return F.linear(x, weight, bias)
+        out = self.buffer(tag, x.shape[0], weight.shape[0], torch.bfloat16)
+        if bias is None:
+            return torch.mm(x, weight.t(), out=out)
+        return torch.addmm(bias, x, weight.t(), out=out)
 
     def _skinny(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
         """Whether the set-up-free product takes this step: few tokens, and a matrix that the
@@ -187,37 +212,39 @@ class Runtime:
                 and self._skinny(x, weight)
                 and weight.shape[0] == (heads + 2 * kv_heads) * head_dim):
             return None
-        out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+        out = self.buffer("qkv", x.shape[0], weight.shape[0], torch.bfloat16)
         return ops.gemm_skinny_qkv_rope(weight, x, out, bias, positions, cos_sin, slot_of, k_pages,
                                         v_pages, page_stride, page_size, heads, kv_heads, head_dim,
                                         self.error)
 
-    def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    def linear_swiglu(self, x: torch.Tensor, gate_up: torch.Tensor,
+                      tag: Optional[str] = None) -> torch.Tensor:
         """silu(x @ gate.T) * (x @ up.T) for the stacked weight [gate rows; up rows]: one fused
         kernel for steps of few tokens, else the library product and the SwiGLU kernel."""
         prepared = self._few_tokens(x, gate_up) if self.dtype is torch.bfloat16 else None
         if prepared is not None and prepared.swiglu:
-            return self._few_token_product(prepared, x, None, torch.bfloat16)
+            return self._few_token_product(prepared, x, None, torch.bfloat16, tag)
         tiled = self._tiled(x, gate_up) if self.dtype is torch.bfloat16 else None
         if tiled is not None and tiled.swiglu:
-            return self._tiled_product(tiled, x, None, torch.bfloat16)
-        both = self.linear(x, gate_up, None) if prepared is None else F.linear(x, gate_up)
-        act = torch.empty((x.shape[0], gate_up.shape[0] // 2), dtype=both.dtype, device=x.device)
+            return self._tiled_product(tiled, x, None, torch.bfloat16, tag)
+        wide = None if tag is None else tag + ".gate_up"
+        both = self.linear(x, gate_up, None, wide) if prepared is None else F.linear(x, gate_up)
+        act = self.buffer(tag, x.shape[0], gate_up.shape[0] // 2, both.dtype)
         return ops.swiglu(both, act)
 
-    def linear_f32_out(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    def linear_f32_out(self, x: torch.Tensor, weight: torch.Tensor,
+                       tag: Optional[str] = None) -> torch.Tensor:
         """x @ weight.T with a float32 result (the logits)."""
         if self.dtype is torch.float32:
-            return ops.gemm_f32(x, weight, None)
+            return ops.gemm_f32(x, weight, None, self.buffer(tag, x.shape[0], weight.shape[0], torch.float32))
         prepared = self._few_tokens(x, weight)
         if prepared is not None and not prepared.swiglu:
-            return self._few_token_product(prepared, x, None, torch.float32)
+            return self._few_token_product(prepared, x, None, torch.float32, tag)
         tiled = self._tiled(x, weight)
         if tiled is not None and not tiled.swiglu:
-            return self._tiled_product(tiled, x, None, torch.float32)
+            return self._tiled_product(tiled, x, None, torch.float32, tag)
         if self._skinny(x, weight):
-            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
-            return ops.gemm_skinny(weight, x, out, None)
+            return ops.gemm_skinny(weight, x, self.buffer(tag, x.shape[0], weight.shape[0], torch.float32), None)
         if self._f32_out is None:
             try:
                 torch.mm(x[:1], weight[:8].t(), out_dtype=torch.float32)

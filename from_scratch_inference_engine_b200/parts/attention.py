@@ -109,11 +109,13 @@ class GqaAttention(Mixer):
                 self.head_dim, self.position.rotary_dim)
         qkv = rt.qkv_rotated_and_cached(y, self.w_qkv, self.b_qkv, *rope)
         if qkv is None:
-            qkv = rt.linear(y, self.w_qkv, self.b_qkv)
+            qkv = rt.linear(y, self.w_qkv, self.b_qkv, "qkv")
             ops.rope_kv_write(qkv, *rope, ctx.error)
-        out = torch.empty((tokens, self.q_width), dtype=qkv.dtype, device=qkv.device)
+        # working memory shared by all attention layers of a model: a layer's q, k, v and its
+        # attention output are dead when the next attention layer runs
+        out = rt.buffer("attention.out", tokens, self.q_width, qkv.dtype)
         self._attend(ctx, qkv, group, cache, out)
-        return rt.linear(out, self.w_o, None)
+        return rt.linear(out, self.w_o, None, "attention.o")
 
     def _attend(self, ctx, qkv: torch.Tensor, group, cache: LayerCache, out: torch.Tensor) -> None:
         """Attention of the step's tokens over the pages.  Work is cut into tiles of query

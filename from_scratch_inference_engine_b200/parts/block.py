@@ -9,6 +9,7 @@ import torch
 from ..config.spec import LayerSpec
 from ..weights.tensor_spec import TensorSpec
 from .base import LayerCache, Part, build_part, register_part
+from .norm import RMSNorm
 
 
 @register_part("arrangement", "prenorm")
@@ -46,7 +47,16 @@ class PreNormBlock(Part):
 
     def forward(self, ctx, x: torch.Tensor, delta: Optional[torch.Tensor],
                 cache: LayerCache) -> torch.Tensor:
-        y = self.mixer_norm.forward(x, delta)
+        # the normed rows are read by the sublayer that follows and by nothing after it
+        y = self._normed(self.mixer_norm, x, delta, "prenorm.mixer_in")
         mixed = self.mixer.forward(ctx, y, cache)
-        y = self.feed_forward_norm.forward(x, mixed)
+        y = self._normed(self.feed_forward_norm, x, mixed, "prenorm.feed_forward_in")
         return self.feed_forward.forward(ctx, y)
+
+    @staticmethod
+    def _normed(norm, x, delta, tag):
+        """A norm of this package is told where its result may live; any other norm part has the
+        plain interface forward(x, delta)."""
+        if isinstance(norm, RMSNorm):
+            return norm.forward(x, delta, tag=tag)
+        return norm.forward(x, delta)

@@ -41,4 +41,5 @@ class SwiGluMlp(Part):
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
         rt = self.runtime
-        return rt.linear(rt.linear_swiglu(y, self.w_gate_up), self.w_down, None)
+        # the activation and the result are dead when the next feed-forward of the model runs
+        return rt.linear(rt.linear_swiglu(y, self.w_gate_up, "swiglu.act"), self.w_down, None, "swiglu.down")

@@ -100,7 +100,7 @@ class DecoderModel:
         nothing is wanted).  `caches[i]` belongs to call i of the run order."""
         rt = self.runtime
         hidden = self.spec.hidden_size
-        x = torch.empty((ctx.num_tokens, hidden), dtype=torch.float32, device=rt.device)
+        x = rt.buffer("model.residual", ctx.num_tokens, hidden, torch.float32)
         ops.embed_gather(ctx.token_ids, self.embedding, x, ctx.error)
         delta = None
         for index, (layer, _, _) in enumerate(self.schedule):
@@ -108,7 +108,9 @@ class DecoderModel:
         if want_rows is None or want_rows.numel() == 0:
             return None
         y = self.final_norm.forward(x, delta, rows=want_rows, write_x=False)
-        return rt.linear_f32_out(y, self.head)
+        # the logits live where the last step's lived: whoever gets them reads them (or queues
+        # what reads them on this stream) before the next step runs
+        return rt.linear_f32_out(y, self.head, "model.logits")
 
 
 def _arrangement_spec(layer):

@@ -33,7 +33,9 @@ class RMSNorm(Part):
         self.gain = tensors[self.prefix + "weight"].contiguous()
 
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor],
-                rows: Optional[torch.Tensor] = None, write_x: bool = True) -> torch.Tensor:
+                rows: Optional[torch.Tensor] = None, write_x: bool = True,
+                tag: Optional[str] = None) -> torch.Tensor:
+        """`tag`: where the result may live (`Runtime.buffer`); None asks for fresh memory."""
         count = x.shape[0] if rows is None else rows.numel()
-        out = torch.empty((count, self.width), dtype=self.runtime.dtype, device=x.device)
+        out = self.runtime.buffer(tag, count, self.width, self.runtime.dtype)
         return ops.add_rmsnorm(x, delta, self.gain, self.eps, out, rows=rows, write_x=write_x)
