@@ -15,8 +15,8 @@ from .base import LayerCache, Mixer, build_part, register_part
 
 
 def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
-                     blocks_per_sm: int = 2, decode_slots: int = 3, decode_fixed: int = 270
-                     ) -> int:
+                     blocks_per_sm: int = 2, decode_slots: int = 3, decode_fixed: int = 270,
+                     merge_cost: int = 350) -> int:
     """Into how many key ranges to split each tile (at most 32, each at least 128 keys).
 
     Tiles of decoded tokens all have the same work, so the time is waves x (fixed cost of a
@@ -36,7 +36,9 @@ def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
     slots = decode_slots * sms
     best, best_cost = 1, None
     for n in range(1, max(1, min(32, longest // 128)) + 1):
-        cost = -(-blocks * n // slots) * (decode_fixed + longest / n)
+        # any split costs the launch that merges the partial results (`merge_cost`, in keys: 5 us
+        # after the mma.sync kernel at batch 8, 17 us after the tcgen05 kernel with 200 requests)
+        cost = -(-blocks * n // slots) * (decode_fixed + longest / n) + (merge_cost if n > 1 else 0)
         if best_cost is None or cost < best_cost * 0.98:
             best, best_cost = n, cost
     return best
@@ -150,7 +152,7 @@ class GqaAttention(Mixer):
                                   >= ctx.runtime.decode_tcgen05_min_blocks)
                 if decode_tcgen05:
                     nsplit = attention_splits(tiles.count * self.num_kv_heads, longest, sms, True,
-                                              decode_slots=2, decode_fixed=530)
+                                              decode_slots=2, decode_fixed=530, merge_cost=1300)
                 else:
                     nsplit = splits(tiles.count * self.num_kv_heads, longest, row_class == 0,
                                     1 if on_tcgen05 else 2)

@@ -426,7 +426,7 @@ def test_attention_tc_decode_long_contexts_with_the_engine_s_split(ops):
     from from_scratch_inference_engine_b200.parts.attention import attention_splits
     items = [(3900 + 13 * i, 1) for i in range(16)]
     case = PagedCase(torch.bfloat16, 28, 4, 128, 16, items=items, seed=31)
-    nsplit = attention_splits(16 * 4, 4100, 148, True, decode_slots=2, decode_fixed=530)
+    nsplit = attention_splits(16 * 4, 4100, 148, True, decode_slots=2, decode_fixed=530, merge_cost=1300)
     assert nsplit == 4
     for n in (1, nsplit):
         assert_rows_close(case.run_mma(ops, n, tc_decode=True), case.want, case, torch.bfloat16)

@@ -422,6 +422,10 @@ def test_key_splits_of_the_attention_launch():
     # decoded tokens, tcgen05 kernel (two blocks per SM, dearer blocks): one wave unsplit
     assert attention_splits(256, 4096, sms, True, decode_slots=2, decode_fixed=530) == 1
     assert attention_splits(148, 4096, sms, True, decode_slots=2, decode_fixed=530) == 2
+    # 200 requests x 2 kv heads, contexts of up to 2,560 keys (a serving step): two waves of whole
+    # key ranges beat three waves of halves once the merge launch is counted
+    assert attention_splits(400, 2560, sms, True, decode_slots=2, decode_fixed=530, merge_cost=1300) == 1
+    assert attention_splits(400, 2560, sms, True, decode_slots=2, decode_fixed=530, merge_cost=0) == 2
     # prompt tiles: as many splits as fill the slots, none when there are tiles enough
     assert attention_splits(2 * sms, 8192, sms, False) == 1
     assert attention_splits(sms // 2, 8192, sms, False) == 4
