@@ -190,6 +190,238 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o,
     }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Tiles of up to 16 query rows in float storage: decoded tokens (the heads of one group are
+// the rows) and short portions.  The kernel above gives such a tile to two of its eight warps;
+// here all 256 threads work on every chunk of 32 keys:
+//   scores   warp w owns rows w and w + 8, lane j key j of the chunk: a dot product over the
+//            head with q read as a broadcast and k row j in 16-byte pieces (rows padded by
+//            four floats, so the lanes' pieces fall into different banks);
+//   softmax  the running maximum and sum of a row live in its warp; the chunk's weights and
+//            the row's correction factor go to shared memory;
+//   values   thread (row group, four columns of the head) adds the chunk's weighted values to
+//            its rows' sums in registers.
+// The next chunk's keys and values are copied into the other half of shared memory meanwhile
+// (cp.async, 16 bytes at a time, page by page through the block table).
+// Same arguments, key ranges, splits and outputs as attn_generic_kernel; head sizes that are
+// multiples of 4 up to 256.
+constexpr int FR = 16;            // rows per tile
+constexpr int FK = 32;            // keys per chunk
+constexpr int FTHREADS = 256;
+constexpr int FMAX_RPT = 4;       // rows per thread in the values phase (head size <= 256)
+
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;                     // 0 source bytes: zeros arrive
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+__global__ void __launch_bounds__(FTHREADS)
+attn_rows16_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) float fsm[];
+    const int hd = p.head_dim, kld = hd + 4;
+    float* qs = fsm;                                   // [FR][hd], pre-multiplied by the scale
+    float* ks = qs + FR * hd;                          // [2][FK][hd + 4]
+    float* vs = ks + 2 * FK * kld;                     // [2][FK][hd]
+    float* pr = vs + 2 * FK * hd;                      // [FR][FK] weights of the chunk
+    float* corr = pr + FR * FK;                        // [FR] correction of the sums so far
+    float* lsum = corr + FR;                           // [FR] final sums
+    __shared__ long long key_base[3][FK];
+
+    const int kvh = blockIdx.x, tile = blockIdx.y, split = blockIdx.z;
+    const int group = p.heads / p.kv_heads;
+    const int item = p.tile_item[tile];
+    const int row0 = p.tile_row0[tile];
+    const int qstart = p.item_qstart[item], qlen = p.item_qlen[item], pos0 = p.item_pos0[item];
+    const int nrows = min(FR, qlen * group - row0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* q = (const float*)p.q;
+    const float* kp = (const float*)p.k_pages;
+    const float* vp = (const float*)p.v_pages;
+    const int* bt = p.block_tables + (size_t)item * p.bt_stride;
+
+    for (int e = tid; e < FR * hd; e += FTHREADS) {
+        const int r = e / hd, d = e - r * hd;
+        float v = 0.f;
+        if (r < nrows) {
+            const int row = row0 + r;
+            const int tok = qstart + row / group, h = kvh * group + row % group;
+            v = q[(size_t)tok * p.q_ld + h * hd + d] * p.scale;
+        }
+        qs[e] = v;
+    }
+
+    const int pos_first = pos0 + row0 / group;
+    const int pos_last = pos0 + (row0 + nrows - 1) / group;
+    int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int kend = pos_last + 1;
+    if (p.nsplit > 1) {
+        const int span = kend - kbegin;
+        int chunk = (span + p.nsplit - 1) / p.nsplit;
+        chunk = ((chunk + FK - 1) / FK) * FK;
+        const int b = kbegin + split * chunk;
+        kend = min(kend, b + chunk);
+        kbegin = b;
+    }
+    const int chunks = kend > kbegin ? (kend - kbegin + FK - 1) / FK : 0;
+
+    auto find_rows = [&](int c) {                      // where the keys of chunk c lie in the pages
+        if (tid < FK) {
+            const int kj = kbegin + c * FK + tid;
+            long long base = -1;
+            if (c < chunks && kj < kend) {
+                const int page = bt[kj / p.page_size];
+                if (page >= 0)
+                    base = (long long)page * p.page_stride + ((long long)kvh * p.page_size + kj % p.page_size) * hd;
+            }
+            key_base[c % 3][tid] = base;
+        }
+    };
+    auto fetch = [&](int c) {                          // chunk c's keys and values on their way
+        float* kd = ks + (c & 1) * FK * kld;
+        float* vd = vs + (c & 1) * FK * hd;
+        const int pieces = hd / 4;
+        for (int e = tid; e < FK * pieces; e += FTHREADS) {
+            const int j = e / pieces, d = (e - j * pieces) * 4;
+            const long long base = key_base[c % 3][j];
+            copy16(kd + j * kld + d, base >= 0 ? kp + base + d : kp, base >= 0);
+            copy16(vd + j * hd + d, base >= 0 ? vp + base + d : vp, base >= 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    // rows of this warp in the scores phase, rows and columns of this thread in the values phase
+    const int ra = warp, rb = warp + 8;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    const int pieces = hd / 4;
+    const int row_groups = FTHREADS / pieces;                       // 4 or more (head size <= 256)
+    const int cg = tid % pieces, rg = tid / pieces;
+    const bool has_values = rg < row_groups;
+    float4 acc[FMAX_RPT];
+#pragma unroll
+    for (int i = 0; i < FMAX_RPT; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    find_rows(0);
+    __syncthreads();                                   // qs and key_base[0] are in place
+    if (chunks > 0) fetch(0);
+    find_rows(1);
+    for (int c = 0; c < chunks; ++c) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                               // chunk c has landed; the last chunk's weights are used up
+        if (c + 1 < chunks) fetch(c + 1);
+        find_rows(c + 2);
+        const float* kc = ks + (c & 1) * FK * kld;
+        const float* vc = vs + (c & 1) * FK * hd;
+        const int kj = kbegin + c * FK + lane;
+        const bool key_ok = kj < kend && key_base[c % 3][lane] >= 0;
+
+        // ---- scores of rows ra and rb against key `lane`
+        float s_a = 0.f, s_b = 0.f;
+        const bool use_a = ra < nrows, use_b = rb < nrows;
+        if (use_a) {
+            const float* kr = kc + lane * kld;
+            const float* qa = qs + ra * hd;
+            const float* qb = qs + rb * hd;
+            for (int d = 0; d < hd; d += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                const float4 xa = *reinterpret_cast<const float4*>(qa + d);
+                s_a = fmaf(xa.x, kv.x, s_a); s_a = fmaf(xa.y, kv.y, s_a);
+                s_a = fmaf(xa.z, kv.z, s_a); s_a = fmaf(xa.w, kv.w, s_a);
+                if (use_b) {
+                    const float4 xb = *reinterpret_cast<const float4*>(qb + d);
+                    s_b = fmaf(xb.x, kv.x, s_b); s_b = fmaf(xb.y, kv.y, s_b);
+                    s_b = fmaf(xb.z, kv.z, s_b); s_b = fmaf(xb.w, kv.w, s_b);
+                }
+            }
+        }
+        // ---- running softmax of the two rows; weights and corrections to shared memory
+        auto update = [&](int r, bool used, float s, float& m, float& l) {
+            float pj = 0.f, factor = 1.f;
+            if (used) {
+                const int pos = pos0 + (row0 + r) / group;
+                const bool seen = key_ok && kj <= pos && (p.window <= 0 || kj > pos - p.window);
+                s = seen ? s : -INFINITY;
+                const float m_new = fmaxf(m, warp_max(s));
+                if (m_new != -INFINITY) {
+                    factor = expf(m - m_new);             // m = -inf gives 0
+                    pj = seen ? expf(s - m_new) : 0.f;
+                    l = l * factor + warp_sum(pj);
+                    m = m_new;
+                }
+            }
+            pr[r * FK + lane] = pj;
+            if (lane == 0) corr[r] = factor;
+        };
+        update(ra, use_a, s_a, m_a, l_a);
+        update(rb, use_b, s_b, m_b, l_b);
+        __syncthreads();
+        // ---- weighted values
+        if (has_values) {
+#pragma unroll
+            for (int i = 0; i < FMAX_RPT; ++i) {
+                const int r = rg + i * row_groups;
+                if (r < nrows) {
+                    const float f = corr[r];
+                    acc[i].x *= f; acc[i].y *= f; acc[i].z *= f; acc[i].w *= f;
+                }
+            }
+            for (int j = 0; j < FK; ++j) {
+                const float4 vv = *reinterpret_cast<const float4*>(vc + j * hd + cg * 4);
+#pragma unroll
+                for (int i = 0; i < FMAX_RPT; ++i) {
+                    const int r = rg + i * row_groups;
+                    if (r < nrows) {
+                        const float w = pr[r * FK + j];
+                        acc[i].x = fmaf(w, vv.x, acc[i].x); acc[i].y = fmaf(w, vv.y, acc[i].y);
+                        acc[i].z = fmaf(w, vv.z, acc[i].z); acc[i].w = fmaf(w, vv.w, acc[i].w);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // ---- results: the sums of a row are with its warp, its weighted values with other threads
+    if (lane == 0) {
+        if (ra < nrows) {
+            lsum[ra] = l_a;
+            if (p.nsplit > 1) {
+                const int row = row0 + ra;
+                const size_t idx = ((size_t)split * p.tokens + qstart + row / group) * p.heads + kvh * group + row % group;
+                p.part_ml[idx * 2] = m_a; p.part_ml[idx * 2 + 1] = l_a;
+            }
+        }
+        if (rb < nrows) {
+            lsum[rb] = l_b;
+            if (p.nsplit > 1) {
+                const int row = row0 + rb;
+                const size_t idx = ((size_t)split * p.tokens + qstart + row / group) * p.heads + kvh * group + row % group;
+                p.part_ml[idx * 2] = m_b; p.part_ml[idx * 2 + 1] = l_b;
+            }
+        }
+    }
+    __syncthreads();
+    if (has_values) {
+#pragma unroll
+        for (int i = 0; i < FMAX_RPT; ++i) {
+            const int r = rg + i * row_groups;
+            if (r >= nrows) continue;
+            const int row = row0 + r;
+            const int tok = qstart + row / group, h = kvh * group + row % group;
+            if (p.nsplit == 1) {
+                const float l = lsum[r];
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                float* o = (float*)p.out + (size_t)tok * p.out_ld + h * hd + cg * 4;
+                o[0] = acc[i].x * inv; o[1] = acc[i].y * inv; o[2] = acc[i].z * inv; o[3] = acc[i].w * inv;
+            } else {
+                const size_t idx = ((size_t)split * p.tokens + tok) * p.heads + h;
+                float* o = p.part_o + idx * hd + cg * 4;
+                o[0] = acc[i].x; o[1] = acc[i].y; o[2] = acc[i].z; o[3] = acc[i].w;
+            }
+        }
+    }
+}
+
 }  // namespace fsie
 
 using namespace fsie;
@@ -197,22 +429,30 @@ using namespace fsie;
 extern "C" {
 
 int fsie_attn_generic_rows() { return ROWS; }
+int fsie_attn_rows16_rows() { return FR; }
 
 // Launch over `tiles` row tiles.  With nsplit > 1 the caller provides part_o
 // [nsplit, tokens, heads, head_dim] and part_ml [nsplit, tokens, heads, 2] in float.
-int fsie_attn_generic(const void* q, int q_ld, const void* k_pages, const void* v_pages,
-                      long long page_stride, int page_size, const int* block_tables, int bt_stride,
-                      const int* tile_item, const int* tile_row0, int tiles,
-                      const int* item_qstart, const int* item_qlen, const int* item_pos0,
-                      void* out, int out_ld, float* part_o, float* part_ml, int tokens, int heads,
-                      int kv_heads, int head_dim, int window, int nsplit, float scale, int dtype,
-                      cudaStream_t stream) {
-    if (tiles <= 0 || tokens <= 0) return 0;
+// rows16: the tiles hold up to 16 rows and take attn_rows16_kernel (float storage, head sizes in
+// steps of 4); else up to 32 rows and attn_generic_kernel.  merge: the partial results of all
+// tokens are merged after this launch (a step whose tiles go out in several launches asks for
+// it with the last one only).
+int fsie_attn_tiles(const void* q, int q_ld, const void* k_pages, const void* v_pages,
+                    long long page_stride, int page_size, const int* block_tables, int bt_stride,
+                    const int* tile_item, const int* tile_row0, int tiles,
+                    const int* item_qstart, const int* item_qlen, const int* item_pos0,
+                    void* out, int out_ld, float* part_o, float* part_ml, int tokens, int heads,
+                    int kv_heads, int head_dim, int window, int nsplit, float scale, int dtype,
+                    int rows16, int merge, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
     if (tiles > 65535) return ERR_UNSUPPORTED;          // tiles are the grid's y dimension
     if (head_dim <= 0 || head_dim > 32 * MAX_DPL || kv_heads <= 0 || heads % kv_heads != 0 ||
-        nsplit < 1 || page_size <= 0)
+        nsplit < 1 || page_size <= 0 || tiles < 0)
         return ERR_BAD_ARGUMENT;
     if (nsplit > 1 && (!part_o || !part_ml)) return ERR_BAD_ARGUMENT;
+    if (rows16 && (dtype != DTYPE_F32 || head_dim % 4 != 0 || page_stride % 4 != 0 ||
+                   ((((size_t)k_pages) | ((size_t)v_pages)) & 15) != 0))
+        return ERR_UNSUPPORTED;
     AttnParams p;
     p.q = q; p.q_ld = q_ld; p.k_pages = k_pages; p.v_pages = v_pages;
     p.page_stride = page_stride; p.page_size = page_size;
@@ -222,18 +462,28 @@ int fsie_attn_generic(const void* q, int q_ld, const void* k_pages, const void* 
     p.out = out; p.out_ld = out_ld; p.part_o = part_o; p.part_ml = part_ml;
     p.tokens = tokens; p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
     p.window = window; p.nsplit = nsplit; p.scale = scale;
-    const size_t smem = sizeof(float) * ((size_t)ROWS * head_dim + (size_t)KT * (head_dim + 1) +
-                                         (size_t)KT * head_dim);
-    dim3 grid(kv_heads, tiles, nsplit);
-    if (dtype == DTYPE_F32) {
-        cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_generic_kernel<float><<<grid, WARPS * 32, smem, stream>>>(p);
-    } else {
-        cudaFuncSetAttribute(attn_generic_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_generic_kernel<bf16><<<grid, WARPS * 32, smem, stream>>>(p);
+    int rc = 0;
+    if (tiles > 0) {
+        dim3 grid(kv_heads, tiles, nsplit);
+        if (rows16) {
+            const size_t smem = sizeof(float) * ((size_t)FR * head_dim + 2 * (size_t)FK * (head_dim + 4) +
+                                                 2 * (size_t)FK * head_dim + (size_t)FR * FK + 2 * FR);
+            cudaFuncSetAttribute(attn_rows16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attn_rows16_kernel<<<grid, FTHREADS, smem, stream>>>(p);
+        } else {
+            const size_t smem = sizeof(float) * ((size_t)ROWS * head_dim + (size_t)KT * (head_dim + 1) +
+                                                 (size_t)KT * head_dim);
+            if (dtype == DTYPE_F32) {
+                cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                attn_generic_kernel<float><<<grid, WARPS * 32, smem, stream>>>(p);
+            } else {
+                cudaFuncSetAttribute(attn_generic_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                attn_generic_kernel<bf16><<<grid, WARPS * 32, smem, stream>>>(p);
+            }
+        }
+        rc = FSIE_LAUNCH_CHECK();
     }
-    int rc = FSIE_LAUNCH_CHECK();
-    if (rc != 0 || nsplit == 1) return rc;
+    if (rc != 0 || nsplit == 1 || !merge) return rc;
     dim3 cgrid(tokens, heads);
     const int threads = head_dim >= 128 ? 128 : (head_dim >= 64 ? 64 : 32);
     if (dtype == DTYPE_F32)
@@ -241,6 +491,21 @@ int fsie_attn_generic(const void* q, int q_ld, const void* k_pages, const void* 
     else
         attn_combine_kernel<bf16><<<cgrid, threads, 0, stream>>>(part_o, part_ml, (bf16*)out, out_ld, tokens, heads, head_dim, nsplit);
     return FSIE_LAUNCH_CHECK();
+}
+
+// The launch as callers outside the engine know it: tiles of up to 32 rows, merged at once.
+int fsie_attn_generic(const void* q, int q_ld, const void* k_pages, const void* v_pages,
+                      long long page_stride, int page_size, const int* block_tables, int bt_stride,
+                      const int* tile_item, const int* tile_row0, int tiles,
+                      const int* item_qstart, const int* item_qlen, const int* item_pos0,
+                      void* out, int out_ld, float* part_o, float* part_ml, int tokens, int heads,
+                      int kv_heads, int head_dim, int window, int nsplit, float scale, int dtype,
+                      cudaStream_t stream) {
+    if (tiles <= 0 || tokens <= 0) return 0;
+    return fsie_attn_tiles(q, q_ld, k_pages, v_pages, page_stride, page_size, block_tables, bt_stride,
+                           tile_item, tile_row0, tiles, item_qstart, item_qlen, item_pos0, out, out_ld,
+                           part_o, part_ml, tokens, heads, kv_heads, head_dim, window, nsplit, scale,
+                           dtype, 0, 1, stream);
 }
 
 }  // extern "C"

@@ -89,7 +89,12 @@ def core():
         lib.fsie_gemm_f32_rows_limit.restype = i
         lib.fsie_attn_generic.argtypes = [p, i, p, p, ll, i, p, i, p, p, i, p, p, p, p, i, p, p,
                                           i, i, i, i, i, i, f, i, p]
+        lib.fsie_attn_tiles.argtypes = [p, i, p, p, ll, i, p, i, p, p, i, p, p, p, p, i, p, p,
+                                        i, i, i, i, i, i, f, i, i, i, p]
+        lib.fsie_attn_tiles.restype = i
         lib.fsie_attn_generic_rows.argtypes = []
+        lib.fsie_attn_rows16_rows.argtypes = []
+        lib.fsie_attn_rows16_rows.restype = i
         lib.fsie_argmax.argtypes = [p, i, i, p, p]
         lib.fsie_argmax_staged.argtypes = [p, i, i, p, p, i, p]
         lib.fsie_sample.argtypes = [p, i, i, p, p, p, p, p, p]
@@ -256,7 +261,12 @@ def attention_generic(q: torch.Tensor, q_ld: int, k_pages: torch.Tensor, v_pages
                       out: torch.Tensor, tokens: int, heads: int, kv_heads: int, head_dim: int,
                       window: int, scale: float, nsplit: int = 1,
                       part_o: Optional[torch.Tensor] = None,
-                      part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      part_ml: Optional[torch.Tensor] = None, rows16: bool = False,
+                      merge: bool = True) -> torch.Tensor:
+    """The 32-bit attention over tiles of up to 32 query rows (any storage, any head size up to
+    256), or with `rows16` over tiles of up to 16 rows by the kernel for few rows (float storage,
+    head sizes in steps of 4).  `merge=False` leaves the partial results of split key ranges
+    unmerged: a step whose tiles go out in several launches merges with the last."""
     for name, t in (("block_tables", block_tables), ("tile_item", tile_item),
                     ("tile_row0", tile_row0), ("item_qstart", item_qstart),
                     ("item_qlen", item_qlen), ("item_pos0", item_pos0)):
@@ -271,14 +281,24 @@ def attention_generic(q: torch.Tensor, q_ld: int, k_pages: torch.Tensor, v_pages
         if part_o.numel() < nsplit * tokens * heads * head_dim or \
                 part_ml.numel() < nsplit * tokens * heads * 2:
             raise KernelError("attention: split scratch is too small")
-    _check(core().fsie_attn_generic(_ptr(q), q_ld, _ptr(k_pages), _ptr(v_pages), page_stride,
-                                    page_size, _ptr(block_tables), block_tables.stride(0),
-                                    _ptr(tile_item), _ptr(tile_row0), num_tiles,
-                                    _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0),
-                                    _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), tokens,
-                                    heads, kv_heads, head_dim, window, nsplit, float(scale),
-                                    _tag(q.dtype), _stream()), "attention_generic")
+    _check(core().fsie_attn_tiles(_ptr(q), q_ld, _ptr(k_pages), _ptr(v_pages), page_stride,
+                                  page_size, _ptr(block_tables), block_tables.stride(0),
+                                  _ptr(tile_item), _ptr(tile_row0), num_tiles,
+                                  _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0),
+                                  _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), tokens,
+                                  heads, kv_heads, head_dim, window, nsplit, float(scale),
+                                  _tag(q.dtype), int(rows16), int(merge), _stream()),
+           "attention_generic")
     return out
+
+
+def attention_rows16_fits(dtype: torch.dtype, head_dim: int, page_stride: int) -> bool:
+    """Whether the 32-bit attention kernel for tiles of up to 16 rows takes this cache."""
+    return dtype is torch.float32 and head_dim % 4 == 0 and head_dim <= 256 and page_stride % 4 == 0
+
+
+def attention_rows16_rows() -> int:
+    return int(core().fsie_attn_rows16_rows())
 
 
 _attn_mma = {}

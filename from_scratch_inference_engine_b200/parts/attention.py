@@ -182,13 +182,25 @@ class GqaAttention(Mixer):
                                   self.window, self.scale, nsplit, part_o, part_ml,
                                   class_tokens, count)
             return
-        tiles = ctx.attention_tiles(group_size, ops.attention_rows_per_tile())
-        nsplit = splits(tiles.count * self.num_kv_heads, ctx.max_context)
+        # 32-bit arithmetic on CUDA cores: requests of up to 16 query rows (decoded tokens, short
+        # portions) take the kernel in which every warp works on such a tile, the others the
+        # kernel for tiles of 32 rows; one choice of key splits and one merge for both
+        if ops.attention_rows16_fits(qkv.dtype, self.head_dim, cache.page_stride):
+            classes = ctx.attention_row_classes(group_size, (ops.attention_rows16_rows(),
+                                                             ops.attention_rows_per_tile()))
+            launches = [(row_class == 0, tiles) for row_class, tiles, _, _, _ in classes]
+        else:
+            launches = [(False, ctx.attention_tiles(group_size, ops.attention_rows_per_tile()))]
+        blocks = sum(tiles.count for _, tiles in launches) * self.num_kv_heads
+        decoding = all(rows16 for rows16, _ in launches)
+        nsplit = splits(blocks, ctx.max_context, even_work=decoding, blocks_per_sm=2)
         part_o = part_ml = None
         if nsplit > 1:
             part_o = ctx.scratch("attention.part_o", nsplit * tokens * self.q_width)
             part_ml = ctx.scratch("attention.part_ml", nsplit * tokens * self.num_heads * 2)
-        ops.attention_generic(qkv, qkv.stride(0), *common, tiles.item, tiles.row0, tiles.count,
-                              ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out, tokens,
-                              self.num_heads, self.num_kv_heads, self.head_dim, self.window,
-                              self.scale, nsplit, part_o, part_ml)
+        for index, (rows16, tiles) in enumerate(launches):
+            ops.attention_generic(qkv, qkv.stride(0), *common, tiles.item, tiles.row0, tiles.count,
+                                  ctx.item_qstart, ctx.item_qlen, ctx.item_pos0, out, tokens,
+                                  self.num_heads, self.num_kv_heads, self.head_dim, self.window,
+                                  self.scale, nsplit, part_o, part_ml, rows16=rows16,
+                                  merge=index == len(launches) - 1)

@@ -226,14 +226,21 @@ class PagedCase:
         self.q = torch.cat(qs)
         self.want = torch.cat(self.want)
 
-    def run(self, ops, nsplit=1):
+    def run(self, ops, nsplit=1, rows16=False):
+        """The 32-bit kernels; with rows16 the requests of up to 16 query rows go to the kernel
+        for few rows first (unmerged) and the others follow, as the engine launches them."""
         group = self.heads // self.kv_heads
         rows = ops.attention_rows_per_tile()
         tile_item, tile_row0, qstart = [], [], []
+        few_item, few_row0 = [], []
         at = 0
         for i, (past, new) in enumerate(self.items):
             qstart.append(at)
             at += new
+            if rows16 and new * group <= ops.attention_rows16_rows():
+                few_item.append(i)
+                few_row0.append(0)
+                continue
             for r0 in range(0, new * group, rows):
                 tile_item.append(i)
                 tile_row0.append(r0)
@@ -247,6 +254,13 @@ class PagedCase:
             part_o = torch.full((nsplit * tokens * self.heads * self.hd,), float("nan"),
                                 device="cuda")
             part_ml = torch.full((nsplit * tokens * self.heads * 2,), float("nan"), device="cuda")
+        if few_item:
+            ops.attention_generic(q, q.stride(0), pages[:, 0, 0], pages[:, 0, 1], pages.stride(0),
+                                  self.page_size, dev(self.tables), i32(few_item), i32(few_row0),
+                                  len(few_item), i32(qstart), i32([n for _, n in self.items]),
+                                  i32([p for p, _ in self.items]), out, tokens, self.heads,
+                                  self.kv_heads, self.hd, self.window, 1.0 / math.sqrt(self.hd),
+                                  nsplit, part_o, part_ml, rows16=True, merge=False)
         ops.attention_generic(q, q.stride(0), pages[:, 0, 0], pages[:, 0, 1], pages.stride(0),
                               self.page_size, dev(self.tables), i32(tile_item), i32(tile_row0),
                               len(tile_item), i32(qstart), i32([n for _, n in self.items]),
@@ -337,11 +351,15 @@ def run_kernel(case, ops, kernel, nsplit=1):
         if case.hd not in ops.ATTENTION_TC_HEAD_DIMS or case.page_size not in ops.ATTENTION_TC_PAGES:
             pytest.skip("the tcgen05 kernel takes head sizes 64 and 128 and pages of 8..128")
         return case.run_mma(ops, nsplit, tc=True)
+    if kernel == "rows16":
+        if case.hd % 4:
+            pytest.skip("the kernel for few rows takes head sizes in steps of 4")
+        return case.run(ops, nsplit, rows16=True)
     return case.run_mma(ops, nsplit) if kernel == "mma" else case.run(ops, nsplit)
 
 
-KERNELS = [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16),
-           ("tc", torch.bfloat16)]
+KERNELS = [("generic", torch.float32), ("generic", torch.bfloat16), ("rows16", torch.float32),
+           ("mma", torch.bfloat16), ("tc", torch.bfloat16)]
 
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
