@@ -204,12 +204,12 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o,
 //            its rows' sums in registers.
 // The next chunk's keys and values are copied into the other half of shared memory meanwhile
 // (cp.async, 16 bytes at a time, page by page through the block table).
-// Same arguments, key ranges, splits and outputs as attn_generic_kernel; head sizes that are
-// multiples of 4 up to 256.
+// Same arguments, key ranges, splits and outputs as attn_generic_kernel.  Compiled per head
+// size (32, 64, 96, 128, 256), so that every loop over the head unrolls with constant offsets;
+// other head sizes take the kernel above.
 constexpr int FR = 16;            // rows per tile
 constexpr int FK = 32;            // keys per chunk
 constexpr int FTHREADS = 256;
-constexpr int FMAX_RPT = 4;       // rows per thread in the values phase (head size <= 256)
 
 __device__ __forceinline__ void copy16(void* dst, const void* src, bool valid) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -217,10 +217,14 @@ __device__ __forceinline__ void copy16(void* dst, const void* src, bool valid) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
+template <int HD>
 __global__ void __launch_bounds__(FTHREADS)
 attn_rows16_kernel(const AttnParams p) {
     extern __shared__ __align__(16) float fsm[];
-    const int hd = p.head_dim, kld = hd + 4;
+    constexpr int hd = HD, kld = HD + 4;
+    constexpr int pieces = HD / 4;                                  // 16-byte pieces of a row
+    constexpr int row_groups = FTHREADS / pieces;                   // threads side by side along the rows
+    constexpr int RPT = (FR + row_groups - 1) / row_groups;         // rows per thread in the values phase
     float* qs = fsm;                                   // [FR][hd], pre-multiplied by the scale
     float* ks = qs + FR * hd;                          // [2][FK][hd + 4]
     float* vs = ks + 2 * FK * kld;                     // [2][FK][hd]
@@ -281,7 +285,7 @@ attn_rows16_kernel(const AttnParams p) {
     auto fetch = [&](int c) {                          // chunk c's keys and values on their way
         float* kd = ks + (c & 1) * FK * kld;
         float* vd = vs + (c & 1) * FK * hd;
-        const int pieces = hd / 4;
+#pragma unroll
         for (int e = tid; e < FK * pieces; e += FTHREADS) {
             const int j = e / pieces, d = (e - j * pieces) * 4;
             const long long base = key_base[c % 3][j];
@@ -294,13 +298,15 @@ attn_rows16_kernel(const AttnParams p) {
     // rows of this warp in the scores phase, rows and columns of this thread in the values phase
     const int ra = warp, rb = warp + 8;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-    const int pieces = hd / 4;
-    const int row_groups = FTHREADS / pieces;                       // 4 or more (head size <= 256)
     const int cg = tid % pieces, rg = tid / pieces;
     const bool has_values = rg < row_groups;
-    float4 acc[FMAX_RPT];
+    float4 acc[RPT];
+    bool row_on[RPT];                                               // which of this thread's rows exist
 #pragma unroll
-    for (int i = 0; i < FMAX_RPT; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < RPT; ++i) {
+        acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        row_on[i] = has_values && rg + i * row_groups < nrows;
+    }
 
     find_rows(0);
     __syncthreads();                                   // qs and key_base[0] are in place
@@ -323,17 +329,23 @@ attn_rows16_kernel(const AttnParams p) {
             const float* kr = kc + lane * kld;
             const float* qa = qs + ra * hd;
             const float* qb = qs + rb * hd;
+            // four partial sums per row, added at the end: the chain of dependent additions is
+            // a quarter as long
+            float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
             for (int d = 0; d < hd; d += 4) {
                 const float4 kv = *reinterpret_cast<const float4*>(kr + d);
                 const float4 xa = *reinterpret_cast<const float4*>(qa + d);
-                s_a = fmaf(xa.x, kv.x, s_a); s_a = fmaf(xa.y, kv.y, s_a);
-                s_a = fmaf(xa.z, kv.z, s_a); s_a = fmaf(xa.w, kv.w, s_a);
+                pa[0] = fmaf(xa.x, kv.x, pa[0]); pa[1] = fmaf(xa.y, kv.y, pa[1]);
+                pa[2] = fmaf(xa.z, kv.z, pa[2]); pa[3] = fmaf(xa.w, kv.w, pa[3]);
                 if (use_b) {
                     const float4 xb = *reinterpret_cast<const float4*>(qb + d);
-                    s_b = fmaf(xb.x, kv.x, s_b); s_b = fmaf(xb.y, kv.y, s_b);
-                    s_b = fmaf(xb.z, kv.z, s_b); s_b = fmaf(xb.w, kv.w, s_b);
+                    pb[0] = fmaf(xb.x, kv.x, pb[0]); pb[1] = fmaf(xb.y, kv.y, pb[1]);
+                    pb[2] = fmaf(xb.z, kv.z, pb[2]); pb[3] = fmaf(xb.w, kv.w, pb[3]);
                 }
             }
+            s_a = (pa[0] + pa[1]) + (pa[2] + pa[3]);
+            s_b = (pb[0] + pb[1]) + (pb[2] + pb[3]);
         }
         // ---- running softmax of the two rows; weights and corrections to shared memory
         auto update = [&](int r, bool used, float s, float& m, float& l) {
@@ -357,22 +369,22 @@ attn_rows16_kernel(const AttnParams p) {
         update(rb, use_b, s_b, m_b, l_b);
         __syncthreads();
         // ---- weighted values
-        if (has_values) {
+        if (row_on[0]) {                               // a thread's first row exists if any of its rows does
 #pragma unroll
-            for (int i = 0; i < FMAX_RPT; ++i) {
-                const int r = rg + i * row_groups;
-                if (r < nrows) {
-                    const float f = corr[r];
+            for (int i = 0; i < RPT; ++i) {
+                if (row_on[i]) {
+                    const float f = corr[rg + i * row_groups];
                     acc[i].x *= f; acc[i].y *= f; acc[i].z *= f; acc[i].w *= f;
                 }
             }
+            const float* vcol = vc + cg * 4;
+#pragma unroll 8
             for (int j = 0; j < FK; ++j) {
-                const float4 vv = *reinterpret_cast<const float4*>(vc + j * hd + cg * 4);
+                const float4 vv = *reinterpret_cast<const float4*>(vcol + j * hd);
 #pragma unroll
-                for (int i = 0; i < FMAX_RPT; ++i) {
-                    const int r = rg + i * row_groups;
-                    if (r < nrows) {
-                        const float w = pr[r * FK + j];
+                for (int i = 0; i < RPT; ++i) {
+                    if (row_on[i]) {
+                        const float w = pr[(rg + i * row_groups) * FK + j];
                         acc[i].x = fmaf(w, vv.x, acc[i].x); acc[i].y = fmaf(w, vv.y, acc[i].y);
                         acc[i].z = fmaf(w, vv.z, acc[i].z); acc[i].w = fmaf(w, vv.w, acc[i].w);
                     }
@@ -403,9 +415,9 @@ attn_rows16_kernel(const AttnParams p) {
     __syncthreads();
     if (has_values) {
 #pragma unroll
-        for (int i = 0; i < FMAX_RPT; ++i) {
+        for (int i = 0; i < RPT; ++i) {
             const int r = rg + i * row_groups;
-            if (r >= nrows) continue;
+            if (!row_on[i]) continue;
             const int row = row0 + r;
             const int tok = qstart + row / group, h = kvh * group + row % group;
             if (p.nsplit == 1) {
@@ -430,6 +442,10 @@ extern "C" {
 
 int fsie_attn_generic_rows() { return ROWS; }
 int fsie_attn_rows16_rows() { return FR; }
+// head sizes the kernel for tiles of up to 16 rows is compiled for
+int fsie_attn_rows16_takes(int head_dim) {
+    return head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128 || head_dim == 256;
+}
 
 // Launch over `tiles` row tiles.  With nsplit > 1 the caller provides part_o
 // [nsplit, tokens, heads, head_dim] and part_ml [nsplit, tokens, heads, 2] in float.
@@ -450,7 +466,7 @@ int fsie_attn_tiles(const void* q, int q_ld, const void* k_pages, const void* v_
         nsplit < 1 || page_size <= 0 || tiles < 0)
         return ERR_BAD_ARGUMENT;
     if (nsplit > 1 && (!part_o || !part_ml)) return ERR_BAD_ARGUMENT;
-    if (rows16 && (dtype != DTYPE_F32 || head_dim % 4 != 0 || page_stride % 4 != 0 ||
+    if (rows16 && (dtype != DTYPE_F32 || !fsie_attn_rows16_takes(head_dim) || page_stride % 4 != 0 ||
                    ((((size_t)k_pages) | ((size_t)v_pages)) & 15) != 0))
         return ERR_UNSUPPORTED;
     AttnParams p;
@@ -468,8 +484,16 @@ int fsie_attn_tiles(const void* q, int q_ld, const void* k_pages, const void* v_
         if (rows16) {
             const size_t smem = sizeof(float) * ((size_t)FR * head_dim + 2 * (size_t)FK * (head_dim + 4) +
                                                  2 * (size_t)FK * head_dim + (size_t)FR * FK + 2 * FR);
-            cudaFuncSetAttribute(attn_rows16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attn_rows16_kernel<<<grid, FTHREADS, smem, stream>>>(p);
+#define FSIE_ROWS16(HDV)                                                                                        \
+    case HDV:                                                                                                   \
+        cudaFuncSetAttribute(attn_rows16_kernel<HDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        attn_rows16_kernel<HDV><<<grid, FTHREADS, smem, stream>>>(p);                                           \
+        break;
+            switch (head_dim) {
+                FSIE_ROWS16(32) FSIE_ROWS16(64) FSIE_ROWS16(96) FSIE_ROWS16(128) FSIE_ROWS16(256)
+                default: return ERR_UNSUPPORTED;
+            }
+#undef FSIE_ROWS16
         } else {
             const size_t smem = sizeof(float) * ((size_t)ROWS * head_dim + (size_t)KT * (head_dim + 1) +
                                                  (size_t)KT * head_dim);

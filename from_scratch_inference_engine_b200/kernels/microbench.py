@@ -104,7 +104,8 @@ def run_attention(args, timer, decode: bool):
         if args.variant == "tc" and row_class == 2:
             per_tile = ops.ATTENTION_TC_ROWS
     else:
-        row_class, per_tile = -1, ops.attention_rows_per_tile()
+        rows16 = args.variant == "rows16" and rows <= ops.attention_rows16_rows()
+        row_class, per_tile = -1, ops.attention_rows16_rows() if rows16 else ops.attention_rows_per_tile()
     tile_item, tile_row0 = [], []
     for i in range(args.batch):
         for r0 in range(0, rows, per_tile):
@@ -148,7 +149,7 @@ def run_attention(args, timer, decode: bool):
             ops.attention_generic(q, q.stride(0), pages[:, 0, 0], pages[:, 0, 1], pages.stride(0),
                                   page, tables, tile_item, tile_row0, tile_item.numel(), qstart,
                                   qlen, pos0, out, tokens, heads, kv_heads, hd, 0, scale, nsplit,
-                                  part_o, part_ml)
+                                  part_o, part_ml, rows16=rows16)
     ms = timer(launch)
     extra = {}
     elem = 2 if dtype is torch.bfloat16 else 4
@@ -161,7 +162,7 @@ def run_attention(args, timer, decode: bool):
         extra["error"] = int(error.item())
     extra.update({"nsplit": nsplit, "tiles": tile_item.numel(),
                   "variant": ("tc" if use_tc else "tc_decode" if use_tcd else "mma")
-                  if row_class >= 0 else "generic"})
+                  if row_class >= 0 else ("rows16" if rows16 else "generic")})
     return ms, io_bytes, flops, extra
 
 
@@ -284,8 +285,9 @@ def main(argv=None) -> int:
     parser.add_argument("--n", type=int, default=37888)
     parser.add_argument("--k", type=int, default=3584)
     parser.add_argument("--nsplit", type=int, default=0, help="0 = the engine's choice")
-    parser.add_argument("--variant", default="mma", choices=["mma", "tc"],
-                        help="bfloat16 attention: mma.sync with cp.async loads, or tcgen05")
+    parser.add_argument("--variant", default="mma", choices=["mma", "tc", "rows16"],
+                        help="bfloat16 attention: mma.sync with cp.async loads, or tcgen05; float32 "
+                             "attention: rows16 takes the kernel for tiles of up to 16 rows")
     parser.add_argument("--f32-kind", default="auto", choices=["auto", "rows", "tiles", "plain"],
                         help="gemm_f32: which of the float32 kernels (frac_ffma is of the nominal "
                              "74.4 TFLOP/s: 148 SMs x 128 lanes x 2 x 1.965 GHz)")

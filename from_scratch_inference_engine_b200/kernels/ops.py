@@ -95,6 +95,8 @@ def core():
         lib.fsie_attn_generic_rows.argtypes = []
         lib.fsie_attn_rows16_rows.argtypes = []
         lib.fsie_attn_rows16_rows.restype = i
+        lib.fsie_attn_rows16_takes.argtypes = [i]
+        lib.fsie_attn_rows16_takes.restype = i
         lib.fsie_argmax.argtypes = [p, i, i, p, p]
         lib.fsie_argmax_staged.argtypes = [p, i, i, p, p, i, p]
         lib.fsie_sample.argtypes = [p, i, i, p, p, p, p, p, p]
@@ -294,7 +296,8 @@ def attention_generic(q: torch.Tensor, q_ld: int, k_pages: torch.Tensor, v_pages
 
 def attention_rows16_fits(dtype: torch.dtype, head_dim: int, page_stride: int) -> bool:
     """Whether the 32-bit attention kernel for tiles of up to 16 rows takes this cache."""
-    return dtype is torch.float32 and head_dim % 4 == 0 and head_dim <= 256 and page_stride % 4 == 0
+    return (dtype is torch.float32 and page_stride % 4 == 0
+            and bool(core().fsie_attn_rows16_takes(int(head_dim))))
 
 
 def attention_rows16_rows() -> int:

@@ -352,8 +352,8 @@ def run_kernel(case, ops, kernel, nsplit=1):
             pytest.skip("the tcgen05 kernel takes head sizes 64 and 128 and pages of 8..128")
         return case.run_mma(ops, nsplit, tc=True)
     if kernel == "rows16":
-        if case.hd % 4:
-            pytest.skip("the kernel for few rows takes head sizes in steps of 4")
+        if not ops.attention_rows16_fits(torch.float32, case.hd, case.hd):
+            pytest.skip("the kernel for few rows is compiled for head sizes 32, 64, 96, 128 and 256")
         return case.run(ops, nsplit, rows16=True)
     return case.run_mma(ops, nsplit) if kernel == "mma" else case.run(ops, nsplit)
 
