@@ -26,6 +26,7 @@ from __future__ import annotations
 
 import argparse
 import hashlib
+import os
 import shutil
 import subprocess
 import sys
@@ -74,8 +75,12 @@ def sources_digest(files) -> str:
 
 def build(checkout: Path | None = None, verbose: bool = True) -> Path:
     """Returns the path of the built binary (built only when sources changed)."""
-    if checkout is None and Path("/root/reference/src/cuda/model.cu").exists():
-        checkout = Path("/root/reference")
+    if checkout is None:
+        # a checkout named `reference` beside this repository, or the one FSIE_REFERENCE names
+        for candidate in (os.environ.get("FSIE_REFERENCE"), ROOT.parent / "reference"):
+            if candidate and (Path(candidate) / "src/cuda/model.cu").exists():
+                checkout = Path(candidate)
+                break
     if checkout is not None and (checkout / "src/cuda/model.cu").exists():
         REF_COPY.mkdir(parents=True, exist_ok=True)
         copy_reference(checkout)
