@@ -5,7 +5,9 @@
 namespace fsie {
 
 // Merge the key splits of one (token, head); same arithmetic as attention_generic.cu.  The
-// weight e^(m_z - M) of split z is computed once by lane z (nsplit <= 32) and broadcast.
+// weights e^(m_z - M) of splits z and z + 32 are computed once by lane z (nsplit <= 64) and
+// broadcast.
+constexpr int MAX_KEY_SPLITS = 64;
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                         bf16* __restrict__ out, int out_ld, int tokens, int heads,
                                         int nsplit, const int* __restrict__ token_list) {
@@ -15,14 +17,19 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     const int lane = threadIdx.x & 31;
     const size_t stride = (size_t)tokens * heads;              // (token, head) slots per split
     const size_t slot = (size_t)tok * heads + h;
-    float mz = -INFINITY, lz = 0.f;
+    float mz = -INFINITY, lz = 0.f, mz_hi = -INFINITY, lz_hi = 0.f;
     if (lane < nsplit) {
         mz = part_ml[(lane * stride + slot) * 2];
         lz = part_ml[(lane * stride + slot) * 2 + 1];
     }
-    const float mmax = warp_max(mz);
+    if (lane + 32 < nsplit) {
+        mz_hi = part_ml[((lane + 32) * stride + slot) * 2];
+        lz_hi = part_ml[((lane + 32) * stride + slot) * 2 + 1];
+    }
+    const float mmax = warp_max(fmaxf(mz, mz_hi));
     const float wz = mz == -INFINITY ? 0.f : __expf(mz - mmax);
-    const float denom = warp_sum(lz * wz);
+    const float wz_hi = mz_hi == -INFINITY ? 0.f : __expf(mz_hi - mmax);
+    const float denom = warp_sum(lz * wz + lz_hi * wz_hi);
     const float inv = denom > 0.f ? 1.0f / denom : 0.f;
     for (int d = threadIdx.x * 2; d < HD; d += blockDim.x * 2) {
         float a0 = 0.f, a1 = 0.f;
@@ -37,7 +44,9 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float w = __shfl_sync(0xffffffffu, wz, min(z0 + j, 31));
+                const int z = min(z0 + j, MAX_KEY_SPLITS - 1);
+                const float lo = __shfl_sync(0xffffffffu, wz, z & 31), hi = __shfl_sync(0xffffffffu, wz_hi, z & 31);
+                const float w = z < 32 ? lo : hi;
                 if (z0 + j < nsplit && w != 0.f) { a0 += v[j].x * w; a1 += v[j].y * w; }   // a split without keys may hold anything
             }
         }

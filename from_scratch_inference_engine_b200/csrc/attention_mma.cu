@@ -447,7 +447,7 @@ int fsie_attn_mma(int row_class, const void* q, int q_ld, const void* k_pages, c
     const int count = combine_tokens ? num_combine : tokens;
     if (count <= 0) return 0;
     dim3 cgrid(count, heads);
-    if (nsplit > 32) return ERR_BAD_ARGUMENT;
+    if (nsplit > MAX_KEY_SPLITS) return ERR_BAD_ARGUMENT;
     return launch_dependent(attn_combine_kernel, cgrid, dim3(HD >= 128 ? 64 : 32), 0, stream,
                             (const float*)part_o, (const float*)part_ml, (bf16*)out, out_ld, tokens, heads, nsplit,
                             combine_tokens);

@@ -938,7 +938,7 @@ int fsie_attn_tc(const void* pages_map, int entries, int entry, const void* q, i
     if (tiles <= 0 || tokens <= 0) return 0;
     if (head_dim != HD) return ERR_UNSUPPORTED;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return ERR_UNSUPPORTED;
-    if (kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 || nsplit > 32 || (q_ld % 8) != 0 ||
+    if (kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 || nsplit > MAX_KEY_SPLITS || (q_ld % 8) != 0 ||
         (out_ld % 8) != 0 || entries <= 0 || entry < 0 || entry >= entries || !error)
         return ERR_BAD_ARGUMENT;
     if (nsplit > 1 && (!part_o || !part_ml)) return ERR_BAD_ARGUMENT;
@@ -984,7 +984,7 @@ int fsie_attn_tc_decode(const void* pages_map, int entries, int entry, const voi
     if (tiles <= 0 || tokens <= 0) return 0;
     if (head_dim != HD || tiles > 65535) return ERR_UNSUPPORTED;     // tiles are the grid's y dimension
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return ERR_UNSUPPORTED;
-    if (kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 || nsplit > 32 || (q_ld % 8) != 0 ||
+    if (kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 || nsplit > MAX_KEY_SPLITS || (q_ld % 8) != 0 ||
         entries <= 0 || entry < 0 || entry >= entries || !error)
         return ERR_BAD_ARGUMENT;
     if (nsplit > 1 && (!part_o || !part_ml)) return ERR_BAD_ARGUMENT;

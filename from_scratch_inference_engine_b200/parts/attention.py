@@ -14,10 +14,13 @@ from ..weights.tensor_spec import TensorSpec
 from .base import LayerCache, Mixer, build_part, register_part
 
 
+MAX_KEY_SPLITS = 64        # what the kernels that merge partial results take
+
+
 def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
                      blocks_per_sm: int = 2, decode_slots: int = 3, decode_fixed: int = 270,
                      merge_cost: int = 350) -> int:
-    """Into how many key ranges to split each tile (at most 32, each at least 128 keys).
+    """Into how many key ranges to split each tile (at most 64, each at least 128 keys).
 
     Tiles of decoded tokens all have the same work, so the time is waves x (fixed cost of a
     block + keys per range); measured at batch 64 and context 4,096 the fixed cost of the
@@ -32,10 +35,10 @@ def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
         if blocks >= slots:
             return 1
         wanted = slots // blocks if blocks_per_sm == 1 else -(-slots // blocks)
-        return max(1, min(wanted, longest // 128, 32))
+        return max(1, min(wanted, longest // 128, MAX_KEY_SPLITS))
     slots = decode_slots * sms
     best, best_cost = 1, None
-    for n in range(1, max(1, min(32, longest // 128)) + 1):
+    for n in range(1, max(1, min(MAX_KEY_SPLITS, longest // 128)) + 1):
         # any split costs the launch that merges the partial results (`merge_cost`, in keys: 5 us
         # after the mma.sync kernel at batch 8, 17 us after the tcgen05 kernel with 200 requests)
         cost = -(-blocks * n // slots) * (decode_fixed + longest / n) + (merge_cost if n > 1 else 0)

@@ -378,13 +378,13 @@ def test_attention_long_context(ops, kernel, dtype):
     """Thousands of keys over hundreds of shuffled pages: a long prompt portion on top of a long
     history, a decoded token, and a whole prompt, with and without split key ranges."""
     case = PagedCase(dtype, 4, 2, 64, 16, items=[(3000, 300), (4100, 1), (0, 700)], seed=12)
-    for nsplit in (1, 7):
+    for nsplit in (1, 7, 64):            # 64: ranges of 128 keys (mma.sync kernel 64), more than 32 of them hold keys
         got = run_kernel(case, ops, kernel, nsplit)
         assert_rows_close(got, case.want, case, dtype)
 
 
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
-@pytest.mark.parametrize("nsplit", [2, 5, 32])
+@pytest.mark.parametrize("nsplit", [2, 5, 32, 37, 64])
 def test_attention_split_keys(ops, kernel, dtype, nsplit):
     case = PagedCase(dtype, 14, 2, 64, 16, items=[(700, 1), (0, 3), (301, 1), (33, 2), (400, 20)],
                      seed=5)

@@ -201,3 +201,41 @@ def test_replay_with_the_tcgen05_kernel_for_decoded_tokens(folders, family, monk
     assert calls
     if family == "tail":
         assert runner._graphs, "the decoded tokens did not go through a captured step"
+
+
+ODD = {
+    # nothing a multiple of anything: head size 20 (no tensor-core attention, the 32-bit kernel on
+    # bfloat16 storage), widths that are no multiples of 8 (no 16-byte rows for the own products)
+    "all odd": dict(hidden_size=100, num_attention_heads=5, num_key_value_heads=5, head_dim=20,
+                    intermediate_size=37, vocab_size=101, tie_word_embeddings=False),
+    # 33 heads in groups of 3, head size 16, a prime vocabulary, tied head
+    "many small heads": dict(hidden_size=264, num_attention_heads=33, num_key_value_heads=11,
+                             head_dim=16, intermediate_size=1000, vocab_size=4099,
+                             tie_word_embeddings=True),
+    # head size 112 (a multiple of 16 that is neither 64 nor 128), pages of 5 tokens
+    "head 112": dict(hidden_size=256, num_attention_heads=2, num_key_value_heads=2, head_dim=112,
+                     intermediate_size=520, vocab_size=777, tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page_size", [("all odd", 16), ("many small heads", 8), ("head 112", 5)])
+def test_replay_at_sizes_that_fit_no_tile(tmp_path, name, page_size, dtype):
+    """Sizes that the fast kernels do not take must fall to kernels that do, never to a wrong
+    result: mixed steps with a release and a second run, against the plain implementation.
+    (bfloat16 bound: 2.5 times what these three were seen at, 3.3e-2 at most.)"""
+    from from_scratch_inference_engine_b200.config import config_from_dict
+    from from_scratch_inference_engine_b200.weights import write_random_model
+    config = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2,
+                  rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=512, **ODD[name])
+    folder = write_random_model(tmp_path / "odd", config_from_dict(config), 3, 0.1, torch.bfloat16)
+    requests = {k: helpers.random_ids(config["vocab_size"], n, i)
+                for i, (k, n) in enumerate({"a": 150, "b": 40, "c": 97, "d": 3}.items())}
+    steps, names = helpers.trace_mixed_with_recompute(requests, 3)
+    need = helpers.live_tokens_needed(steps, round_to=page_size)
+    runner = build_runner(folder, dtype, need, page_size)
+    rows = helpers.run_trace_in_process(runner, steps)
+    worst, scale, bad = helpers.compare_rows(rows, names, folder, 1e-4 if dtype == "float32" else 8e-2,
+                                             f"{dtype} {name}")
+    assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
+    assert all(pool.num_free == pool.num_pages for pool in runner.cache.pools)

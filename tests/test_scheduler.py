@@ -408,7 +408,7 @@ def test_a_plan_that_would_preempt_is_given_up_while_tokens_are_pending():
 
 def test_key_splits_of_the_attention_launch():
     """How many key ranges a tile is cut into (host arithmetic of parts/attention.py): decoded
-    tokens fill the block slots without falling under 128 keys per range and never split past 32;
+    tokens fill the block slots without falling under 128 keys per range and never split past 64;
     prompt tiles split only into slots that would stay empty."""
     from from_scratch_inference_engine_b200.parts.attention import attention_splits
     sms = 148
@@ -417,7 +417,7 @@ def test_key_splits_of_the_attention_launch():
     assert 9 <= n <= 13 and 32 * n <= 3 * sms
     assert attention_splits(4, 4096, sms, True) >= 24           # batch 1
     assert attention_splits(4, 200, sms, True) == 1              # too short to split
-    assert attention_splits(4, 100000, sms, True) <= 32
+    assert 32 < attention_splits(4, 100000, sms, True) <= 64     # batch 1, a very long context
     assert attention_splits(2048, 4096, sms, True) <= 2          # many pairs: waves, not splits
     # decoded tokens, tcgen05 kernel (two blocks per SM, dearer blocks): one wave unsplit
     assert attention_splits(256, 4096, sms, True, decode_slots=2, decode_fixed=530) == 1
