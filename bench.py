@@ -307,6 +307,73 @@ def long_context_workload(args) -> int:
     return 0
 
 
+def timeline_workload(args) -> int:
+    """Where the time of one decode step goes while it runs as it does in serving (a replayed
+    graph whose kernels overlap their heads and tails): kernel start and end times of one
+    step as the profiling interface records them, per kernel kind what its end adds to
+    the latest end before it, and one layer in order.  Text, not a bench value."""
+    import numpy as np
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from from_scratch_inference_engine_b200 import LoadedModel, ModelRunner, StepEntry
+    from from_scratch_inference_engine_b200.config import config_from_dict
+    from from_scratch_inference_engine_b200.kernels import ops
+
+    shape = dict(SHAPE_7B)
+    shape["num_hidden_layers"] = args.layers or shape["num_hidden_layers"]
+    config = config_from_dict(shape)
+    batch, context, page = args.batch, args.context, 16
+    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16", max_positions=context + 64)
+    rng = np.random.default_rng(0)
+    runner = ModelRunner(model.model, model.runtime, page_size=page,
+                         num_pages=batch * (context // page + 2), max_requests=batch)
+    handles = []
+    for r in range(batch):
+        handle = runner.cache.open(r)
+        ids = rng.integers(0, config.vocab_size, size=context - 40).tolist()
+        for at in range(0, len(ids), 2048):
+            runner.step([StepEntry(handle, ids[at:at + 2048])])
+        handles.append(handle)
+    picks = torch.empty(batch, dtype=torch.int32, device=model.runtime.device)
+
+    def step():
+        logits = runner.step([StepEntry(h, [int(rng.integers(0, 1000))], [0]) for h in handles])
+        ops.argmax(logits, picks)
+    for _ in range(8):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(6):
+            step()
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                    key=lambda e: e.time_range.start)
+    first = [i for i, e in enumerate(events) if "embed" in e.name]
+    if len(first) < 5:
+        print("timeline: the steps were not found in the profile")
+        return 1
+    one = events[first[3]:first[4]]
+    origin = one[0].time_range.start
+    name = lambda e: e.name.replace("fsie::", "").replace("void ", "")[:44]
+    print(f"decode step, batch {batch}, context {context}, {shape['num_hidden_layers']} layers: "
+          f"{events[first[4]].time_range.start - origin:.1f} us, {len(one)} kernels")
+    print("   start     end  kernel (us from the step's first kernel; the second layer and what follows it)")
+    per_layer = max(1, (len(one) - 5) // shape["num_hidden_layers"])
+    for e in one[2 + per_layer:2 + 2 * per_layer + 2]:
+        print(f"{e.time_range.start - origin:8.1f} {e.time_range.end - origin:7.1f}  {name(e)}")
+    # every kernel waits for the one before it, so the step advances with the latest end so far:
+    # a kernel's share is what its end adds to that
+    cost, count, latest = {}, {}, origin
+    for e in one:
+        cost[name(e)] = cost.get(name(e), 0.0) + max(0.0, e.time_range.end - latest)
+        count[name(e)] = count.get(name(e), 0) + 1
+        latest = max(latest, e.time_range.end)
+    print("what each kernel's end adds to the latest end before it, summed over the step:")
+    for key, value in sorted(cost.items(), key=lambda kv: -kv[1]):
+        print(f"{value:9.1f} us  x{count[key]:3d}  {key}")
+    return 0
+
+
 def reference_arm(args) -> int:
     """The same metric and shape through the unmodified reference engine (built from its own
     sources by baseline/build_reference.py; its CUDA engine, CudaEngine::step, decodes the batch
@@ -379,10 +446,11 @@ def main() -> int:
                              "(0 = the engine's choice, 16; up to 64 for measuring that choice)")
     parser.add_argument("--fp32-steps", type=int, default=8,
                         help="decode steps timed on the float32 path after the bf16 run (0 = skip)")
-    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long"],
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline"],
                         help="decode: the default measurement; serving: continuous batching of 256 "
                              "requests at the 1.5B shape; long: the 14B shape, decode at batch 32 with "
-                             "8,192-token contexts and chunked prefill of an 8,192-token prompt")
+                             "8,192-token contexts and chunked prefill of an 8,192-token prompt; "
+                             "timeline: kernel start and end times inside one decode step (text)")
     parser.add_argument("--requests", type=int, default=256)
     parser.add_argument("--step-tokens", type=int, default=2048, help="serving: token budget of one step")
     parser.add_argument("--num-blocks", type=int, default=16384)
@@ -397,6 +465,8 @@ def main() -> int:
         return serving_workload(args)
     if args.workload == "long":
         return long_context_workload(args)
+    if args.workload == "timeline":
+        return timeline_workload(args)
 
     import numpy as np
     import torch
