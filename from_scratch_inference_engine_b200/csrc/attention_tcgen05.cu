@@ -190,6 +190,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
     const int pos_first = pos0 + row0 / group;
     const int pos_last = pos0 + (row0 + nrows - 1) / group;
     int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    // tiles hold whole pages, and keys before the window are masked: the range starts on a tile
+    // boundary before it is split, so that the splits' ranges stay disjoint
+    kbegin = kbegin / BN * BN;
     int kend = pos_last + 1;
     if (p.nsplit > 1) {
         const int span = kend - kbegin;
@@ -199,7 +202,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnParams p
         kend = min(kend, b + chunk);
         kbegin = b;
     }
-    kbegin = kbegin / BN * BN;          // tiles hold whole pages; keys before the window are masked
     const int ntiles = kend > kbegin ? (kend - kbegin + BN - 1) / BN : 0;
 
     // ---- set-up: barriers and tensor memory; then the producer starts fetching keys at once while
@@ -590,6 +592,9 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnP
     const int pos_first = pos0 + row0 / group;
     const int pos_last = pos0 + (row0 + nrows - 1) / group;
     int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    // tiles hold whole pages, and keys before the window are masked: the range starts on a tile
+    // boundary before it is split, so that the splits' ranges stay disjoint
+    kbegin = kbegin / KEYS * KEYS;
     int kend = pos_last + 1;
     if (p.nsplit > 1) {
         const int span = kend - kbegin;
@@ -599,7 +604,6 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap pages_map, const AttnP
         kend = min(kend, b + chunk);
         kbegin = b;
     }
-    kbegin = kbegin / KEYS * KEYS;      // tiles hold whole pages; keys before the window are masked
     const int ntiles = kend > kbegin ? (kend - kbegin + KEYS - 1) / KEYS : 0;
 
     if (tid == 0) {

@@ -425,6 +425,24 @@ def test_attention_window_edge(ops, kernel, dtype, window):
     assert_rows_close(got, case.want, case, dtype)
 
 
+@pytest.mark.parametrize("kernel,dtype", KERNELS)
+@pytest.mark.parametrize("window,nsplit", [(26, 2), (150, 2), (300, 3)])
+def test_attention_window_with_split_keys(ops, kernel, dtype, window, nsplit):
+    """A window that does not start on a tile of keys, cut into key ranges.  No key stands out
+    here: every key of the window counts alike, so a key that two ranges see (ranges that
+    overlap once they are rounded to tiles) or that none sees moves the result."""
+    case = PagedCase(dtype, 8, 2, 128, 16, items=[(700, 1), (450, 40), (0, 350), (131, 2)],
+                     window=window, seed=11)
+    assert_rows_close(run_kernel(case, ops, kernel, nsplit), case.want, case, dtype)
+
+
+@pytest.mark.parametrize("window,nsplit", [(150, 2), (300, 3), (1000, 4)])
+def test_attention_tc_decode_window_with_split_keys(ops, window, nsplit):
+    case = PagedCase(torch.bfloat16, 14, 2, 128, 16, items=[(700, 1), (1450, 1), (131, 2), (2000, 1)],
+                     window=window, seed=12)
+    assert_rows_close(case.run_mma(ops, nsplit, tc_decode=True), case.want, case, torch.bfloat16)
+
+
 @pytest.mark.parametrize("heads,kv_heads,page_size", [(28, 4, 16), (40, 8, 32), (16, 1, 8), (3, 3, 128),
                                                       (12, 2, 64)])
 def test_attention_tc_decode_sizes(ops, heads, kv_heads, page_size):

@@ -239,3 +239,31 @@ def test_replay_at_sizes_that_fit_no_tile(tmp_path, name, page_size, dtype):
                                              f"{dtype} {name}")
     assert not bad, f"{len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
     assert all(pool.num_free == pool.num_pages for pool in runner.cache.pools)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,page_size", [(26, 32), (61, 16), (200, 16)])
+def test_replay_window_that_starts_inside_a_tile_of_keys(tmp_path, window, page_size, dtype):
+    """Windowed layers at a head size the tcgen05 attention takes, prompts long enough that a
+    portion's key range is cut in two: the window of a token just behind a tile's edge reaches
+    back into the tile before it, which one range must see and no range twice.
+    (One layer: its bfloat16 results were seen at 1.4e-2 to 2.4e-2 of the row's largest logit, the
+    bound is 2.5 times that; a key counted twice moved them by 1.6e-1 to 2.2e-1.)"""
+    from from_scratch_inference_engine_b200.config import config_from_dict
+    from from_scratch_inference_engine_b200.weights import write_random_model
+    config = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=1,
+                  rope_theta=1e6, rms_norm_eps=1e-5, max_position_embeddings=1024, hidden_size=300,
+                  num_attention_heads=16, num_key_value_heads=4, head_dim=128, intermediate_size=356,
+                  vocab_size=1575, tie_word_embeddings=True, use_sliding_window=True,
+                  sliding_window=window, max_window_layers=0)
+    folder = write_random_model(tmp_path / "window", config_from_dict(config), 21, 0.1, torch.bfloat16)
+    requests = {k: helpers.random_ids(config["vocab_size"], n, i)
+                for i, (k, n) in enumerate({"a": 238, "b": 106, "c": 307, "d": 72}.items())}
+    for family, (steps, names) in (("tail", (helpers.trace_tail_by_one(requests, 20), requests)),
+                                   ("recompute", helpers.trace_mixed_with_recompute(requests, 21))):
+        need = helpers.live_tokens_needed(steps, round_to=page_size)
+        runner = build_runner(folder, dtype, need, page_size)
+        rows = helpers.run_trace_in_process(runner, steps)
+        worst, scale, bad = helpers.compare_rows(rows, names, folder, 1e-4 if dtype == "float32" else 6e-2,
+                                                 f"{dtype} window {window} {family}")
+        assert not bad, f"{family}: {len(bad)} rows differ, first {bad[:3]}, worst {worst:.3e} at scale {scale:.3f}"
