@@ -31,7 +31,11 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     const float wz_hi = mz_hi == -INFINITY ? 0.f : __expf(mz_hi - mmax);
     const float denom = warp_sum(lz * wz + lz_hi * wz_hi);
     const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-    for (int d = threadIdx.x * 2; d < HD; d += blockDim.x * 2) {
+    // every lane of a warp takes every turn of this loop (the weights travel by shuffles); lanes
+    // beyond the head's end - head sizes that are no multiple of 64 - load and store nothing
+    for (int d0 = 0; d0 < HD; d0 += blockDim.x * 2) {
+        const int d = d0 + threadIdx.x * 2;
+        const bool mine = d < HD;
         float a0 = 0.f, a1 = 0.f;
         for (int z0 = 0; z0 < nsplit; z0 += 8) {
             // eight splits' values are asked for before the first is used: one trip to memory for
@@ -40,7 +44,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int z = min(z0 + j, nsplit - 1);
-                v[j] = *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d);
+                v[j] = mine ? *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d)
+                            : make_float2(0.f, 0.f);
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -50,8 +55,9 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
                 if (z0 + j < nsplit && w != 0.f) { a0 += v[j].x * w; a1 += v[j].y * w; }   // a split without keys may hold anything
             }
         }
-        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * out_ld + h * HD + d) =
-            __floats2bfloat162_rn(a0 * inv, a1 * inv);
+        if (mine)
+            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)tok * out_ld + h * HD + d) =
+                __floats2bfloat162_rn(a0 * inv, a1 * inv);
     }
 }
 

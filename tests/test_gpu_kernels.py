@@ -393,6 +393,15 @@ def test_attention_split_keys(ops, kernel, dtype, nsplit):
     assert_rows_close(whole, case.want, case, dtype)
 
 
+@pytest.mark.parametrize("hd", [16, 48, 80, 112, 160, 256])
+@pytest.mark.parametrize("nsplit", [9, 17, 33])
+def test_attention_split_keys_at_other_head_sizes(ops, hd, nsplit):
+    """The merge of more than eight key ranges at head sizes that are no multiple of 64 (its
+    threads hold two dimensions each, so the last warp's lanes are not all in use)."""
+    case = PagedCase(torch.bfloat16, 6, 2, hd, 16, items=[(1300, 1), (0, 3), (2200, 1), (700, 20)], seed=13)
+    assert_rows_close(run_kernel(case, ops, "mma", nsplit), case.want, case, torch.bfloat16)
+
+
 @pytest.mark.parametrize("kernel,dtype", KERNELS)
 @pytest.mark.parametrize("key_at", ["first", "page_edge", "far", "self"])
 def test_attention_finds_one_far_key_among_hundreds(ops, kernel, dtype, key_at):
