@@ -236,7 +236,8 @@ def long_context_workload(args) -> int:
     batch, context, portion, page = 32, 8192, 2048, 16
     steps, warmup = min(args.steps, 32), max(args.warmup, 3)
     rng = np.random.default_rng(0)
-    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16", max_positions=context + 64)
+    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16", max_positions=context + 64,
+                                    **({"share_tiles": False} if args.share_tiles == "off" else {}))
     device = model.runtime.device
 
     def timed(fn):
@@ -444,6 +445,9 @@ def main() -> int:
     parser.add_argument("--few-token-limit", type=int, default=0,
                         help="steps of up to this many tokens take the engine's few-token tcgen05 product "
                              "(0 = the engine's choice, 16; up to 64 for measuring that choice)")
+    parser.add_argument("--share-tiles", default="on", choices=["on", "off"],
+                        help="off: the tiled product leaves a partial last round of tiles to the pairs of "
+                             "blocks it falls to instead of sharing it out among all (for measuring that choice)")
     parser.add_argument("--fp32-steps", type=int, default=8,
                         help="decode steps timed on the float32 path after the bf16 run (0 = skip)")
     parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline"],
@@ -487,6 +491,8 @@ def main() -> int:
     compute = "bfloat16" if args.dtype in ("bf16", "bfloat16") else "float32"
     bytes_per = 2 if compute == "bfloat16" else 4
     options = {"few_token_limit": args.few_token_limit} if args.few_token_limit else {}
+    if args.share_tiles == "off":
+        options["share_tiles"] = False
     model = LoadedModel.from_random(config, seed=0, std=0.02, dtype=compute,
                                     max_positions=args.context + 64, **options)
     device = model.runtime.device

@@ -25,6 +25,14 @@
 // first block supplies 128 gate rows and the second the 128 up rows of the same outputs, and
 // the epilogue writes 128 columns of silu(gate) * up.
 //
+// Tiles that do not fill a last round of the pairs (112 tiles on 74 pairs leave 36 pairs idle for
+// a whole tile's time) are shared out: after the full rounds, the k-blocks of the remaining tiles
+// are numbered tile after tile and cut into equal shares, one per pair, so a pair's share may end
+// one tile and begin the next.  A pair that has summed only part of a tile's k range leaves its
+// 32-bit sums in a workspace; the pair that arrives last at the tile's counter (per 32 rows, no
+// pair waits for another) adds the parts in the order of the shares - the same bits on every run -
+// and runs the epilogue.
+//
 // Rows of x beyond M and rows of w beyond its end are zero-filled by TMA and never stored.
 // Every wait on an mbarrier is bounded: when it runs out the kernel records where in
 // *error, lets the copies it started land, frees its tensor memory and returns.
@@ -63,8 +71,70 @@ struct TileGemmParams {
     int m_tiles, n_tiles;
     int out_f32;
     int tma_store;                  // y is written through map_y (bf16, rows on 16-byte boundaries)
+    // sharing of the last, partial round (share_pairs = 0: every tile is summed by one pair)
+    int full_rounds;                // rounds in which every pair takes a whole tile
+    int shared_tiles;               // tiles after those rounds
+    int share_pairs;                // pairs that take an equal share of their k-blocks
+    int max_parts;                  // most pairs that share one tile
+    float* workspace;               // [shared tile][part][block of the pair][128 rows][256 columns]
+    int* counters;                  // [shared tile][block of the pair][quarter], zero between launches
     int* error;
 };
+
+// One piece of work of a pair: k-blocks [kb0, kb1) of a tile.  shared >= 0: the tile is the
+// shared one of that index and this pair sums part `part` of `parts` of its k range.
+struct WorkItem { int tile, kb0, kb1, shared, part, parts; };
+
+__device__ __forceinline__ long long share_begin(long long units, int pairs, int j) { return units * j / pairs; }
+// the pair whose share holds unit u
+__device__ __forceinline__ int share_of(long long units, int pairs, long long u) {
+    int j = (int)(u * pairs / units);
+    while (j + 1 < pairs && share_begin(units, pairs, j + 1) <= u) ++j;
+    while (j > 0 && share_begin(units, pairs, j) > u) --j;
+    return j;
+}
+static int host_share_of(long long units, int pairs, long long u) {
+    int j = (int)(u * pairs / units);
+    while (j + 1 < pairs && units * (j + 1) / pairs <= u) ++j;
+    while (j > 0 && units * j / pairs > u) --j;
+    return j;
+}
+// The pair's i-th piece of work; false when it has no more.
+__device__ __forceinline__ bool work_item(const TileGemmParams& p, int pair, int pairs, int kblocks, int total_tiles,
+                                          int i, WorkItem& w) {
+    w.kb0 = 0; w.kb1 = kblocks; w.shared = -1; w.part = 0; w.parts = 1;
+    if (p.share_pairs == 0) {
+        w.tile = pair + i * pairs;
+        return w.tile < total_tiles;
+    }
+    // The shared tiles come first: what their parts cost beyond the sums (the workspace traffic,
+    // the adding by whoever comes last) then runs in the epilogue warps under the MMAs of the
+    // whole tiles that follow.
+    int pieces = 0;
+    long long u0 = 0, u1 = 0;
+    const long long units = (long long)p.shared_tiles * kblocks;
+    if (pair < p.share_pairs) {
+        u0 = share_begin(units, p.share_pairs, pair); u1 = share_begin(units, p.share_pairs, pair + 1);
+        if (u1 > u0) pieces = (int)((u1 - 1) / kblocks - u0 / kblocks) + 1;
+    }
+    if (i >= pieces) {
+        const int round = i - pieces;
+        w.tile = pair + round * pairs;
+        return round < p.full_rounds;
+    }
+    const int r = (int)(u0 / kblocks) + i;
+    const long long first = (long long)r * kblocks;
+    w.tile = p.full_rounds * pairs + r;
+    w.kb0 = (int)(u0 > first ? u0 - first : 0);
+    w.kb1 = (int)(u1 - first < kblocks ? u1 - first : kblocks);
+    if (w.kb0 > 0 || w.kb1 < kblocks) {
+        const int lowest = share_of(units, p.share_pairs, first);
+        w.shared = r;
+        w.part = pair - lowest;
+        w.parts = share_of(units, p.share_pairs, first + kblocks - 1) - lowest + 1;
+    }
+    return true;
+}
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -127,6 +197,24 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v) {
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
 }
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// the reverse: D[lane, column + j] = v[j]
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr),
+          "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Stores 32 consecutive outputs of one row, columns n .. n + 31 as far as they lie below N.
 __device__ __forceinline__ void store_row_chunk(const TileGemmParams& p, int row, int n, const float* v, bool vector_ok) {
@@ -221,10 +309,12 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             const int n0 = tile_n(tile) * TILE_COLS;
             return EPI == EPI_SWIGLU ? (rank == 0 ? n0 : p.up_row0 + n0) : n0 + rank * HALF;
         };
-        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+        WorkItem work;
+        for (int item = 0; ok && work_item(p, pair, pairs, kblocks, total_tiles, item, work); ++item) {
+            const int tile = work.tile;
             const int m0 = tile_m(tile) * TILE + rank * HALF;
             const int w_row = w_row_of(tile);
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+            for (int kb = work.kb0; kb < work.kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) {
                     atomicExch(p.error, ERR_TMA_WAIT); atomicExch(&abort_flag, 1);
@@ -253,7 +343,8 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const uint32_t idesc = umma_idesc(TILE, TILE);
         int it = 0, local_tile = 0;
         bool ok = true;
-        for (int tile = pair; tile < total_tiles && ok; tile += pairs, ++local_tile) {
+        WorkItem work;
+        for (; ok && work_item(p, pair, pairs, kblocks, total_tiles, local_tile, work); ++local_tile) {
             const int buf = local_tile & 1;
             if (local_tile >= 2) {      // both blocks' epilogue warps have read this accumulator's previous tile
                 if (!mbar_wait(&acc_empty[buf], ((local_tile >> 1) - 1) & 1)) {
@@ -261,7 +352,7 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+            for (int kb = work.kb0; kb < work.kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 if (*(volatile int*)&abort_flag) { ok = false; break; }
                 if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
@@ -275,7 +366,7 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 #pragma unroll
                     for (int k = 0; k < ATOM_K / UMMA_K; ++k) {
                         // 16 elements further along k: 32 bytes inside the swizzled row (address field in 16-byte units)
-                        umma_bf16_pair(tmem + buf * TILE, a + 2 * k, b + 2 * k, idesc, (kb > 0 || at > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16_pair(tmem + buf * TILE, a + 2 * k, b + 2 * k, idesc, (kb > work.kb0 || at > 0 || k > 0) ? 1u : 0u);
                     }
                 }
                 umma_commit_pair(&empty_bar[s]);     // the stage is free in both blocks once these MMAs have read it
@@ -292,7 +383,9 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const bool vector_ok = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
         unsigned char* boxes = smem + STAGES * STAGE_BYTES + (warp - 2) * 2 * OUT_BOX_BYTES;
         int local_tile = 0, groups = 0;
-        for (int tile = pair; tile < total_tiles; tile += pairs, ++local_tile) {
+        WorkItem work;
+        for (; work_item(p, pair, pairs, kblocks, total_tiles, local_tile, work); ++local_tile) {
+            const int tile = work.tile;
             const int buf = local_tile & 1;
             const int row0 = tile_m(tile) * TILE + rank * HALF + quarter * 32;
             const int n0 = tile_n(tile) * TILE_COLS;
@@ -302,6 +395,75 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16) + buf * TILE;
+            // ---- a tile whose k range this pair has summed only in part
+            // Workspace of one part and one warp: 8 chunks of 32 columns, a chunk as 8 x 32 lanes x 16
+            // bytes, so that a warp's store (and the load of the same lane later) is one 512-byte run.
+            constexpr size_t WARP_FLOATS = (size_t)32 * TILE, PART_FLOATS = (size_t)2 * HALF * TILE;
+            if (work.shared >= 0) {
+                float* warp_of_part0 = p.workspace + (size_t)work.shared * p.max_parts * PART_FLOATS +
+                                       ((size_t)rank * EPILOGUE_WARPS + quarter) * WARP_FLOATS;
+                float* mine = warp_of_part0 + (size_t)work.part * PART_FLOATS;
+#pragma unroll 1
+                for (int c = 0; c < TILE / 32; ++c) {
+                    float v[32];
+                    tmem_load_32(trow + c * 32, v);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        __stcg(reinterpret_cast<float4*>(mine + c * 1024 + q * 128 + lane * 4),
+                               make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                }
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    int* counter = p.counters + (work.shared * 2 + rank) * EPILOGUE_WARPS + quarter;
+                    last = atomicAdd(counter, 1) == work.parts - 1;
+                    if (last) *counter = 0;          // for the next launch; nobody else comes in this one
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (!last) {                         // another pair will add the parts and store
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_first_block(&acc_empty[buf]);
+                    continue;
+                }
+                __threadfence();
+                // Add the parts (four at most) into the accumulator in tensor memory, in the order of
+                // the shares: this pair's own part comes from tensor memory, the others' are asked for
+                // together.  The epilogue below then finds the whole sums where it always finds them.
+#pragma unroll 1
+                for (int c = 0; c < TILE / 32; ++c) {
+                    float4 theirs[3][8];
+#pragma unroll
+                    for (int o = 0; o < 3; ++o) {
+                        const int part = o < work.part ? o : o + 1;      // the o-th part that is not this pair's
+                        if (part < work.parts) {
+                            const float* src = warp_of_part0 + (size_t)part * PART_FLOATS + c * 1024 + lane * 4;
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) theirs[o][q] = __ldcg(reinterpret_cast<const float4*>(src + q * 128));
+                        }
+                    }
+                    float own[32], sum[32];
+                    tmem_load_32(trow + c * 32, own);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int part = 0; part < 4; ++part) {
+                        if (part >= work.parts) break;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            float4 t;
+                            if (part == work.part) t = make_float4(own[4 * q], own[4 * q + 1], own[4 * q + 2], own[4 * q + 3]);
+                            else if (part < work.part) t = theirs[part < 3 ? part : 2][q];
+                            else t = theirs[part > 0 ? part - 1 : 0][q];
+                            if (part == 0) { sum[4 * q] = t.x; sum[4 * q + 1] = t.y; sum[4 * q + 2] = t.z; sum[4 * q + 3] = t.w; }
+                            else { sum[4 * q] += t.x; sum[4 * q + 1] += t.y; sum[4 * q + 2] += t.z; sum[4 * q + 3] += t.w; }
+                        }
+                    }
+                    tmem_store_32(trow + c * 32, sum);
+                }
+                tmem_store_wait();
+            }
 #pragma unroll 1
             for (int c = 0; c < TILE_COLS / 32; ++c) {
                 const int col = c * 32, n = n0 + col;
@@ -438,14 +600,42 @@ static int configure(int* max_pairs_out) {
     return 0;
 }
 
+// How the tiles after the last full round are shared out among `pairs` pairs: fills the sharing
+// fields of p and returns the floats of workspace and the counters that the launch needs (0, 0
+// when every tile is summed by one pair: no partial round, nothing to gain, or shares too short).
+static void plan_sharing(TileGemmParams& p, long long tiles, int pairs, long long* floats, int* counters) {
+    p.full_rounds = 0; p.shared_tiles = 0; p.share_pairs = 0; p.max_parts = 1;
+    *floats = 0; *counters = 0;
+    const int kblocks = (p.K + BK - 1) / BK;
+    const int rest = (int)(tiles % pairs);
+    // A partial round that occupies nine pairs in ten already gains too little for the workspace
+    // traffic; and the adding of the parts hides under the whole tiles that follow, so without a
+    // full round (fewer tiles than pairs: measured slower than leaving the tiles whole) nothing is shared.
+    if (pairs < 2 || rest == 0 || tiles < pairs || rest * 10 >= pairs * 9) return;
+    // at most four pairs per tile (the pair that arrives last adds their parts), shares of two k-blocks at least
+    int share_pairs = pairs < 3 * rest ? pairs : 3 * rest;
+    const long long units = (long long)rest * kblocks;
+    if (share_pairs > units / 2) share_pairs = (int)(units / 2);
+    int most = 1;
+    for (;; --share_pairs) {
+        if (share_pairs <= rest) return;
+        most = 1;
+        for (int r = 0; r < rest; ++r) {
+            const int parts = host_share_of(units, share_pairs, (long long)(r + 1) * kblocks - 1) -
+                              host_share_of(units, share_pairs, (long long)r * kblocks) + 1;
+            if (parts > most) most = parts;
+        }
+        if (most <= 4) break;
+    }
+    p.full_rounds = (int)(tiles / pairs); p.shared_tiles = rest; p.share_pairs = share_pairs; p.max_parts = most;
+    *floats = (long long)rest * most * 2 * HALF * TILE;
+    *counters = rest * 2 * EPILOGUE_WARPS;
+}
+
 // Launch of `pairs` clusters of two blocks as a programmatic dependent of the kernel before it.
 template <int EPI>
 static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const CUtensorMap& map_y, const TileGemmParams& p,
                   int pairs, cudaStream_t stream) {
-    int max_pairs = 0;
-    const int rc = configure<EPI>(&max_pairs);
-    if (rc != 0) return rc;
-    if (pairs > max_pairs) pairs = max_pairs;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(2 * pairs, 1, 1);
     config.blockDim = dim3(THREADS, 1, 1);
@@ -490,11 +680,43 @@ int fsie_gemm_tiles_weight_map(void* map_out, const void* w, long long rows, lon
     return rc;
 }
 
+// The pairs that a launch with these sizes uses, and what it needs to share out a partial last
+// round of tiles: floats of workspace and ints of counters (both 0 when it does not share).
+static int plan(int M, int N, int K, int swiglu, int blocks, TileGemmParams& p, int* pairs_out, long long* floats,
+                int* counters) {
+    int max_pairs = 0;
+    const int rc = swiglu ? configure<EPI_SWIGLU>(&max_pairs) : configure<EPI_PLAIN>(&max_pairs);
+    if (rc != 0) return rc;
+    p.M = M; p.N = N; p.K = K;
+    p.m_tiles = (M + TILE - 1) / TILE;
+    p.n_tiles = swiglu ? (N + TILE / 2 - 1) / (TILE / 2) : (N + TILE - 1) / TILE;
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    int pairs = blocks / 2 > 0 ? blocks / 2 : 1;
+    if (pairs > max_pairs) pairs = max_pairs;
+    if (tiles < pairs) pairs = (int)tiles;
+    *pairs_out = pairs;
+    plan_sharing(p, tiles, pairs, floats, counters);
+    return 0;
+}
+
+// What fsie_gemm_tiles needs beside its operands for these sizes: floats of workspace and ints of
+// counters (zero before the first launch; every launch leaves them zero).  Both 0 where no tile is shared.
+int fsie_gemm_tiles_workspace(int M, int N, int K, int swiglu, int blocks, long long* floats, int* counters) {
+    *floats = 0; *counters = 0;
+    if (M <= 0 || N <= 0 || K <= 0 || blocks <= 0) return 0;
+    TileGemmParams p;
+    int pairs = 0;
+    return plan(M, N, K, swiglu, blocks, p, &pairs, floats, counters);
+}
+
 // y[M, N] = x[M, K] * w^T (+ bias), or for swiglu y[M, N] = silu(x w_gate^T) * (x w_up^T) with
 // w = [gate rows (N); up rows (N)].  `blocks` is the size of the persistent grid (the number
-// of SMs; it is cut to the pairs that can run at once and to the number of tiles).
+// of SMs; it is cut to the pairs that can run at once and to the number of tiles).  workspace and
+// counters: see fsie_gemm_tiles_workspace; with less than that (or null) every tile is summed by
+// one pair, as if the last round were full.
 int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* y, long long ldy, const void* bias,
-                    int M, int N, int K, int swiglu, int out_f32, int blocks, int* error, cudaStream_t stream) {
+                    int M, int N, int K, int swiglu, int out_f32, int blocks, float* workspace,
+                    long long workspace_floats, int* counters, int counters_len, int* error, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || blocks <= 0 || (swiglu && out_f32))
         return ERR_BAD_ARGUMENT;
@@ -503,7 +725,14 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
     int rc = make_map(&map_x, x, M, K, ldx);
     if (rc != 0) return rc;
     TileGemmParams p;
-    p.y = y; p.ldy = ldy; p.bias = (const bf16*)bias; p.M = M; p.N = N; p.K = K;
+    int pairs = 0, need_counters = 0;
+    long long need_floats = 0;
+    rc = plan(M, N, K, swiglu, blocks, p, &pairs, &need_floats, &need_counters);
+    if (rc != 0) return rc;
+    if (p.share_pairs > 0 && (!workspace || !counters || workspace_floats < need_floats || counters_len < need_counters))
+        p.share_pairs = 0;
+    p.workspace = workspace; p.counters = counters;
+    p.y = y; p.ldy = ldy; p.bias = (const bf16*)bias;
     p.up_row0 = N; p.out_f32 = out_f32; p.error = error;
     // the copy engine writes y when its rows start on 16-byte boundaries; else the lanes store their rows
     p.tma_store = !out_f32 && ldy % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
@@ -512,11 +741,6 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
         rc = make_out_map(&map_y, y, M, N, ldy);
         if (rc != 0) return rc;
     }
-    p.m_tiles = (M + TILE - 1) / TILE;
-    p.n_tiles = swiglu ? (N + TILE / 2 - 1) / (TILE / 2) : (N + TILE - 1) / TILE;
-    const long long tiles = (long long)p.m_tiles * p.n_tiles;
-    int pairs = blocks / 2 > 0 ? blocks / 2 : 1;
-    if (tiles < pairs) pairs = (int)tiles;
     return swiglu ? launch<EPI_SWIGLU>(map_w, map_x, map_y, p, pairs, stream) : launch<EPI_PLAIN>(map_w, map_x, map_y, p, pairs, stream);
 }
 

@@ -40,7 +40,8 @@ class Runtime:
     def __init__(self, device="cuda:0", dtype=torch.bfloat16, max_positions: int = 0,
                  few_token_min_elements: int = 32 * 1024 * 1024, products: str = "own",
                  tiled_min_tiles: Optional[int] = None,
-                 decode_tcgen05_min_blocks: Optional[int] = None, few_token_limit: int = 16):
+                 decode_tcgen05_min_blocks: Optional[int] = None, few_token_limit: int = 16,
+                 share_tiles: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this engine has no CPU path")
         self.device = torch.device(device)
@@ -80,6 +81,9 @@ class Runtime:
                                           else int(decode_tcgen05_min_blocks))
         # steps of few tokens rotate q, k and write k, v in the q, k, v product's epilogue
         self.fused_qkv_rope = True
+        # the tiled product shares a partial last round of tiles out among all pairs of blocks
+        self.share_tiles = bool(share_tiles)
+        self._tiles_counters: Optional[torch.Tensor] = None
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -152,7 +156,17 @@ class Runtime:
 
     def _tiled_product(self, prepared, x, bias, out_dtype, tag=None) -> torch.Tensor:
         out = self.buffer(tag, x.shape[0], prepared.n, out_dtype)
-        return ops.gemm_tiles(prepared, x, out, bias, self.error, self.sm_count)
+        # where the tiles leave a partial last round, the kernel shares that round's tiles out among
+        # all pairs of blocks and needs room for their partial sums (kept, grown when more is needed)
+        floats, counters = ops.gemm_tiles_workspace(x.shape[0], prepared.n, prepared.k, prepared.swiglu,
+                                                    self.sm_count) if self.share_tiles else (0, 0)
+        workspace = None
+        if floats:
+            if self._tiles_counters is None or self._tiles_counters.numel() < counters:
+                self._tiles_counters = torch.zeros(max(counters, 1024), dtype=torch.int32, device=self.device)
+            workspace = self.buffer("gemm_tiles.parts", 1, floats, torch.float32).view(-1)
+        return ops.gemm_tiles(prepared, x, out, bias, self.error, self.sm_count, workspace,
+                              self._tiles_counters if workspace is not None else None)
 
     def _few_tokens(self, x: torch.Tensor, weight: torch.Tensor) -> Optional["ops.DecodeWeight"]:
         if x.shape[0] > max(self.few_token_limit, self.few_token_limit_fused) or x.stride(0) % 8:

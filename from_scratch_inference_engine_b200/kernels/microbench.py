@@ -239,8 +239,13 @@ def run(args):
         out = torch.empty((m, n), dtype=dtype, device="cuda")
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
         sms = torch.cuda.get_device_properties(0).multi_processor_count
-        ms = timer(lambda: ops.gemm_tiles(weight, x, out, None, error, sms))
-        extra = {"error": int(error.item())}
+        floats, ints = (0, 0) if args.variant == "whole_tiles" else \
+            ops.gemm_tiles_workspace(m, n, k, swiglu, sms)
+        workspace = torch.empty(floats, dtype=torch.float32, device="cuda") if floats else None
+        counters = torch.zeros(max(ints, 1), dtype=torch.int32, device="cuda") if floats else None
+        ms = timer(lambda: ops.gemm_tiles(weight, x, out, None, error, sms, workspace, counters))
+        extra = {"error": int(error.item()), "workspace_floats": floats,
+                 "counters_left": int(counters.abs().sum().item()) if floats else 0}
         nbytes, flops = (m * k + w.shape[0] * k + m * n) * elem, 2.0 * m * w.shape[0] * k
     elif args.kernel in ("linear", "gemm_f32"):
         m, n, k = args.tokens, args.n, args.k
@@ -285,9 +290,10 @@ def main(argv=None) -> int:
     parser.add_argument("--n", type=int, default=37888)
     parser.add_argument("--k", type=int, default=3584)
     parser.add_argument("--nsplit", type=int, default=0, help="0 = the engine's choice")
-    parser.add_argument("--variant", default="mma", choices=["mma", "tc", "rows16"],
+    parser.add_argument("--variant", default="mma", choices=["mma", "tc", "rows16", "whole_tiles"],
                         help="bfloat16 attention: mma.sync with cp.async loads, or tcgen05; float32 "
-                             "attention: rows16 takes the kernel for tiles of up to 16 rows")
+                             "attention: rows16 takes the kernel for tiles of up to 16 rows; gemm_tiles: "
+                             "whole_tiles leaves a partial last round of tiles to the pairs it falls to")
     parser.add_argument("--f32-kind", default="auto", choices=["auto", "rows", "tiles", "plain"],
                         help="gemm_f32: which of the float32 kernels (frac_ffma is of the nominal "
                              "74.4 TFLOP/s: 148 SMs x 128 lanes x 2 x 1.965 GHz)")

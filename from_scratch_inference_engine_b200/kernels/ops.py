@@ -9,7 +9,7 @@ machine without the compiled library or without a GPU they raise.
 from __future__ import annotations
 
 import ctypes
-from typing import Dict, Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -645,10 +645,11 @@ def gemm_tiles_lib():
         i, ll, p = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p
         lib.fsie_gemm_tiles_map_bytes.argtypes = []
         lib.fsie_gemm_tiles_weight_map.argtypes = [p, p, ll, ll]
-        lib.fsie_gemm_tiles.argtypes = [p, p, ll, p, ll, p, i, i, i, i, i, i, p, p]
+        lib.fsie_gemm_tiles.argtypes = [p, p, ll, p, ll, p, i, i, i, i, i, i, p, ll, p, i, p, p]
+        lib.fsie_gemm_tiles_workspace.argtypes = [i, i, i, i, i, ctypes.POINTER(ll), ctypes.POINTER(i)]
         lib.fsie_gemm_tiles_pairs.argtypes = []
         for name in ("fsie_gemm_tiles_map_bytes", "fsie_gemm_tiles_weight_map", "fsie_gemm_tiles",
-                     "fsie_gemm_tiles_pairs"):
+                     "fsie_gemm_tiles_pairs", "fsie_gemm_tiles_workspace"):
             getattr(lib, name).restype = i
         pairs = lib.fsie_gemm_tiles_pairs()       # also sets the kernels up, outside any capture
         if pairs <= 0:
@@ -684,10 +685,26 @@ class TiledWeight:
                "gemm_tiles weight map")
 
 
+def gemm_tiles_workspace(rows: int, n: int, k: int, swiglu: bool, blocks: int) -> Tuple[int, int]:
+    """(floats of workspace, ints of counters) with which `gemm_tiles` shares the tiles of a
+    partial last round out among all pairs of blocks; (0, 0) where it has none to share."""
+    floats, counters = ctypes.c_longlong(0), ctypes.c_int(0)
+    code = gemm_tiles_lib().fsie_gemm_tiles_workspace(rows, n, k, int(swiglu), blocks,
+                                                      ctypes.byref(floats), ctypes.byref(counters))
+    if code != 0:
+        raise KernelError(f"gemm_tiles_workspace failed with code {code}")
+    return int(floats.value), int(counters.value)
+
+
 def gemm_tiles(weight: TiledWeight, x: torch.Tensor, out: torch.Tensor,
-               bias: Optional[torch.Tensor], error: torch.Tensor, blocks: int) -> torch.Tensor:
+               bias: Optional[torch.Tensor], error: torch.Tensor, blocks: int,
+               workspace: Optional[torch.Tensor] = None,
+               counters: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w.T (+ bias), or silu(x @ gate.T) * (x @ up.T), any M; out is
-    bfloat16 (or float32 for the plain product).  `blocks`: size of the persistent grid."""
+    bfloat16 (or float32 for the plain product).  `blocks`: size of the persistent grid.
+    workspace (float32) and counters (int32, zero before the first call; every call leaves them
+    zero) of the sizes `gemm_tiles_workspace` names let the kernel share out the tiles of a
+    partial last round; without them every tile is summed by one pair of blocks."""
     _need(x, torch.bfloat16, "x", contiguous=False)
     _need(out, None, "out", contiguous=False)
     rows, k = x.shape
@@ -701,9 +718,14 @@ def gemm_tiles(weight: TiledWeight, x: torch.Tensor, out: torch.Tensor,
         _need(bias, torch.bfloat16, "bias")
         if weight.swiglu or bias.numel() != weight.n:
             raise KernelError("gemm_tiles: bias does not fit")
+    if workspace is not None:
+        _need(workspace, torch.float32, "workspace")
+        _need(counters, torch.int32, "counters")
     _check(gemm_tiles_lib().fsie_gemm_tiles(
         weight.map_ptr, _ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(bias), rows,
-        weight.n, k, int(weight.swiglu), int(out.dtype is torch.float32), blocks, _ptr(error),
+        weight.n, k, int(weight.swiglu), int(out.dtype is torch.float32), blocks,
+        _ptr(workspace), workspace.numel() if workspace is not None else 0,
+        _ptr(counters), counters.numel() if counters is not None else 0, _ptr(error),
         _stream()), "gemm_tiles")
     return out
 

@@ -659,6 +659,58 @@ def test_gemm_tiles_swiglu_epilogue(ops, rows, inter, k, blocks):
     assert (out.double() - want).abs().max().item() < 2.5e-2 * want.abs().max().item()
 
 
+@pytest.mark.parametrize("rows,n,k,blocks,swiglu", [
+    (700, 1288, 1024, 10, False),      # 18 tiles on 5 pairs: 3 tiles shared out among 5
+    (2048, 3584, 512, 148, False),     # 112 tiles on 74 pairs: 38 shared out among 74, k-blocks cut 2 and 3 ways
+    (300, 2000, 2056, 148, False),     # fewer tiles than pairs never share; ragged k
+    (1000, 520, 1536, 12, False),      # 12 tiles on 6 pairs: a full last round
+    (515, 1100, 776, 14, True),        # SwiGLU: 27 tiles on 7 pairs, 6 shared; ragged everywhere
+    (2300, 300, 4096, 16, False),      # 18 tiles on 8 pairs: 2 shared four ways each
+])
+def test_gemm_tiles_shares_a_partial_last_round(ops, rows, n, k, blocks, swiglu):
+    """With a workspace the tiles that do not fill a last round are cut along k among all pairs
+    and the parts are added by whoever comes last, in the order of the shares: the result is
+    the same on every run, equals the product, and the counters are left at zero."""
+    torch.manual_seed(rows + n)
+    x = dev(torch.randn(rows, k), torch.bfloat16)
+    w = dev(torch.randn((2 if swiglu else 1) * n, k) / math.sqrt(k), torch.bfloat16)
+    bias = None if swiglu else dev(torch.randn(n), torch.bfloat16)
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    full = x.double() @ w.double().T
+    if swiglu:
+        full = full.to(torch.bfloat16).double()
+        want = plain.silu_mul(full[:, :n], full[:, n:])
+    else:
+        want = full + bias.double()
+    weight = ops.TiledWeight(w, swiglu=swiglu)
+    floats, ints = ops.gemm_tiles_workspace(rows, n, k, swiglu, blocks)
+    workspace = torch.full((max(floats, 1),), float("nan"), dtype=torch.float32, device="cuda")
+    counters = torch.zeros(max(ints, 1), dtype=torch.int32, device="cuda")
+    outs = []
+    for _ in range(3):
+        out = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.gemm_tiles(weight, x, out, bias, error, blocks, workspace, counters)
+        assert error.item() == 0 and counters.abs().sum().item() == 0
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    bound = (2.5e-2 if swiglu else 1.6e-2) * want.abs().max().item()
+    assert (outs[0].double() - want).abs().max().item() < bound
+    # the same tiles summed by one pair each differ from the shared ones by the order of the sums only
+    whole = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tiles(weight, x, whole, bias, error, blocks)
+    assert (whole.double() - outs[0].double()).abs().max().item() <= 1.6e-2 * want.abs().max().item()
+    if not swiglu:
+        out32 = torch.full((rows, n), float("nan"), dtype=torch.float32, device="cuda")
+        ops.gemm_tiles(weight, x, out32, None, error, blocks, workspace, counters)
+        assert (out32.double() - full).abs().max().item() < 2e-3 * full.abs().max().item()
+
+
+def test_gemm_tiles_workspace_is_asked_for_only_where_a_round_is_partial(ops):
+    assert ops.gemm_tiles_workspace(2048, 3584, 18944, False, 148)[0] > 0          # 112 tiles, 74 pairs
+    assert ops.gemm_tiles_workspace(2048, 18944, 3584, True, 148) == (0, 0)        # 1,184 tiles: 16 full rounds
+    assert ops.gemm_tiles_workspace(256, 256, 4096, False, 148) == (0, 0)          # one tile
+
+
 @pytest.mark.parametrize("rows,blocks", [(2600, 148), (2600, 6), (4200, 10), (2049, 148)])
 def test_gemm_tiles_bands_of_row_tiles(ops, rows, blocks):
     """More than eight tiles of rows: the tiles are walked in bands of eight row tiles, the
