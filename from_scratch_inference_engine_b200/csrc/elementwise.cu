@@ -87,13 +87,25 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restric
                                        const int* __restrict__ rows, int hidden, float eps,
                                        int write_x) {
     __shared__ float scratch[32];
-    grid_dependency_wait();
-    grid_dependents_go();
     const int r = blockIdx.x;
     const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    const int chunks = hidden / 8;
+    // the gain and the list of rows do not come from the kernel before this one: they are on
+    // their way while that kernel still runs (rows of up to 16,384 values: beyond that the
+    // registers of the block's up to 1,024 threads do not hold the gain beside the row)
+    constexpr bool EARLY_GAIN = NCH <= 2;
+    float g[NCH][8];
+    if (EARLY_GAIN) {
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < chunks) load8(gain + c * 8, g[k]);
+        }
+    }
+    grid_dependency_wait();
+    grid_dependents_go();
     float* xr = x + s * hidden;
     const T* dr = delta ? delta + s * hidden : nullptr;
-    const int chunks = hidden / 8;
     float v[NCH][8];
     float ss = 0.f;
 #pragma unroll
@@ -119,10 +131,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restric
         const int c = threadIdx.x + k * blockDim.x;
         if (c < chunks) {
             if (write_x && dr) store8(xr + c * 8, v[k]);
-            float g[8], o[8];
-            load8(gain + c * 8, g);
+            float o[8];
+            if (!EARLY_GAIN) load8(gain + c * 8, g[k]);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = (v[k][i] * scale) * g[i];
+            for (int i = 0; i < 8; ++i) o[i] = (v[k][i] * scale) * g[k][i];
             store8(yr + c * 8, o);
         }
     }
