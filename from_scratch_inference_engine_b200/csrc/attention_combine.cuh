@@ -26,6 +26,16 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
         mz_hi = part_ml[((lane + 32) * stride + slot) * 2];
         lz_hi = part_ml[((lane + 32) * stride + slot) * 2 + 1];
     }
+    // the first eight splits' values are asked for at once, beside the maxima and sums above: their
+    // addresses do not depend on those (one trip to memory instead of two in a row)
+    const int d_first = threadIdx.x * 2;
+    float2 ahead[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int z = min(j, nsplit - 1);
+        ahead[j] = d_first < HD ? *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d_first)
+                                : make_float2(0.f, 0.f);
+    }
     const float mmax = warp_max(fmaxf(mz, mz_hi));
     const float wz = mz == -INFINITY ? 0.f : __expf(mz - mmax);
     const float wz_hi = mz_hi == -INFINITY ? 0.f : __expf(mz_hi - mmax);
@@ -44,8 +54,9 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int z = min(z0 + j, nsplit - 1);
-                v[j] = mine ? *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d)
-                            : make_float2(0.f, 0.f);
+                if (d0 == 0 && z0 == 0) v[j] = ahead[j];
+                else v[j] = mine ? *reinterpret_cast<const float2*>(part_o + (z * stride + slot) * HD + d)
+                                 : make_float2(0.f, 0.f);
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
