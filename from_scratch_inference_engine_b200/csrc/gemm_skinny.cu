@@ -92,6 +92,27 @@ gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
     };
 #pragma unroll
     for (int j = 0; j < SK_AHEAD; ++j) ask(j, warp + j * SK_WARPS);    // weights do not depend on the kernel before
+    // Nor does what the epilogue's rotation needs: the token's position and slot were staged before
+    // the step, the table and the bias are constants.  A thread of the epilogue owns one rotation
+    // pair of one token (the block has more threads than such pairs) and fetches its angle now.
+    constexpr int TP = 8 * TT;
+    static_assert(8 * TP <= 32 * SK_WARPS, "one rotation pair per thread");
+    int early_pos = 0, early_slot = -1;
+    float early_cos = 1.f, early_sin = 0.f, early_bias_lo = 0.f, early_bias_hi = 0.f;
+    if (ROPE) {
+        const int token = threadIdx.x >> 3, r = threadIdx.x & 7;
+        if (threadIdx.x < 8 * TP && token < p.T) {
+            const int per_head = rope.head_dim / 16;
+            const int head = blockIdx.x / per_head, d = (blockIdx.x - head * per_head) * 8 + r;
+            early_pos = rope.positions[token];
+            if (head < rope.heads + rope.kv_heads && early_pos >= 0 && early_pos < rope.table_len) {
+                const float* cs = rope.cos_sin + (size_t)early_pos * rope.head_dim;
+                early_cos = cs[d]; early_sin = cs[rope.head_dim / 2 + d];
+            }
+            if (head >= rope.heads && rope.slot_of) early_slot = rope.slot_of[token];
+            if (p.bias) { early_bias_lo = __bfloat162float(p.bias[row0 + r]); early_bias_hi = __bfloat162float(p.bias[row8 + r]); }
+        }
+    }
     grid_dependency_wait();
     grid_dependents_go();
     // x: token 8 n + g, the same 16 bytes of k as this lane's weights (tokens beyond T read as zero);
@@ -122,7 +143,6 @@ gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
     }
     cp_async_wait<0>();
     // acc[n]: rows g (0, 1) and g + 8 (2, 3), tokens 8 n + 2 t and 8 n + 2 t + 1
-    constexpr int TP = 8 * TT;
 #pragma unroll
     for (int n = 0; n < TT; ++n) {
         float* mine = red + ((size_t)warp * SK_ROWS) * TP + 8 * n + 2 * t;
@@ -145,16 +165,17 @@ gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
                 lo += red[((size_t)w * SK_ROWS + r) * TP + token];
                 hi += red[((size_t)w * SK_ROWS + r + 8) * TP + token];
             }
-            if (p.bias) { lo += __bfloat162float(p.bias[row0 + r]); hi += __bfloat162float(p.bias[row8 + r]); }
+            lo += early_bias_lo; hi += early_bias_hi;             // (e is this thread's own pair: see above)
             // the unfused path stores the product as bfloat16 before it rotates: the same rounding here
             lo = __bfloat162float(__float2bfloat16_rn(lo));
             hi = __bfloat162float(__float2bfloat16_rn(hi));
             const int d = d0 + r;
             if (head < rope.heads + rope.kv_heads) {              // a query or key head: rotate
-                int pos = rope.positions[token];
-                if (pos < 0 || pos >= rope.table_len) { atomicExch(rope.error, 2); pos = 0; }
-                const float* cs = rope.cos_sin + (size_t)pos * rope.head_dim;
-                const float c = cs[d], sn = cs[half + d];
+                float c = early_cos, sn = early_sin;
+                if (early_pos < 0 || early_pos >= rope.table_len) {     // refused: as position 0, and the step fails
+                    atomicExch(rope.error, 2);
+                    c = rope.cos_sin[d]; sn = rope.cos_sin[half + d];
+                }
                 const float a = lo * c - hi * sn, b = hi * c + lo * sn;
                 lo = a; hi = b;
             }
@@ -162,7 +183,7 @@ gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
             if (head < rope.heads) {
                 dst = reinterpret_cast<bf16*>(p.y) + (size_t)token * p.ldy + head * rope.head_dim;
             } else {
-                const int slot = rope.slot_of ? rope.slot_of[token] : -1;
+                const int slot = early_slot;
                 if (slot < 0) continue;
                 const long long page = slot / rope.page_size;
                 const int offset = slot - (int)page * rope.page_size;
