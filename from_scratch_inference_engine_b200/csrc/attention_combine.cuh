@@ -11,9 +11,10 @@ constexpr int MAX_KEY_SPLITS = 64;
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                         bf16* __restrict__ out, int out_ld, int tokens, int heads,
                                         int nsplit, const int* __restrict__ token_list) {
+    // the list of tokens was staged before the step: it is read while the attention kernel still runs
+    const int tok = token_list ? token_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     grid_dependency_wait();
     grid_dependents_go();
-    const int tok = token_list ? token_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const size_t stride = (size_t)tokens * heads;              // (token, head) slots per split
     const size_t slot = (size_t)tok * heads + h;
