@@ -336,10 +336,20 @@ def timeline_workload(args) -> int:
             runner.step([StepEntry(handle, ids[at:at + 2048])])
         handles.append(handle)
     picks = torch.empty(batch, dtype=torch.int32, device=model.runtime.device)
+    if args.timeline_of == "prefill":
+        # one prompt of --prefill-tokens in one step, again and again
+        for handle in handles:
+            runner.cache.close(handle)
+        prompt = rng.integers(0, config.vocab_size, size=args.prefill_tokens).tolist()
 
-    def step():
-        logits = runner.step([StepEntry(h, [int(rng.integers(0, 1000))], [0]) for h in handles])
-        ops.argmax(logits, picks)
+        def step():
+            handle = runner.cache.open("p")
+            runner.step([StepEntry(handle, prompt, [len(prompt) - 1])])
+            runner.cache.close(handle)
+    else:
+        def step():
+            logits = runner.step([StepEntry(h, [int(rng.integers(0, 1000))], [0]) for h in handles])
+            ops.argmax(logits, picks)
     for _ in range(8):
         step()
     torch.cuda.synchronize()
@@ -356,7 +366,9 @@ def timeline_workload(args) -> int:
     one = events[first[3]:first[4]]
     origin = one[0].time_range.start
     name = lambda e: e.name.replace("fsie::", "").replace("void ", "")[:44]
-    print(f"decode step, batch {batch}, context {context}, {shape['num_hidden_layers']} layers: "
+    what = f"prefill step of {args.prefill_tokens} tokens" if args.timeline_of == "prefill" else \
+        f"decode step, batch {batch}, context {context}"
+    print(f"{what}, {shape['num_hidden_layers']} layers: "
           f"{events[first[4]].time_range.start - origin:.1f} us, {len(one)} kernels")
     print("   start     end  kernel (us from the step's first kernel; the second layer and what follows it)")
     per_layer = max(1, (len(one) - 5) // shape["num_hidden_layers"])
@@ -445,6 +457,8 @@ def main() -> int:
     parser.add_argument("--few-token-limit", type=int, default=0,
                         help="steps of up to this many tokens take the engine's few-token tcgen05 product "
                              "(0 = the engine's choice, 16; up to 64 for measuring that choice)")
+    parser.add_argument("--timeline-of", default="decode", choices=["decode", "prefill"],
+                        help="timeline: a decode step, or a step of one prompt of --prefill-tokens")
     parser.add_argument("--share-tiles", default="on", choices=["on", "off"],
                         help="off: the tiled product leaves a partial last round of tiles to the pairs of "
                              "blocks it falls to instead of sharing it out among all (for measuring that choice)")
