@@ -324,7 +324,8 @@ def timeline_workload(args) -> int:
     shape["num_hidden_layers"] = args.layers or shape["num_hidden_layers"]
     config = config_from_dict(shape)
     batch, context, page = args.batch, args.context, 16
-    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16", max_positions=context + 64)
+    model = LoadedModel.from_random(config, seed=0, std=0.02, dtype="bfloat16", max_positions=context + 64,
+                                    **({"share_tiles": False} if args.share_tiles == "off" else {}))
     rng = np.random.default_rng(0)
     runner = ModelRunner(model.model, model.runtime, page_size=page,
                          num_pages=batch * (context // page + 2), max_requests=batch)
