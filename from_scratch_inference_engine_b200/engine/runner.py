@@ -318,6 +318,7 @@ class ModelRunner:
         code = int(self.error.item())
         if code:
             self.error.zero_()
+            self.runtime.reset_after_fault()
             what = {1: "token id outside the vocabulary", 2: "position outside the table",
                     11: "matrix product: the copy engine's stage never became free",
                     12: "matrix product: a tile never arrived", 13: "matrix product: the "

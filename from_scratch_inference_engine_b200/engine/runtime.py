@@ -106,6 +106,12 @@ class Runtime:
             self._buffers[key] = have
         return have[:rows * cols].view(rows, cols)
 
+    def reset_after_fault(self) -> None:
+        """After a kernel has set the error flag: a tiled product that gave up may have left the
+        counters of its shared tiles above zero, where the next launch expects zero."""
+        if self._tiles_counters is not None:
+            self._tiles_counters.zero_()
+
     def pages_map(self, pages: torch.Tensor):
         """TMA descriptor of a cache group's page tensor (made once per tensor), or None when
         the tcgen05 attention kernels do not take its head size or page size."""
