@@ -83,7 +83,10 @@ class Runtime:
         self.fused_qkv_rope = True
         # the tiled product shares a partial last round of tiles out among all pairs of blocks
         self.share_tiles = bool(share_tiles)
-        self._tiles_counters: Optional[torch.Tensor] = None
+        # its counters (eight per shared tile, fewer tiles than pairs of SMs): made now, so that a
+        # step that is being captured into a graph never allocates them
+        self._tiles_counters = torch.zeros(8 * max(self.sm_count // 2, 1) + 8, dtype=torch.int32,
+                                           device=self.device)
         # bf16 products must accumulate in 32-bit all the way
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -109,8 +112,7 @@ class Runtime:
     def reset_after_fault(self) -> None:
         """After a kernel has set the error flag: a tiled product that gave up may have left the
         counters of its shared tiles above zero, where the next launch expects zero."""
-        if self._tiles_counters is not None:
-            self._tiles_counters.zero_()
+        self._tiles_counters.zero_()
 
     def pages_map(self, pages: torch.Tensor):
         """TMA descriptor of a cache group's page tensor (made once per tensor), or None when
@@ -167,9 +169,7 @@ class Runtime:
         floats, counters = ops.gemm_tiles_workspace(x.shape[0], prepared.n, prepared.k, prepared.swiglu,
                                                     self.sm_count) if self.share_tiles else (0, 0)
         workspace = None
-        if floats:
-            if self._tiles_counters is None or self._tiles_counters.numel() < counters:
-                self._tiles_counters = torch.zeros(max(counters, 1024), dtype=torch.int32, device=self.device)
+        if floats and counters <= self._tiles_counters.numel():
             workspace = self.buffer("gemm_tiles.parts", 1, floats, torch.float32).view(-1)
         return ops.gemm_tiles(prepared, x, out, bias, self.error, self.sm_count, workspace,
                               self._tiles_counters if workspace is not None else None)
