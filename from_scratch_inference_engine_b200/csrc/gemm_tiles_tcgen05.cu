@@ -85,18 +85,12 @@ struct TileGemmParams {
 // shared one of that index and this pair sums part `part` of `parts` of its k range.
 struct WorkItem { int tile, kb0, kb1, shared, part, parts; };
 
-__device__ __forceinline__ long long share_begin(long long units, int pairs, int j) { return units * j / pairs; }
+__host__ __device__ __forceinline__ long long share_begin(long long units, int pairs, int j) { return units * j / pairs; }
 // the pair whose share holds unit u
-__device__ __forceinline__ int share_of(long long units, int pairs, long long u) {
+__host__ __device__ __forceinline__ int share_of(long long units, int pairs, long long u) {
     int j = (int)(u * pairs / units);
     while (j + 1 < pairs && share_begin(units, pairs, j + 1) <= u) ++j;
     while (j > 0 && share_begin(units, pairs, j) > u) --j;
-    return j;
-}
-static int host_share_of(long long units, int pairs, long long u) {
-    int j = (int)(u * pairs / units);
-    while (j + 1 < pairs && units * (j + 1) / pairs <= u) ++j;
-    while (j > 0 && units * j / pairs > u) --j;
     return j;
 }
 // The pair's i-th piece of work; false when it has no more.
@@ -621,8 +615,8 @@ static void plan_sharing(TileGemmParams& p, long long tiles, int pairs, long lon
         if (share_pairs <= rest) return;
         most = 1;
         for (int r = 0; r < rest; ++r) {
-            const int parts = host_share_of(units, share_pairs, (long long)(r + 1) * kblocks - 1) -
-                              host_share_of(units, share_pairs, (long long)r * kblocks) + 1;
+            const int parts = share_of(units, share_pairs, (long long)(r + 1) * kblocks - 1) -
+                              share_of(units, share_pairs, (long long)r * kblocks) + 1;
             if (parts > most) most = parts;
         }
         if (most <= 4) break;
