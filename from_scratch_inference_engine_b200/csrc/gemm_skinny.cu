@@ -125,11 +125,7 @@ gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
 #pragma unroll
     for (int n = 0; n < TT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
     int slot = 0;
-    for (int c = warp; c < chunks; c += SK_WARPS) {
-        uint4 b[TT];
-#pragma unroll
-        for (int n = 0; n < TT; ++n)
-            b[n] = x_of[n] ? *reinterpret_cast<const uint4*>(x_of[n] + c * SK_CHUNK) : make_uint4(0, 0, 0, 0);
+    auto multiply = [&](const uint4 (&b)[TT], int c) {              // chunk c of the weights (this slot) times the tokens' chunk
         cp_async_wait<SK_AHEAD - 1>();                            // the oldest group - this slot - has landed
         const uint4 a_lo = *reinterpret_cast<const uint4*>(mine + slot * 1024);
         const uint4 a_hi = *reinterpret_cast<const uint4*>(mine + slot * 1024 + 512);
@@ -140,6 +136,24 @@ gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
         }
         ask(slot, c + SK_WARPS * SK_AHEAD);                       // refill what has just been used
         slot = slot + 1 == SK_AHEAD ? 0 : slot + 1;
+    };
+    // the x values of four of the warp's chunks are asked for together: a trip to L2 per four chunks
+    // instead of one per chunk
+    constexpr int X_AHEAD = 4;
+    for (int c0 = warp; c0 < chunks; c0 += X_AHEAD * SK_WARPS) {
+        uint4 b[X_AHEAD][TT];
+#pragma unroll
+        for (int j = 0; j < X_AHEAD; ++j) {
+            const int c = c0 + j * SK_WARPS;
+#pragma unroll
+            for (int n = 0; n < TT; ++n)
+                b[j][n] = (c < chunks && x_of[n]) ? *reinterpret_cast<const uint4*>(x_of[n] + c * SK_CHUNK) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < X_AHEAD; ++j) {
+            const int c = c0 + j * SK_WARPS;
+            if (c < chunks) multiply(b[j], c);
+        }
     }
     cp_async_wait<0>();
     // acc[n]: rows g (0, 1) and g + 8 (2, 3), tokens 8 n + 2 t and 8 n + 2 t + 1
