@@ -19,17 +19,25 @@ MAX_KEY_SPLITS = 64        # what the kernels that merge partial results take
 
 def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
                      blocks_per_sm: int = 2, decode_slots: int = 3, decode_fixed: int = 270,
-                     merge_cost: int = 350) -> int:
+                     merge_cost: int = 350, tile_keys: int = 64, merge_step: int = 28) -> int:
     """Into how many key ranges to split each tile (at most 64, each at least 128 keys).
 
     Tiles of decoded tokens all have the same work, so the time is waves x (fixed cost of a
-    block + keys per range); measured at batch 64 and context 4,096 the fixed cost of the
-    mma.sync kernel equals about 270 keys and three blocks fit on an SM (the tcgen05 kernel
-    for decoded tokens: 530 keys, two blocks: `decode_fixed`, `decode_slots`).  Tiles of a
-    prompt have uneven work and
-    are split only when there are fewer of them than block slots (`blocks_per_sm` per SM;
-    the tcgen05 kernel has one, and its partial results cost more than a little idling, so
-    it splits only to fill slots that would stay empty)."""
+    block + the keys of a range) + the launch that merges the ranges.  A range is a whole number
+    of the kernel's key tiles (`tile_keys`: 64 for the mma.sync kernel, 128 for the tcgen05 one),
+    so the candidates are tiles per range, two at least, and the count is what covers the
+    longest context with that many - 4,091 keys in ranges of two tiles are 32 ranges, none
+    empty, where 29 or 31 ranges would have been three tiles each.  Costs are in keys (a
+    64-key tile takes about 2 us): measured at context 4,096 the fixed cost of an mma.sync block
+    is about 270 keys and three blocks fit on an SM (tcgen05 kernel for decoded tokens: 530
+    keys, two blocks: `decode_fixed`, `decode_slots`); the merge costs `merge_cost` (5 us after
+    the mma.sync kernel at batch 8, 17 us after the tcgen05 kernel with 200 requests) and
+    `merge_step` more for every eight ranges beyond sixteen (it reads eight at a time), less
+    for eight or fewer.  Chosen this way a decode step at contexts of 4,090 takes 2.86 instead
+    of 2.91 ms at batch 1, 3.00 instead of 3.05 ms at batch 4, and as before at batch 8.
+    Tiles of a prompt have uneven work and are split only when there are fewer of them than
+    block slots (`blocks_per_sm` per SM; the tcgen05 kernel has one, and its partial results
+    cost more than a little idling, so it splits only to fill slots that would stay empty)."""
     if not even_work:
         slots = blocks_per_sm * sms
         if blocks >= slots:
@@ -37,12 +45,15 @@ def attention_splits(blocks: int, longest: int, sms: int, even_work: bool,
         wanted = slots // blocks if blocks_per_sm == 1 else -(-slots // blocks)
         return max(1, min(wanted, longest // 128, MAX_KEY_SPLITS))
     slots = decode_slots * sms
-    best, best_cost = 1, None
-    for n in range(1, max(1, min(MAX_KEY_SPLITS, longest // 128)) + 1):
-        # any split costs the launch that merges the partial results (`merge_cost`, in keys: 5 us
-        # after the mma.sync kernel at batch 8, 17 us after the tcgen05 kernel with 200 requests)
-        cost = -(-blocks * n // slots) * (decode_fixed + longest / n) + (merge_cost if n > 1 else 0)
-        if best_cost is None or cost < best_cost * 0.98:
+    best, best_cost = 1, -(-blocks // slots) * (decode_fixed + longest)
+    least = max(2, -(-128 // tile_keys))                # tiles of a range: 128 keys at least
+    for tiles in range(-(-longest // tile_keys) - 1, least - 1, -1):
+        n = -(-longest // (tiles * tile_keys))
+        if n < 2 or n > MAX_KEY_SPLITS:
+            continue
+        cost = -(-blocks * n // slots) * (decode_fixed + tiles * tile_keys) \
+            + merge_cost + merge_step * (-(-n // 8) - 2)
+        if cost < best_cost:
             best, best_cost = n, cost
     return best
 
@@ -155,7 +166,8 @@ class GqaAttention(Mixer):
                                   >= ctx.runtime.decode_tcgen05_min_blocks)
                 if decode_tcgen05:
                     nsplit = attention_splits(tiles.count * self.num_kv_heads, longest, sms, True,
-                                              decode_slots=2, decode_fixed=530, merge_cost=1300)
+                                              decode_slots=2, decode_fixed=530, merge_cost=1300,
+                                              tile_keys=128)
                 else:
                     nsplit = splits(tiles.count * self.num_kv_heads, longest, row_class == 0,
                                     1 if on_tcgen05 else 2)

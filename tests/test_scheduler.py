@@ -416,6 +416,13 @@ def test_key_splits_of_the_attention_launch():
     n = attention_splits(32, 4096, sms, True)
     assert 9 <= n <= 13 and 32 * n <= 3 * sms
     assert attention_splits(4, 4096, sms, True) >= 24           # batch 1
+    # a range is a whole number of 64-key tiles: 4,091 keys in ranges of two tiles are 32 ranges,
+    # none of them empty (29 or 31 ranges would be three tiles each, and some ranges empty)
+    assert attention_splits(4, 4091, sms, True) == 32
+    for pairs, longest in ((4, 4091), (16, 4091), (32, 4091), (8, 9000), (4, 700)):
+        n = attention_splits(pairs, longest, sms, True)
+        tiles = -(-(-(-longest // n)) // 64)
+        assert n == 1 or (n - 1) * tiles * 64 < longest <= n * tiles * 64
     assert attention_splits(4, 200, sms, True) == 1              # too short to split
     assert 32 < attention_splits(4, 100000, sms, True) <= 64     # batch 1, a very long context
     assert attention_splits(2048, 4096, sms, True) <= 2          # many pairs: waves, not splits
