@@ -60,7 +60,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // ROPE: the block's 16 rows are 8 rows of a head and the 8 rows half a head further on - the
 // two halves of 8 rotation pairs - and the epilogue is the one SkinnyRope describes.
 template <int TT, bool ROPE>
-__global__ void __launch_bounds__(32 * SK_WARPS)
+__global__ void __launch_bounds__(32 * SK_WARPS, 2)       // two blocks per SM: 64 registers at most
 gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
     extern __shared__ __align__(16) unsigned char sk_ring[];
     __shared__ float red[SK_WARPS * SK_ROWS * 8 * TT];            // [warp][16 rows][8 * TT]
@@ -138,8 +138,9 @@ gemm_skinny_kernel(const SkinnyParams p, const SkinnyRope rope) {
         slot = slot + 1 == SK_AHEAD ? 0 : slot + 1;
     };
     // the x values of four of the warp's chunks are asked for together: a trip to L2 per four chunks
-    // instead of one per chunk
-    constexpr int X_AHEAD = 4;
+    // instead of one per chunk (two chunks with more than 8 tokens: the registers of four would
+    // cost the second block that an SM holds)
+    constexpr int X_AHEAD = TT == 1 ? 4 : 2;
     for (int c0 = warp; c0 < chunks; c0 += X_AHEAD * SK_WARPS) {
         uint4 b[X_AHEAD][TT];
 #pragma unroll
