@@ -457,7 +457,7 @@ def main() -> int:
                         help="compute dtype of the whole run (the default run adds a short fp32 section)")
     parser.add_argument("--few-token-limit", type=int, default=0,
                         help="steps of up to this many tokens take the engine's few-token tcgen05 product "
-                             "(0 = the engine's choice, 16; up to 64 for measuring that choice)")
+                             "(0 = the engine's choice, 32; up to 64 for measuring that choice)")
     parser.add_argument("--timeline-of", default="decode", choices=["decode", "prefill"],
                         help="timeline: a decode step, or a step of one prompt of --prefill-tokens")
     parser.add_argument("--share-tiles", default="on", choices=["on", "off"],

@@ -27,8 +27,8 @@ def parse_dtype(name) -> torch.dtype:
 class Runtime:
     """Device and precision of one engine, and which kernel multiplies which step.
 
-    bfloat16: steps of up to 16 tokens take the engine's few-token products (tcgen05 for the
-    large matrices, a set-up-free mma.sync kernel for the small ones), steps with enough
+    bfloat16: steps of few tokens take the engine's few-token products (tcgen05 for the large
+    matrices up to 32 tokens, a set-up-free mma.sync kernel for the small ones up to 16), steps with enough
     256 x 256 output tiles to fill the GPU take the engine's tiled tcgen05 product, and the
     steps in between take the library product (cuBLAS through torch, bf16 operands, 32-bit
     accumulation), as the reference engine uses the library for its products
@@ -40,7 +40,7 @@ class Runtime:
     def __init__(self, device="cuda:0", dtype=torch.bfloat16, max_positions: int = 0,
                  few_token_min_elements: int = 32 * 1024 * 1024, products: str = "own",
                  tiled_min_tiles: Optional[int] = None,
-                 decode_tcgen05_min_blocks: Optional[int] = None, few_token_limit: int = 16,
+                 decode_tcgen05_min_blocks: Optional[int] = None, few_token_limit: int = 32,
                  share_tiles: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this engine has no CPU path")
@@ -57,8 +57,9 @@ class Runtime:
         self._few_token_weights: Dict[int, ops.DecodeWeight] = {}
         if not 1 <= few_token_limit <= ops.GEMM_DECODE_MAX_TOKENS:
             raise ValueError(f"few_token_limit must lie in 1..{ops.GEMM_DECODE_MAX_TOKENS}")
-        # steps of up to this many tokens take that product (16: beyond it the library measured
-        # faster; up to 64 is possible and is what measurements of that choice set)
+        # steps of up to this many tokens take that product (32: inside a decode step of 24 tokens
+        # it measured 2.5 % ahead of the library, at 32 level with it, at 64 4 % behind; up to 64 is
+        # possible and is what measurements of that choice set)
         self.few_token_limit = int(few_token_limit)
         self.few_token_limit_fused = int(few_token_limit)    # ... the same with the fused SwiGLU
         self.few_token_min_elements = few_token_min_elements   # ... for matrices at least this large
@@ -68,9 +69,11 @@ class Runtime:
             raise ValueError("products must be 'own' or 'library'")
         self.products = products
         self.tiled_min_tiles = tiled_min_tiles       # None: as many tiles as pairs of SMs run at once
-        # decode steps of 17-64 tokens keep the library product: alone the tiled kernel ties with it
-        # there, inside a captured decode step it measured 6 % slower (batch 64)
-        self.tiled_min_rows = 65 if tiled_min_tiles is None else self.few_token_limit + 1
+        # decode steps of up to 64 tokens that the few-token products do not take keep the library
+        # product: alone the tiled kernel ties with it there, inside a captured decode step it
+        # measured 6 % slower (batch 64); a test that forces the tiled product gets it for every step
+        # that is beyond the set-up-free kernel
+        self.tiled_min_rows = 65 if tiled_min_tiles is None else ops.GEMM_SKINNY_MAX_TOKENS + 1
         # matrices that may take the tiled product: storage address -> (weight, swiglu) until a step
         # qualifies, then its descriptor (made, and the kernel library compiled, only then)
         self._tiled_weights: Dict[int, object] = {}
