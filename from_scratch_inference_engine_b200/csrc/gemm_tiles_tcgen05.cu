@@ -606,6 +606,11 @@ static void plan_sharing(TileGemmParams& p, long long tiles, int pairs, long lon
     // traffic; and the adding of the parts hides under the whole tiles that follow, so without a
     // full round (fewer tiles than pairs: measured slower than leaving the tiles whole) nothing is shared.
     if (pairs < 2 || rest == 0 || tiles < pairs || rest * 10 >= pairs * 9) return;
+    // What sharing saves is the idle share of a tile's time, and a tile's time goes with k (about
+    // 20 us at k = 3,584); what it costs (the parts' trip through the workspace, about 10 us where
+    // it is not hidden) does not: with short k it pays only when most pairs would idle (measured:
+    // 112 tiles of k = 3,584 on 74 pairs gain nothing, 112 tiles of k = 18,944 gain 23 us of 203).
+    if ((long long)(pairs - rest) * p.K < 1800LL * pairs) return;
     // at most four pairs per tile (the pair that arrives last adds their parts), shares of two k-blocks at least
     int share_pairs = pairs < 3 * rest ? pairs : 3 * rest;
     const long long units = (long long)rest * kblocks;
