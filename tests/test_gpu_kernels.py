@@ -659,15 +659,16 @@ def test_gemm_tiles_swiglu_epilogue(ops, rows, inter, k, blocks):
     assert (out.double() - want).abs().max().item() < 2.5e-2 * want.abs().max().item()
 
 
-@pytest.mark.parametrize("rows,n,k,blocks,swiglu", [
-    (700, 1288, 1024, 10, False),      # 18 tiles on 5 pairs: 3 tiles shared out among 5
-    (2048, 3584, 512, 148, False),     # 112 tiles on 74 pairs: 38 shared out among 74, k-blocks cut 2 and 3 ways
-    (300, 2000, 2056, 148, False),     # fewer tiles than pairs never share; ragged k
-    (1000, 520, 1536, 12, False),      # 12 tiles on 6 pairs: a full last round
-    (515, 1100, 776, 14, True),        # SwiGLU: 27 tiles on 7 pairs, 6 shared; ragged everywhere
-    (2300, 300, 4096, 16, False),      # 18 tiles on 8 pairs: 2 shared four ways each
+@pytest.mark.parametrize("rows,n,k,blocks,swiglu,shares", [
+    (700, 1288, 6144, 10, False, True),     # 18 tiles on 5 pairs: 3 tiles shared out among 5
+    (2048, 3584, 4096, 148, False, True),   # 112 tiles on 74 pairs: 38 shared out among 74, k-blocks cut 2 and 3 ways
+    (2048, 3584, 512, 148, False, False),   # the same with a k so short that sharing would not pay
+    (300, 2000, 2056, 148, False, False),   # fewer tiles than pairs never share; ragged k
+    (1000, 520, 1536, 12, False, False),    # 12 tiles on 6 pairs: a full last round
+    (515, 1100, 6152, 20, True, True),      # SwiGLU: 27 tiles on 10 pairs, 7 shared; ragged everywhere
+    (2300, 300, 4096, 16, False, True),     # 18 tiles on 8 pairs: 2 shared three ways each
 ])
-def test_gemm_tiles_shares_a_partial_last_round(ops, rows, n, k, blocks, swiglu):
+def test_gemm_tiles_shares_a_partial_last_round(ops, rows, n, k, blocks, swiglu, shares):
     """With a workspace the tiles that do not fill a last round are cut along k among all pairs
     and the parts are added by whoever comes last, in the order of the shares: the result is
     the same on every run, equals the product, and the counters are left at zero."""
@@ -684,6 +685,7 @@ def test_gemm_tiles_shares_a_partial_last_round(ops, rows, n, k, blocks, swiglu)
         want = full + bias.double()
     weight = ops.TiledWeight(w, swiglu=swiglu)
     floats, ints = ops.gemm_tiles_workspace(rows, n, k, swiglu, blocks)
+    assert (floats > 0) == shares
     workspace = torch.full((max(floats, 1),), float("nan"), dtype=torch.float32, device="cuda")
     counters = torch.zeros(max(ints, 1), dtype=torch.int32, device="cuda")
     outs = []
