@@ -220,26 +220,35 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int ld, const int*
                                          long long page_stride, int page_size,
                                          int heads, int kv_heads, int head_dim, int rotary_dim,
                                          int write_cache, int* error) {
-    grid_dependency_wait();
-    grid_dependents_go();
+    // The token's position and slot were staged before the step and the table is a constant: they,
+    // and the angles of the first rotation item of each thread, are fetched while the kernel
+    // before this one (the q,k,v product) still runs.
     const int t = blockIdx.x;
     int pos = positions[t];
-    if (rotary_dim > 0 && (pos < 0 || pos >= table_len)) {
-        if (threadIdx.x == 0) atomicExch(error, 2);
-        pos = 0;
-    }
+    const bool refused = rotary_dim > 0 && (pos < 0 || pos >= table_len);
+    if (refused) pos = 0;
     const int half = rotary_dim / 2, hc = half / 8, pc = (head_dim - rotary_dim) / 8, dc = head_dim / 8;
     const float* cs = cos_sin + (size_t)pos * rotary_dim;
-    T* row = qkv + (size_t)t * ld;
     const int q_width = heads * head_dim, kv_width = kv_heads * head_dim;
     const int slot = write_cache ? slot_of[t] : -1;
     const bool store = slot >= 0;
+    const int n_q = heads * hc, n_k = kv_heads * hc, n_p = kv_heads * pc, n_v = kv_heads * dc;
+    const int total = n_q + (store ? n_k + n_p + n_v : 0);
+    float c_first[8], s_first[8];
+    if ((int)threadIdx.x < n_q + n_k && (int)threadIdx.x < total) {
+        const int w = (int)threadIdx.x < n_q ? threadIdx.x : threadIdx.x - n_q;
+        const int i = (w % hc) * 8;
+        load8(cs + i, c_first);
+        load8(cs + half + i, s_first);
+    }
+    grid_dependency_wait();
+    grid_dependents_go();
+    if (refused && threadIdx.x == 0) atomicExch(error, 2);
+    T* row = qkv + (size_t)t * ld;
     const long long page = store ? slot / page_size : 0;
     const int offset = store ? slot - (int)page * page_size : 0;
     T* kdst = k_pages + page * page_stride;
     T* vdst = v_pages + page * page_stride;
-    const int n_q = heads * hc, n_k = kv_heads * hc, n_p = kv_heads * pc, n_v = kv_heads * dc;
-    const int total = n_q + (store ? n_k + n_p + n_v : 0);
     for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
         if (idx < n_q + n_k) {
             const bool is_q = idx < n_q;
@@ -249,8 +258,13 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int ld, const int*
             float a[8], b[8], c[8], s[8], lo[8], hi[8];
             load8(head + i, a);
             load8(head + half + i, b);
-            load8(cs + i, c);
-            load8(cs + half + i, s);
+            if (idx == (int)threadIdx.x) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { c[e] = c_first[e]; s[e] = s_first[e]; }
+            } else {
+                load8(cs + i, c);
+                load8(cs + half + i, s);
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 lo[e] = a[e] * c[e] - b[e] * s[e];
