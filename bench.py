@@ -443,8 +443,10 @@ def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
-    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--steps", type=int, default=None,
+                        help="timed decode steps (default 64; with --impl reference 8: a step of the "
+                             "reference engine takes about 11 s)")
+    parser.add_argument("--warmup", type=int, default=None, help="untimed steps before them (default 8; reference 3)")
     parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=4096)
@@ -474,6 +476,10 @@ def main() -> int:
     parser.add_argument("--step-tokens", type=int, default=2048, help="serving: token budget of one step")
     parser.add_argument("--num-blocks", type=int, default=16384)
     args = parser.parse_args()
+    if args.steps is None:
+        args.steps = 8 if args.impl == "reference" else 64
+    if args.warmup is None:
+        args.warmup = 3 if args.impl == "reference" else 8
 
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
